@@ -1,0 +1,190 @@
+/*
+ * mograd_b200 -- C ABI of the B200 (sm_100a) kernel library that replaces
+ * mograd's Mojo kernel library (libmograd_gpu.so) on the training hot path.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE address unless its comment says "host";
+ *     pointers already include any view offset, as AnyBuffer.data_ptr() does
+ *     (mograd/buffer.mojo:62-67);
+ *   - the callee never allocates and never frees: the caller passes outputs
+ *     and, where a *_workspace_bytes query exists, a workspace of at least
+ *     that many bytes (256-byte aligned), both from its own allocator
+ *     (mograd/memory.mojo take_storage / scratch_take);
+ *   - every call only enqueues work on `stream` (a cudaStream_t passed as
+ *     void*; NULL = the legacy default stream) and returns; nothing
+ *     synchronises the device;
+ *   - return value 0 = enqueued; a negative MGB_E* code = nothing was
+ *     launched and mograd_b200_last_error() (thread-local) says why.  The
+ *     reference raises a Mojo Error in the same situations
+ *     (mograd/runtime/gpu/kernels/dispatch.mojo:564-576 for dtypes);
+ *   - dtype codes select the storage type of every tensor argument not
+ *     documented otherwise.  bf16 runs the GEMMs and attention on the
+ *     tcgen05 tensor cores with fp32 accumulation; f32 runs them on the
+ *     CUDA cores in fp32.  Statistics, softmax and reductions are fp32 for
+ *     both.
+ */
+#ifndef MOGRAD_B200_H_
+#define MOGRAD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOGRAD_B200_ABI_VERSION 1
+
+enum mgb_status {
+  MGB_OK = 0,
+  MGB_EINVAL = -1,       /* null pointer, non-positive or inconsistent dims   */
+  MGB_EDTYPE = -2,       /* dtype code not supported by this entry point      */
+  MGB_EALIGN = -3,       /* pointer / leading dimension alignment not met     */
+  MGB_EWORKSPACE = -4,   /* workspace missing or smaller than the query says  */
+  MGB_ECUDA = -5,        /* a CUDA runtime / driver call reported an error    */
+  MGB_EUNSUPPORTED = -6  /* valid request outside what the kernels implement  */
+};
+
+enum mgb_dtype {
+  MGB_BF16 = 0,
+  MGB_F32 = 1
+};
+
+/* Library identity.  No counterpart in the reference, whose Mojo ABI is
+ * locked to the toolchain version instead (scripts/build_gpu.sh:46-48). */
+int mograd_b200_abi_version(void);
+
+/* Message for the last negative status returned on this host thread. */
+const char* mograd_b200_last_error(void);
+
+/* Debug aid, synchronises the device: reads (and clears) the status word the
+ * tensor-core kernels write when one of their bounded waits on a TMA or MMA
+ * barrier gives up (code 0 = none; 101 producer, 102 MMA issuer, 103 epilogue
+ * of the GEMM; 2xx attention).  No counterpart in the reference. */
+int mograd_b200_device_status(int* code, int* detail);
+
+/* ------------------------------------------------------------------------
+ * matmul_bias_bt:  Y[m,n] = sum_k A[m,k] * W[n,k] + bias[n]
+ * Replaces mograd_matmul_bias_bt (mograd/runtime/gpu/kernels/__init__.mojo:
+ * 758-840; signature MatmulBiasStrided, dispatch.mojo:247-257).  Batch dims
+ * of A are collapsed into M by the caller, as the reference requires them to
+ * be collapsible (__init__.mojo:775-776).  bias may be NULL (= the
+ * reference's mograd_matmul_bt, __init__.mojo:688-755).  lda/ldw/ldy are row
+ * strides in elements.  act: 0 = none, 1 = ReLU applied to Y before the
+ * store (fuses the reference's separate mograd_relu launch).
+ * bf16 fast path needs 16-byte aligned A/W and lda, ldw multiples of 8;
+ * other bf16 shapes and all f32 calls take the CUDA-core kernel.
+ * ---------------------------------------------------------------------- */
+int mograd_b200_matmul_bias_bt(const void* a, const void* w, const void* bias, void* y, int64_t M, int64_t N,
+                               int64_t K, int64_t lda, int64_t ldw, int64_t ldy, int act, int dtype,
+                               void* stream);
+
+/* ------------------------------------------------------------------------
+ * Backward of matmul_bias_bt in one call (any of dx, dw, db may be NULL):
+ *   dX[m,k] = sum_n dY[m,n] W[n,k];  dW[n,k] = sum_m dY[m,n] X[m,k];
+ *   db[n] = sum_m dY[m,n].
+ * Replaces the primitive chain the reference's rules build today:
+ * matmul_grad (mograd/grad.mojo:180-183) + transpose_grad (:186-187) +
+ * add_grad (:126-127) + expand_grad -> sum_axis (:278-288), which run on
+ * mograd_matmul / mograd_matmul_bt (__init__.mojo:616-755) and mograd_sum.
+ * dW and db are written in `dtype`.  db is produced inside the dW GEMM from
+ * the dY tiles that pass through shared memory.
+ * ---------------------------------------------------------------------- */
+size_t mograd_b200_matmul_bias_bt_bwd_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
+int mograd_b200_matmul_bias_bt_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw, void* db,
+                                   int64_t M, int64_t N, int64_t K, int64_t lddy, int64_t ldx, int64_t ldw,
+                                   int64_t lddx, int64_t lddw, int dtype, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * LayerNorm forward over the last axis, biased variance:
+ *   y = (x - mean) * rsqrt(var + eps) * gamma + beta
+ * Replaces mograd_layer_norm_fwd (__init__.mojo:1309-1334; signature
+ * LayerNormFwdKernel, dispatch.mojo:281-291).  mean / rstd (float32, one per
+ * row) are optional extra outputs (NULL to skip); the reference saves none.
+ * ---------------------------------------------------------------------- */
+int mograd_b200_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                               float* rstd, int64_t rows, int64_t cols, float eps, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * LayerNorm backward: dx (rows x cols), dgamma, dbeta (cols), mean / rstd
+ * recomputed from x.  Replaces mograd_layer_norm_bwd (__init__.mojo:
+ * 1337-1366; signature LayerNormBwdKernel, dispatch.mojo:317-329; kernels
+ * mograd/runtime/gpu/kernels/normalization.mojo:85-400).  dgamma / dbeta are
+ * plain stores: the caller need not zero them (the reference's dispatch
+ * does, dispatch.mojo:343-344).  cols <= 16384, as in the reference.
+ * ---------------------------------------------------------------------- */
+size_t mograd_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t cols, int dtype);
+int mograd_b200_layer_norm_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dgamma,
+                               void* dbeta, int64_t rows, int64_t cols, float eps, int dtype, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Cross-entropy with dense float labels of the logits' shape, mean over
+ * rows; loss is one element of `dtype`.  Replaces mograd_cross_entropy /
+ * _strided (__init__.mojo:1374-1454; kernels cross_entropy.mojo:14-77,
+ * 155-177) without the reference's host synchronisation.  ldx / ldl are row
+ * strides in elements (the reference's strided variant takes full Layouts;
+ * row-strided views are what its callers produce).
+ * ---------------------------------------------------------------------- */
+size_t mograd_b200_cross_entropy_workspace_bytes(int64_t N, int64_t C, int dtype);
+int mograd_b200_cross_entropy(const void* logits, const void* labels, void* loss, int64_t N, int64_t C,
+                              int64_t ldx, int64_t ldl, int dtype, void* workspace, size_t workspace_bytes,
+                              void* stream);
+
+/* dst = (softmax(logits) - labels) * upstream[0] / N.  Replaces
+ * mograd_cross_entropy_grad / _strided (__init__.mojo:1462-1528; kernel
+ * cross_entropy.mojo:185-241; signature TernaryStrided, dispatch.mojo:
+ * 545-554).  upstream is a one-element device tensor of `dtype`. */
+int mograd_b200_cross_entropy_grad(const void* upstream, const void* logits, const void* labels, void* dst,
+                                   int64_t N, int64_t C, int64_t ldx, int64_t ldl, int64_t lddst, int dtype,
+                                   void* stream);
+
+/* ------------------------------------------------------------------------
+ * Fused softmax-cross-entropy forward + backward with one class index per
+ * row (labels[r] in [0, C), int64): reads the logits once, writes
+ *   loss (float32 scalar, mean over rows) and
+ *   dlogits = (softmax - onehot) * upstream / N   (never materialising the
+ * probabilities).  Same arithmetic as cross_entropy + cross_entropy_grad on
+ * the one-hot labels the reference's train loop builds
+ * (examples/tinyshakespear/train.mojo:38-41).  dlogits may alias logits.
+ * dlogits == NULL computes the loss only; loss == NULL the gradient only.
+ * ---------------------------------------------------------------------- */
+size_t mograd_b200_softmax_xent_workspace_bytes(int64_t N, int64_t C, int dtype);
+int mograd_b200_softmax_xent_fwd_bwd(const void* logits, const int64_t* labels, float* loss, void* dlogits,
+                                     int64_t N, int64_t C, int64_t ldx, int64_t lddx, float upstream,
+                                     int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Attention forward: O = softmax(scale * Q K^T [+ mask | causal]) V.
+ * Q, K, V are BSHD (B,S,H,D); O is BHSD; lse is float32 (B,H,S), natural
+ * log.  Replaces mograd_flash_attn_fwd (__init__.mojo:848-921; signature
+ * FlashAttnFwdKernel, dispatch.mojo:361-377).  mask is an additive
+ * (B,H,S,S) tensor of `dtype`, read only when has_bias != 0; causal and
+ * has_bias together are rejected as in the reference (__init__.mojo:
+ * 868-873).  1 <= D <= 512 (attention/dispatch.mojo:28-29).
+ * bf16, D in {64,128}, no bias: tcgen05 kernel; everything else: CUDA-core
+ * kernel.
+ * ---------------------------------------------------------------------- */
+int mograd_b200_flash_attn_fwd(const void* q, const void* k, const void* v, const void* mask, void* dst,
+                               float* lse, int64_t B, int64_t S, int64_t H, int64_t D, float scale, int causal,
+                               int has_bias, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Attention backward: dQ, dK, dV (BSHD, `dtype`) from dO and O (BHSD),
+ * Q, K, V (BSHD) and lse, recomputing the softmax tile by tile.  Replaces
+ * mograd_flash_attn_bwd (__init__.mojo:924-1006; signature
+ * FlashAttnBwdKernel, dispatch.mojo:418-438; kernels
+ * attention/nvidia_bwd.mojo:784-1575).  The workspace holds
+ * delta = rowsum(O * dO) and the float32 dQ accumulator.
+ * ---------------------------------------------------------------------- */
+size_t mograd_b200_flash_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype);
+int mograd_b200_flash_attn_bwd(const void* dy, const void* o, const void* q, const void* k, const void* v,
+                               const void* mask, const float* lse, void* dq, void* dk, void* dv, int64_t B,
+                               int64_t S, int64_t H, int64_t D, float scale, int causal, int has_bias,
+                               int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOGRAD_B200_H_ */

@@ -1,0 +1,128 @@
+// Library identity, thread-local error text and cached device attributes.
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace mgb {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(MGB_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+  return MGB_OK;
+}
+
+namespace {
+constexpr int kMaxDev = 64;
+struct DevInfo {
+  std::once_flag once;
+  int sms = 0;
+  int smem_optin = 0;
+};
+DevInfo g_dev[kMaxDev];
+
+DevInfo& dev_info() {
+  int d = 0;
+  cudaGetDevice(&d);
+  if (d < 0 || d >= kMaxDev) d = 0;
+  DevInfo& di = g_dev[d];
+  std::call_once(di.once, [&] {
+    cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, d);
+    cudaDeviceGetAttribute(&di.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d);
+    if (di.sms <= 0) di.sms = 148;
+  });
+  return di;
+}
+}  // namespace
+
+int sm_count() { return dev_info().sms; }
+int max_smem_optin() { return dev_info().smem_optin; }
+
+// ---------------------------------------------------------------- TMA maps
+namespace {
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::once_flag g_encode_once;
+EncodeTiledFn g_encode = nullptr;
+}  // namespace
+
+bool encode_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  if (!g_encode) {
+    fail(MGB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  const CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                              const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fail(MGB_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu, box %u x %u)",
+         static_cast<int>(r), rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 1), box[0],
+         rank > 1 ? box[1] : 1u);
+    return false;
+  }
+  return true;
+}
+
+// ------------------------------------------------------ device status word
+__device__ int g_device_status[4];
+
+int* device_status_ptr() {
+  static int* ptrs[kMaxDev] = {};
+  int d = 0;
+  cudaGetDevice(&d);
+  if (d < 0 || d >= kMaxDev) d = 0;
+  if (!ptrs[d]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) == cudaSuccess) ptrs[d] = static_cast<int*>(p);
+  }
+  return ptrs[d];
+}
+
+}  // namespace mgb
+
+MGB_EXPORT int mograd_b200_abi_version(void) { return MOGRAD_B200_ABI_VERSION; }
+MGB_EXPORT const char* mograd_b200_last_error(void) { return mgb::g_err; }
+
+MGB_EXPORT int mograd_b200_device_status(int* code, int* detail) {
+  int* p = mgb::device_status_ptr();
+  if (!p) return mgb::fail(MGB_ECUDA, "device_status: status word not addressable on this device");
+  int host[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpy(host, p, sizeof(host), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return mgb::fail(MGB_ECUDA, "device_status: %s", cudaGetErrorString(e));
+  if (code) *code = host[0];
+  if (detail) *detail = host[1];
+  if (host[0] != 0) {
+    e = cudaMemset(p, 0, sizeof(host));
+    if (e != cudaSuccess) return mgb::fail(MGB_ECUDA, "device_status reset: %s", cudaGetErrorString(e));
+  }
+  return MGB_OK;
+}

@@ -1,0 +1,596 @@
+// matmul_bias_bt forward and its backward (dX, dW, db).
+//
+// bf16 path: one persistent, warp-specialised tcgen05 kernel computes
+//     D[i,j] = sum_l A(i,l) * B(j,l)      (fp32 accumulation in TMEM)
+// for the three products of a Linear layer, which differ only in which
+// operand is K-major (contraction index contiguous in memory) or MN-major:
+//     Y  = X  . W^T : A = X  (K-major),  B = W (K-major)
+//     dX = dY . W   : A = dY (K-major),  B = W viewed [k][n] (MN-major)
+//     dW = dY^T . X : A = dY viewed [n][m] (MN-major), B = X viewed [k][m] (MN-major)
+// so no operand is ever transposed in memory.  Per CTA: warp 0 issues TMA
+// loads of 128-byte-swizzled tiles into a shared-memory ring, warp 1 issues
+// UMMA 128xBNx16 instructions into one of two TMEM accumulators, warps 2-5
+// drain the other accumulator (tcgen05.ld -> bias / ReLU -> bf16 -> global),
+// so the epilogue of tile t overlaps the main loop of tile t+1.  Tiles whose
+// output is small next to the contraction length (dW) are split along the
+// contraction; the fp32 partial tiles go to the workspace and a finalize
+// kernel adds them in a fixed order.
+//
+// f32 path and bf16 operands that TMA cannot address (leading dimension not a
+// multiple of 8 elements, unaligned base): a shared-memory tiled CUDA-core
+// kernel with fp32 accumulation.
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace mgb {
+namespace {
+
+using namespace sm100;
+using bf16 = __nv_bfloat16;
+
+constexpr int BM = 128;
+constexpr int BK = 64;     // bf16 elements per stage along the contraction = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+constexpr int kMaxSplits = 16;
+
+enum : int { kErrTmaWait = 101, kErrMmaWait = 102, kErrEpiWait = 103 };
+
+template <int BN>
+struct Tile {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+struct GemmParams {
+  int M, N, K;                 // D is M x N, contraction length K
+  int num_m, num_n, num_kb;    // tile counts
+  int splits, kb_per_split;
+  bf16* d;                     // output when splits == 1
+  int64_t ldd;
+  float* partial;              // [splits][M][N] when splits > 1
+  const bf16* bias;            // length N or nullptr (splits == 1 only)
+  int act;                     // 1 = ReLU
+  int* status;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                   const GemmParams p) {
+  using T = Tile<BN>;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + T::STAGES * T::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (T::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * T::STAGES + 4);
+  unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + T::STAGES * T::STAGE_BYTES +
+                                                                          8 * (2 * T::STAGES + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, T::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  const int tiles_mn = p.num_m * p.num_n;
+  const int total = tiles_mn * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int split = tile / tiles_mn;
+        const int rem = tile - split * tiles_mn;
+        const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            atomicExch(p.status, kErrTmaWait);
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
+          const uint32_t sb = sa + T::A_BYTES;
+          mbar_expect_tx(full_bar(stage), T::STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d(sa + i * (64 * BK * 2), &tma_a, full_bar(stage), m_blk * BM + i * 64, kb * BK);
+          } else {
+            tma_load_2d(sa, &tma_a, full_bar(stage), kb * BK, m_blk * BM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(sb + i * (64 * BK * 2), &tma_b, full_bar(stage), n_blk * BN + i * 64, kb * BK);
+          } else {
+            tma_load_2d(sb, &tma_b, full_bar(stage), kb * BK, n_blk * BN);
+          }
+          if (++stage == T::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+        const int split = tile / tiles_mn;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) {
+          atomicExch(p.status, kErrMmaWait);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            atomicExch(p.status, kErrMmaWait);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
+          const uint32_t sb = sa + T::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = A_MN ? smem_desc_sw128(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                        : smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = B_MN ? smem_desc_sw128(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                        : smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          if (++stage == T::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
+      const int split = tile / tiles_mn;
+      const int rem = tile - split * tiles_mn;
+      const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), acc_phase)) {
+        if (lane == 0) atomicExch(p.status, kErrEpiWait);
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col0 = n_blk * BN + c0;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld32(t_row + c0, r);
+        tmem_ld_wait();
+        if (row < p.M) {
+          if (p.splits > 1) {
+            float* dst = p.partial + (static_cast<int64_t>(split) * p.M + row) * p.N + col0;
+            if (col0 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
+            }
+          } else {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if (p.bias) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+            }
+            if (p.act == 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+            bf16* dst = p.d + static_cast<int64_t>(row) * p.ldd + col0;
+            if (col0 + 32 <= p.N && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(dst + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+// out[r][c] = T(sum_s partial[s][r][c]) (+ bias[c], ReLU); fixed summation order.
+__global__ void __launch_bounds__(256)
+    splitk_finalize_kernel(const float* __restrict__ partial, int splits, int M, int N, bf16* __restrict__ out,
+                           int64_t ldd, const bf16* __restrict__ bias, int act) {
+  const int64_t total = static_cast<int64_t>(M) * N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[s * total + i];
+    const int64_t r = i / N, c = i - r * N;
+    if (bias) acc += __bfloat162float(bias[c]);
+    if (act == 1) acc = fmaxf(acc, 0.f);
+    out[r * ldd + c] = __float2bfloat16_rn(acc);
+  }
+}
+
+// ------------------------------------------------------- CUDA-core fallback
+// D[i,j] = sum_l A[i*sai + l*sal] * B[j*sbj + l*sbl] (+ bias[j], ReLU), fp32 accumulation.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ bias, T* __restrict__ d,
+                     int M, int N, int K, int64_t sai, int64_t sal, int64_t sbj, int64_t sbl, int64_t ldd, int act) {
+  constexpr int TM = 64, TN = 64, TK = 16;
+  __shared__ float As[TK][TM + 1];
+  __shared__ float Bs[TK][TN + 1];
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const int i0 = blockIdx.y * TM, j0 = blockIdx.x * TN;
+  float acc[4][4] = {};
+  for (int l0 = 0; l0 < K; l0 += TK) {
+    for (int e = threadIdx.x; e < TM * TK; e += 256) {
+      // consecutive threads walk whichever index is contiguous in memory
+      int i, l;
+      if (sal == 1) {
+        l = e % TK;
+        i = e / TK;
+      } else {
+        i = e % TM;
+        l = e / TM;
+      }
+      const int gi = i0 + i, gl = l0 + l;
+      As[l][i] = (gi < M && gl < K) ? to_f32(a[gi * sai + gl * sal]) : 0.f;
+    }
+    for (int e = threadIdx.x; e < TN * TK; e += 256) {
+      int j, l;
+      if (sbl == 1) {
+        l = e % TK;
+        j = e / TK;
+      } else {
+        j = e % TN;
+        l = e / TN;
+      }
+      const int gj = j0 + j, gl = l0 + l;
+      Bs[l][j] = (gj < N && gl < K) ? to_f32(b[gj * sbj + gl * sbl]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int l = 0; l < TK; ++l) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        av[u] = As[l][ty * 4 + u];
+        bv[u] = Bs[l][tx * 4 + u];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[u][v] = fmaf(av[u], bv[v], acc[u][v]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int gi = i0 + ty * 4 + u;
+    if (gi >= M) continue;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int gj = j0 + tx * 4 + v;
+      if (gj >= N) continue;
+      float r = acc[u][v];
+      if (bias) r += to_f32(bias[gj]);
+      if (act == 1) r = fmaxf(r, 0.f);
+      d[static_cast<int64_t>(gi) * ldd + gj] = from_f32<T>(r);
+    }
+  }
+}
+
+// db[n] = sum_m dY[m][n]: each block owns 32 columns and all rows; fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    colsum_kernel(const T* __restrict__ dy, T* __restrict__ db, int M, int N, int64_t ld) {
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
+  float acc = 0.f;
+  if (col < N)
+    for (int m = ry; m < M; m += 8) acc += to_f32(dy[static_cast<int64_t>(m) * ld + col]);
+  red[ry][cx] = acc;
+  __syncthreads();
+  if (ry == 0 && col < N) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += red[i][cx];
+    db[col] = from_f32<T>(s);
+  }
+}
+
+// ------------------------------------------------------------------- host
+struct Operand {
+  const void* ptr;
+  int64_t rows;   // number of rows in memory
+  int64_t cols;   // contiguous extent
+  int64_t ld;     // row stride in elements
+};
+
+bool tma_ok(const Operand& o) { return aligned16(o.ptr) && (o.ld % 8 == 0) && o.ld >= o.cols; }
+
+// Map over a row-major bf16 matrix; box = box_cols x box_rows.
+bool make_map(CUtensorMap* m, const Operand& o, uint32_t box_cols, uint32_t box_rows) {
+  const uint64_t dims[2] = {static_cast<uint64_t>(o.cols), static_cast<uint64_t>(o.rows)};
+  const uint64_t strides[1] = {static_cast<uint64_t>(o.ld) * 2};
+  const uint32_t box[2] = {box_cols, box_rows};
+  return encode_tmap_bf16(m, o.ptr, 2, dims, strides, box);
+}
+
+size_t splitk_bytes(int64_t M, int64_t N, int splits) {
+  return splits > 1 ? round_up(static_cast<size_t>(splits) * M * N * sizeof(float), 256) : 0;
+}
+
+// Split the contraction when the output has too few tiles to fill the GPU.
+int choose_splits(int64_t M, int64_t N, int64_t K, int BN) {
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int64_t num_kb = (K + BK - 1) / BK;
+  const int sms = sm_count();
+  if (tiles * 2 > sms || num_kb < 16) return 1;
+  int64_t s = sms / tiles;
+  if (s > num_kb / 8) s = num_kb / 8;
+  if (s > kMaxSplits) s = kMaxSplits;
+  return s < 1 ? 1 : static_cast<int>(s);
+}
+
+int choose_bn(int64_t N) { return N > 128 ? 256 : 128; }
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st) {
+  using T = Tile<BN>;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, a, 64, A_MN ? BK : BM)) return MGB_ECUDA;
+  if (!make_map(&mb, b, 64, B_MN ? BK : BN)) return MGB_ECUDA;
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN>;
+  static bool attr_done = false;  // per instantiation; the attribute is per function and device
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done || attr_dev != dev) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(MGB_ECUDA, "gemm smem opt-in (%d B): %s", T::SMEM_BYTES, cudaGetErrorString(e));
+    attr_done = true;
+    attr_dev = dev;
+  }
+  const int total = p.num_m * p.num_n * p.splits;
+  const int grid = total < sm_count() ? total : sm_count();
+  kern<<<grid, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
+  return check_launch("gemm_tc_kernel");
+}
+
+// D[M,N] = A . B^T style product on tensor cores; operands described as they lie in memory.
+template <bool A_MN, bool B_MN>
+int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const bf16* bias, int act, int64_t M, int64_t N,
+            int64_t K, void* ws, size_t ws_bytes, bool allow_split, cudaStream_t st) {
+  const int BN = choose_bn(N);
+  GemmParams p{};
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.num_m = static_cast<int>((M + BM - 1) / BM);
+  p.num_n = static_cast<int>((N + BN - 1) / BN);
+  p.num_kb = static_cast<int>((K + BK - 1) / BK);
+  p.splits = allow_split ? choose_splits(M, N, K, BN) : 1;
+  if (p.splits > 1 && (!ws || ws_bytes < splitk_bytes(M, N, p.splits))) p.splits = 1;
+  p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
+  p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  p.d = d;
+  p.ldd = ldd;
+  p.partial = static_cast<float*>(ws);
+  p.bias = p.splits > 1 ? nullptr : bias;
+  p.act = p.splits > 1 ? 0 : act;
+  p.status = device_status_ptr();
+  if (!p.status) return fail(MGB_ECUDA, "gemm: device status word unavailable");
+  int rc = BN == 256 ? launch_tc<256, A_MN, B_MN>(a, b, p, st) : launch_tc<128, A_MN, B_MN>(a, b, p, st);
+  if (rc != MGB_OK) return rc;
+  if (p.splits > 1) {
+    const int64_t total = M * N;
+    int grid = static_cast<int>((total + 255) / 256);
+    if (grid > sm_count() * 8) grid = sm_count() * 8;
+    splitk_finalize_kernel<<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, act);
+    rc = check_launch("splitk_finalize_kernel");
+  }
+  return rc;
+}
+
+template <typename T>
+int gemm_simt(const T* a, const T* b, const T* bias, T* d, int64_t M, int64_t N, int64_t K, int64_t sai, int64_t sal,
+              int64_t sbj, int64_t sbl, int64_t ldd, int act, cudaStream_t st) {
+  dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
+  MGB_REQUIRE(grid.y <= 65535, MGB_EUNSUPPORTED, "matmul: M=%lld too large for the CUDA-core kernel", (long long)M);
+  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a, b, bias, d, static_cast<int>(M), static_cast<int>(N),
+                                            static_cast<int>(K), sai, sal, sbj, sbl, ldd, act);
+  return check_launch("gemm_simt_kernel");
+}
+
+int check_dims(const char* who, int64_t M, int64_t N, int64_t K) {
+  MGB_REQUIRE(M > 0 && N > 0 && K > 0, MGB_EINVAL, "%s: M=%lld N=%lld K=%lld must be positive", who, (long long)M,
+              (long long)N, (long long)K);
+  MGB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), MGB_EUNSUPPORTED, "%s: dimension exceeds 2^31",
+              who);
+  return MGB_OK;
+}
+
+}  // namespace
+}  // namespace mgb
+
+using namespace mgb;
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt(const void* a, const void* w, const void* bias, void* y, int64_t M,
+                                          int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldy, int act,
+                                          int dtype, void* stream) {
+  MGB_REQUIRE(a && w && y, MGB_EINVAL, "matmul_bias_bt: NULL argument");
+  int rc = check_dims("matmul_bias_bt", M, N, K);
+  if (rc != MGB_OK) return rc;
+  MGB_REQUIRE(lda >= K && ldw >= K && ldy >= N, MGB_EINVAL, "matmul_bias_bt: leading dimension too small");
+  MGB_REQUIRE(act == 0 || act == 1, MGB_EINVAL, "matmul_bias_bt: act=%d (0 none, 1 relu)", act);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MGB_F32)
+    return gemm_simt<float>(static_cast<const float*>(a), static_cast<const float*>(w),
+                            static_cast<const float*>(bias), static_cast<float*>(y), M, N, K, lda, 1, ldw, 1, ldy, act,
+                            st);
+  MGB_REQUIRE(dtype == MGB_BF16, MGB_EDTYPE, "matmul_bias_bt: unsupported dtype code %d", dtype);
+  const Operand oa{a, M, K, lda}, ow{w, N, K, ldw};
+  if (tma_ok(oa) && tma_ok(ow))
+    return gemm_tc<false, false>(oa, ow, static_cast<bf16*>(y), ldy, static_cast<const bf16*>(bias), act, M, N, K,
+                                 nullptr, 0, false, st);
+  return gemm_simt<bf16>(static_cast<const bf16*>(a), static_cast<const bf16*>(w), static_cast<const bf16*>(bias),
+                         static_cast<bf16*>(y), M, N, K, lda, 1, ldw, 1, ldy, act, st);
+}
+
+MGB_EXPORT size_t mograd_b200_matmul_bias_bt_bwd_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
+  if (dtype != MGB_BF16 || M <= 0 || N <= 0 || K <= 0) return 0;
+  // dW is N x K with contraction M; dX is M x K with contraction N (never split: M is the large dim).
+  const size_t dw = splitk_bytes(N, K, kMaxSplits);
+  return dw;
+}
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw,
+                                              void* db, int64_t M, int64_t N, int64_t K, int64_t lddy, int64_t ldx,
+                                              int64_t ldw, int64_t lddx, int64_t lddw, int dtype, void* workspace,
+                                              size_t workspace_bytes, void* stream) {
+  MGB_REQUIRE(dy, MGB_EINVAL, "matmul_bias_bt_bwd: dy is NULL");
+  MGB_REQUIRE(dx || dw || db, MGB_EINVAL, "matmul_bias_bt_bwd: no output requested");
+  MGB_REQUIRE(!dx || w, MGB_EINVAL, "matmul_bias_bt_bwd: dX needs W");
+  MGB_REQUIRE(!dw || x, MGB_EINVAL, "matmul_bias_bt_bwd: dW needs X");
+  int rc = check_dims("matmul_bias_bt_bwd", M, N, K);
+  if (rc != MGB_OK) return rc;
+  MGB_REQUIRE(lddy >= N && (!dx || (ldw >= K && lddx >= K)) && (!dw || (ldx >= K && lddw >= K)), MGB_EINVAL,
+              "matmul_bias_bt_bwd: leading dimension too small");
+  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32, MGB_EDTYPE, "matmul_bias_bt_bwd: unsupported dtype code %d", dtype);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MGB_F32) {
+    const float* dyf = static_cast<const float*>(dy);
+    if (dx) {
+      // dX[m,k] = sum_n dY[m,n] W[n,k]: A = dY (i=m, l=n), B(j=k, l=n) = W[n*ldw + k]
+      rc = gemm_simt<float>(dyf, static_cast<const float*>(w), nullptr, static_cast<float*>(dx), M, K, N, lddy, 1, 1,
+                            ldw, lddx, 0, st);
+      if (rc != MGB_OK) return rc;
+    }
+    if (dw) {
+      // dW[n,k] = sum_m dY[m,n] X[m,k]: A(i=n, l=m) = dY[m*lddy + n], B(j=k, l=m) = X[m*ldx + k]
+      rc = gemm_simt<float>(dyf, static_cast<const float*>(x), nullptr, static_cast<float*>(dw), N, K, M, 1, lddy, 1,
+                            ldx, lddw, 0, st);
+      if (rc != MGB_OK) return rc;
+    }
+    if (db) {
+      colsum_kernel<float><<<static_cast<unsigned>((N + 31) / 32), 256, 0, st>>>(dyf, static_cast<float*>(db),
+                                                                               static_cast<int>(M),
+                                                                               static_cast<int>(N), lddy);
+      rc = check_launch("colsum_kernel");
+    }
+    return rc;
+  }
+  const bf16* dyb = static_cast<const bf16*>(dy);
+  const Operand ody{dy, M, N, lddy};
+  if (dx) {
+    const Operand ow{w, N, K, ldw};
+    if (tma_ok(ody) && tma_ok(ow))
+      rc = gemm_tc<false, true>(ody, ow, static_cast<bf16*>(dx), lddx, nullptr, 0, M, K, N, nullptr, 0, false, st);
+    else
+      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(w), nullptr, static_cast<bf16*>(dx), M, K, N, lddy, 1, 1, ldw,
+                           lddx, 0, st);
+    if (rc != MGB_OK) return rc;
+  }
+  if (dw) {
+    const Operand ox{x, M, K, ldx};
+    if (tma_ok(ody) && tma_ok(ox))
+      rc = gemm_tc<true, true>(ody, ox, static_cast<bf16*>(dw), lddw, nullptr, 0, N, K, M, workspace, workspace_bytes,
+                               true, st);
+    else
+      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(x), nullptr, static_cast<bf16*>(dw), N, K, M, 1, lddy, 1, ldx,
+                           lddw, 0, st);
+    if (rc != MGB_OK) return rc;
+  }
+  if (db) {
+    colsum_kernel<bf16><<<static_cast<unsigned>((N + 31) / 32), 256, 0, st>>>(dyb, static_cast<bf16*>(db),
+                                                                            static_cast<int>(M), static_cast<int>(N),
+                                                                            lddy);
+    rc = check_launch("colsum_kernel");
+  }
+  return rc;
+}

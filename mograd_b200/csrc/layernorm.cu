@@ -1,0 +1,481 @@
+// LayerNorm forward and fused backward (dx, dgamma, dbeta).
+//
+// Bandwidth-bound design.  A "team" of WPR warps owns one row at a time; each
+// lane keeps its CHUNKS 16-byte slices of x and dy in registers, so every
+// element of x and dy is read from HBM exactly once and dx written once
+// (the reference makes three passes over x and two over dy per row,
+// mograd/runtime/gpu/kernels/normalization.mojo:126-170).  Row statistics use
+// warp shuffles (plus one shared-memory hop when WPR > 1).  The grid is
+// persistent (a multiple of the SM count); every lane accumulates its columns'
+// dgamma / dbeta contributions in fp32 registers across all rows its team
+// visits, teams are folded inside the CTA, each CTA writes one partial row to
+// the workspace and a second small kernel sums the partial rows in a fixed
+// order.  Both statistics and partials are fp32 (the reference accumulates
+// the partials in the I/O dtype, normalization.mojo:114-115).
+#include "common.cuh"
+
+namespace mgb {
+namespace {
+
+constexpr int kMinWarps = 8;
+constexpr int kFinCols = 16;   // finalize kernel: columns per block
+constexpr int kFinLanes = 16;  // finalize kernel: partial-row lanes per column
+
+template <typename T>
+__device__ __forceinline__ void unpack(const uint4& r, float (&v)[Vec<T>::N]) {
+  load_vec(reinterpret_cast<const T*>(&r), v);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack(const float (&v)[Vec<T>::N]) {
+  uint4 r;
+  store_vec(reinterpret_cast<T*>(&r), v);
+  return r;
+}
+
+// Loads Vec<T>::N elements starting at column `col` of a row; out-of-range
+// columns read as zero.
+template <typename T, bool VEC>
+__device__ __forceinline__ uint4 load_chunk(const T* row, int64_t col, int64_t cols) {
+  constexpr int V = Vec<T>::N;
+  if (VEC) {
+    if (col < cols) return *reinterpret_cast<const uint4*>(row + col);
+    return make_uint4(0, 0, 0, 0);
+  } else {
+    union {
+      uint4 u;
+      T e[V];
+    } t;
+    t.u = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      if (col + j < cols) t.e[j] = row[col + j];
+    return t.u;
+  }
+}
+
+template <typename T, bool VEC>
+__device__ __forceinline__ void store_chunk(T* row, int64_t col, int64_t cols, const uint4& r) {
+  constexpr int V = Vec<T>::N;
+  if (VEC) {
+    if (col < cols) *reinterpret_cast<uint4*>(row + col) = r;
+  } else {
+    const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      if (col + j < cols) row[col + j] = e[j];
+  }
+}
+
+// Sums (a, b) over the team's WPR warps.  `red` holds 2 floats per warp.
+template <int WPR>
+__device__ __forceinline__ void team_sum2(float& a, float& b, float* red, int warp, int team, int lane) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if (WPR > 1) {
+    if (lane == 0) {
+      red[2 * warp] = a;
+      red[2 * warp + 1] = b;
+    }
+    __syncthreads();
+    a = 0.f;
+    b = 0.f;
+#pragma unroll
+    for (int w = 0; w < WPR; ++w) {
+      a += red[2 * (team * WPR + w)];
+      b += red[2 * (team * WPR + w) + 1];
+    }
+  }
+}
+
+template <int WPR>
+struct Shape {
+  static constexpr int WARPS = WPR > kMinWarps ? WPR : kMinWarps;
+  static constexpr int TEAMS = WARPS / WPR;
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr int MIN_CTAS = THREADS <= 256 ? 2 : 1;  // register cap: 128 per thread at 256 threads
+};
+
+template <typename T, int WPR, int CHUNKS, bool VEC>
+__global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
+    ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                  T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t rows,
+                  int64_t cols, float eps) {
+  constexpr int V = Vec<T>::N;
+  using S = Shape<WPR>;
+  __shared__ float redA[2 * S::WARPS];
+  __shared__ float redB[2 * S::WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int team = warp / WPR;
+  const int lt = (warp % WPR) * 32 + lane;
+  const float inv_n = 1.f / static_cast<float>(cols);
+
+  uint4 g_raw[CHUNKS], b_raw[CHUNKS];
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+    g_raw[j] = load_chunk<T, VEC>(gamma, col, cols);
+    b_raw[j] = load_chunk<T, VEC>(beta, col, cols);
+  }
+
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * S::TEAMS; r0 < rows;
+       r0 += static_cast<int64_t>(gridDim.x) * S::TEAMS) {
+    const int64_t row = r0 + team;
+    const bool live = row < rows;
+    const T* xr = x + (live ? row : 0) * cols;
+    uint4 x_raw[CHUNKS];
+    float sx = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+      x_raw[j] = live ? load_chunk<T, VEC>(xr, col, cols) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      float v[V];
+      unpack<T>(x_raw[j], v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) sx += v[e];
+    }
+    float dummy = 0.f;
+    team_sum2<WPR>(sx, dummy, redA, warp, team, lane);
+    const float mu = sx * inv_n;
+    // second moment about the mean; out-of-range columns hold 0 and must not count
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+      float v[V];
+      unpack<T>(x_raw[j], v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float d = (col + e < cols) ? v[e] - mu : 0.f;
+        sq = fmaf(d, d, sq);
+      }
+    }
+    dummy = 0.f;
+    team_sum2<WPR>(sq, dummy, redB, warp, team, lane);
+    const float rs = rsqrtf(sq * inv_n + eps);
+    if (live) {
+      T* yr = y + row * cols;
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+        float v[V], g[V], b[V], o[V];
+        unpack<T>(x_raw[j], v);
+        unpack<T>(g_raw[j], g);
+        unpack<T>(b_raw[j], b);
+#pragma unroll
+        for (int e = 0; e < V; ++e) o[e] = fmaf((v[e] - mu) * rs, g[e], b[e]);
+        store_chunk<T, VEC>(yr, col, cols, pack<T>(o));
+      }
+      if (lt == 0) {
+        if (mean) mean[row] = mu;
+        if (rstd) rstd[row] = rs;
+      }
+    }
+  }
+}
+
+template <typename T, int WPR, int CHUNKS, bool VEC>
+__global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
+    ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                  T* __restrict__ dx, float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
+  constexpr int V = Vec<T>::N;
+  using S = Shape<WPR>;
+  extern __shared__ float fold[];  // [2][cols]: dgamma then dbeta, folded over the CTA's teams
+  __shared__ float redA[2 * S::WARPS];
+  __shared__ float redB[2 * S::WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int team = warp / WPR;
+  const int lt = (warp % WPR) * 32 + lane;
+  const float inv_n = 1.f / static_cast<float>(cols);
+
+  uint4 g_raw[CHUNKS];
+  float dg[CHUNKS][V], db[CHUNKS][V];
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+    g_raw[j] = load_chunk<T, VEC>(gamma, col, cols);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      dg[j][e] = 0.f;
+      db[j][e] = 0.f;
+    }
+  }
+
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * S::TEAMS; r0 < rows;
+       r0 += static_cast<int64_t>(gridDim.x) * S::TEAMS) {
+    const int64_t row = r0 + team;
+    const bool live = row < rows;
+    const T* xr = x + (live ? row : 0) * cols;
+    const T* dyr = dy + (live ? row : 0) * cols;
+    uint4 x_raw[CHUNKS], dy_raw[CHUNKS];
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+      x_raw[j] = live ? load_chunk<T, VEC>(xr, col, cols) : make_uint4(0, 0, 0, 0);
+      dy_raw[j] = live ? load_chunk<T, VEC>(dyr, col, cols) : make_uint4(0, 0, 0, 0);
+    }
+    // mean and E[x^2] (the reference's statistic: var = E[x^2] - mu^2 clamped at 0)
+    float sx = 0.f, sx2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      float v[V];
+      unpack<T>(x_raw[j], v);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        sx += v[e];
+        sx2 = fmaf(v[e], v[e], sx2);
+      }
+    }
+    team_sum2<WPR>(sx, sx2, redA, warp, team, lane);
+    const float mu = sx * inv_n;
+    const float rs = rsqrtf(fmaxf(sx2 * inv_n - mu * mu, 0.f) + eps);
+    // c1 = mean(dy * gamma), c2 = mean(dy * gamma * xhat); padded columns hold dy = 0
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      float v[V], d[V], g[V];
+      unpack<T>(x_raw[j], v);
+      unpack<T>(dy_raw[j], d);
+      unpack<T>(g_raw[j], g);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float dyg = d[e] * g[e];
+        c1 += dyg;
+        c2 = fmaf(dyg, (v[e] - mu) * rs, c2);
+      }
+    }
+    team_sum2<WPR>(c1, c2, redB, warp, team, lane);
+    c1 *= inv_n;
+    c2 *= inv_n;
+    if (live) {
+      T* dxr = dx + row * cols;
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+        float v[V], d[V], g[V], o[V];
+        unpack<T>(x_raw[j], v);
+        unpack<T>(dy_raw[j], d);
+        unpack<T>(g_raw[j], g);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float xhat = (v[e] - mu) * rs;
+          o[e] = rs * (d[e] * g[e] - c1 - xhat * c2);
+          dg[j][e] = fmaf(d[e], xhat, dg[j][e]);
+          db[j][e] += d[e];
+        }
+        store_chunk<T, VEC>(dxr, col, cols, pack<T>(o));
+      }
+    }
+  }
+
+  // fold the teams' column partials inside the CTA, one team per round
+  for (int t = 0; t < S::TEAMS; ++t) {
+    if (team == t) {
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          if (col + e < cols) {
+            if (t == 0) {
+              fold[col + e] = dg[j][e];
+              fold[cols + col + e] = db[j][e];
+            } else {
+              fold[col + e] += dg[j][e];
+              fold[cols + col + e] += db[j][e];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* prow = part + static_cast<int64_t>(blockIdx.x) * 2 * cols;
+  for (int64_t c = threadIdx.x; c < 2 * cols; c += S::THREADS) prow[c] = fold[c];
+}
+
+// dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c], fixed order.
+template <typename T>
+__global__ void __launch_bounds__(kFinCols* kFinLanes)
+    ln_bwd_finalize_kernel(const float* __restrict__ part, int nparts, int64_t cols, T* __restrict__ dgamma,
+                           T* __restrict__ dbeta) {
+  __shared__ float red[kFinLanes][kFinCols + 1];
+  const int cx = threadIdx.x % kFinCols, ry = threadIdx.x / kFinCols;
+  const int64_t c2 = static_cast<int64_t>(blockIdx.x) * kFinCols + cx;  // index into [2*cols]
+  float acc = 0.f;
+  if (c2 < 2 * cols)
+    for (int p = ry; p < nparts; p += kFinLanes) acc += part[static_cast<int64_t>(p) * 2 * cols + c2];
+  red[ry][cx] = acc;
+  __syncthreads();
+  if (ry == 0 && c2 < 2 * cols) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kFinLanes; ++i) s += red[i][cx];
+    if (c2 < cols)
+      dgamma[c2] = from_f32<T>(s);
+    else
+      dbeta[c2 - cols] = from_f32<T>(s);
+  }
+}
+
+struct Plan {
+  int wpr, chunks, grid;
+};
+
+template <typename T>
+bool make_plan(int64_t rows, int64_t cols, Plan& pl) {
+  constexpr int V = Vec<T>::N;
+  int wpr = 1;
+  while (wpr <= 32 && static_cast<int64_t>(V) * 32 * wpr * 4 < cols) wpr *= 2;
+  if (wpr > 32) return false;
+  pl.wpr = wpr;
+  pl.chunks = static_cast<int>((cols + static_cast<int64_t>(V) * 32 * wpr - 1) / (static_cast<int64_t>(V) * 32 * wpr));
+  const int warps = wpr > kMinWarps ? wpr : kMinWarps;
+  const int teams = warps / wpr;
+  const int ctas_per_sm = warps >= 32 ? 1 : 2;
+  int64_t grid = static_cast<int64_t>(sm_count()) * ctas_per_sm;
+  const int64_t need = (rows + teams - 1) / teams;
+  if (grid > need) grid = need;
+  pl.grid = static_cast<int>(grid);
+  return true;
+}
+
+template <typename T, int WPR, int CHUNKS>
+int launch_fwd(const T* x, const T* g, const T* b, T* y, float* mean, float* rstd, int64_t rows, int64_t cols,
+               float eps, bool vec, int grid, cudaStream_t st) {
+  constexpr int TH = Shape<WPR>::THREADS;
+  if (vec)
+    ln_fwd_kernel<T, WPR, CHUNKS, true><<<grid, TH, 0, st>>>(x, g, b, y, mean, rstd, rows, cols, eps);
+  else
+    ln_fwd_kernel<T, WPR, CHUNKS, false><<<grid, TH, 0, st>>>(x, g, b, y, mean, rstd, rows, cols, eps);
+  return check_launch("ln_fwd_kernel");
+}
+
+template <typename T, int WPR, int CHUNKS>
+int launch_bwd(const T* dy, const T* x, const T* g, T* dx, float* part, int64_t rows, int64_t cols, float eps,
+               bool vec, int grid, cudaStream_t st) {
+  constexpr int TH = Shape<WPR>::THREADS;
+  const size_t smem = static_cast<size_t>(2 * cols) * sizeof(float);
+  if (vec) {
+    auto k = ln_bwd_kernel<T, WPR, CHUNKS, true>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    k<<<grid, TH, smem, st>>>(dy, x, g, dx, part, rows, cols, eps);
+  } else {
+    auto k = ln_bwd_kernel<T, WPR, CHUNKS, false>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    k<<<grid, TH, smem, st>>>(dy, x, g, dx, part, rows, cols, eps);
+  }
+  return check_launch("ln_bwd_kernel");
+}
+
+#define MGB_LN_DISPATCH(FN, ...)                                            \
+  switch (pl.wpr * 8 + pl.chunks) {                                         \
+    case 1 * 8 + 1: return FN<T, 1, 1>(__VA_ARGS__);                        \
+    case 1 * 8 + 2: return FN<T, 1, 2>(__VA_ARGS__);                        \
+    case 1 * 8 + 3: return FN<T, 1, 3>(__VA_ARGS__);                        \
+    case 1 * 8 + 4: return FN<T, 1, 4>(__VA_ARGS__);                        \
+    case 2 * 8 + 3: return FN<T, 2, 3>(__VA_ARGS__);                        \
+    case 2 * 8 + 4: return FN<T, 2, 4>(__VA_ARGS__);                        \
+    case 4 * 8 + 3: return FN<T, 4, 3>(__VA_ARGS__);                        \
+    case 4 * 8 + 4: return FN<T, 4, 4>(__VA_ARGS__);                        \
+    case 8 * 8 + 3: return FN<T, 8, 3>(__VA_ARGS__);                        \
+    case 8 * 8 + 4: return FN<T, 8, 4>(__VA_ARGS__);                        \
+    case 16 * 8 + 3: return FN<T, 16, 3>(__VA_ARGS__);                      \
+    case 16 * 8 + 4: return FN<T, 16, 4>(__VA_ARGS__);                      \
+    case 32 * 8 + 3: return FN<T, 32, 3>(__VA_ARGS__);                      \
+    case 32 * 8 + 4: return FN<T, 32, 4>(__VA_ARGS__);                      \
+    default: return fail(MGB_EUNSUPPORTED, "layer_norm: no kernel for wpr=%d chunks=%d", pl.wpr, pl.chunks); \
+  }
+
+template <typename T>
+int ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int64_t rows,
+           int64_t cols, float eps, cudaStream_t st) {
+  Plan pl;
+  if (!make_plan<T>(rows, cols, pl))
+    return fail(MGB_EUNSUPPORTED, "layer_norm_fwd: cols=%lld exceeds 16384", (long long)cols);
+  const bool vec = (cols % Vec<T>::N == 0) && aligned16(x) && aligned16(gamma) && aligned16(beta) && aligned16(y);
+  MGB_LN_DISPATCH(launch_fwd, static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta),
+                  static_cast<T*>(y), mean, rstd, rows, cols, eps, vec, pl.grid, st)
+}
+
+template <typename T>
+int ln_bwd_main(const void* dy, const void* x, const void* gamma, void* dx, float* part, int64_t rows,
+                int64_t cols, float eps, const Plan& pl, cudaStream_t st) {
+  const bool vec = (cols % Vec<T>::N == 0) && aligned16(x) && aligned16(gamma) && aligned16(dy) && aligned16(dx);
+  MGB_LN_DISPATCH(launch_bwd, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma),
+                  static_cast<T*>(dx), part, rows, cols, eps, vec, pl.grid, st)
+}
+
+template <typename T>
+int ln_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dgamma, void* dbeta, int64_t rows,
+           int64_t cols, float eps, void* ws, size_t ws_bytes, cudaStream_t st) {
+  Plan pl;
+  if (!make_plan<T>(rows, cols, pl))
+    return fail(MGB_EUNSUPPORTED, "layer_norm_bwd: cols=%lld exceeds 16384", (long long)cols);
+  const size_t need = static_cast<size_t>(pl.grid) * 2 * cols * sizeof(float);
+  MGB_REQUIRE(ws && ws_bytes >= need, MGB_EWORKSPACE, "layer_norm_bwd: workspace of %zu bytes needed, %zu given", need,
+              ws ? ws_bytes : (size_t)0);
+  float* part = static_cast<float*>(ws);
+  int rc = ln_bwd_main<T>(dy, x, gamma, dx, part, rows, cols, eps, pl, st);
+  if (rc != MGB_OK) return rc;
+  const unsigned fgrid = static_cast<unsigned>((2 * cols + kFinCols - 1) / kFinCols);
+  ln_bwd_finalize_kernel<T><<<fgrid, kFinCols * kFinLanes, 0, st>>>(part, pl.grid, cols, static_cast<T*>(dgamma),
+                                                                    static_cast<T*>(dbeta));
+  return check_launch("ln_bwd_finalize_kernel");
+}
+
+int check_ln(const char* who, int64_t rows, int64_t cols) {
+  MGB_REQUIRE(rows > 0 && cols > 0, MGB_EINVAL, "%s: rows=%lld cols=%lld must be positive", who, (long long)rows,
+              (long long)cols);
+  MGB_REQUIRE(cols <= 16384, MGB_EUNSUPPORTED, "%s: cols=%lld exceeds 16384", who, (long long)cols);
+  return MGB_OK;
+}
+
+}  // namespace
+}  // namespace mgb
+
+using namespace mgb;
+
+MGB_EXPORT int mograd_b200_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                                          float* rstd, int64_t rows, int64_t cols, float eps, int dtype,
+                                          void* stream) {
+  MGB_REQUIRE(x && gamma && beta && y, MGB_EINVAL, "layer_norm_fwd: NULL argument");
+  int rc = check_ln("layer_norm_fwd", rows, cols);
+  if (rc != MGB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MGB_BF16:
+      return ln_fwd<__nv_bfloat16>(x, gamma, beta, y, mean, rstd, rows, cols, eps, st);
+    case MGB_F32:
+      return ln_fwd<float>(x, gamma, beta, y, mean, rstd, rows, cols, eps, st);
+    default:
+      return fail(MGB_EDTYPE, "layer_norm_fwd: unsupported dtype code %d", dtype);
+  }
+}
+
+MGB_EXPORT size_t mograd_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t cols, int dtype) {
+  if (rows <= 0 || cols <= 0 || cols > 16384) return 0;
+  Plan pl;
+  const bool ok = dtype == MGB_BF16 ? make_plan<__nv_bfloat16>(rows, cols, pl) : make_plan<float>(rows, cols, pl);
+  if (!ok) return 0;
+  return round_up(static_cast<size_t>(pl.grid) * 2 * cols * sizeof(float), 256);
+}
+
+MGB_EXPORT int mograd_b200_layer_norm_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dgamma,
+                                          void* dbeta, int64_t rows, int64_t cols, float eps, int dtype,
+                                          void* workspace, size_t workspace_bytes, void* stream) {
+  MGB_REQUIRE(dy && x && gamma && dx && dgamma && dbeta, MGB_EINVAL, "layer_norm_bwd: NULL argument");
+  int rc = check_ln("layer_norm_bwd", rows, cols);
+  if (rc != MGB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MGB_BF16:
+      return ln_bwd<__nv_bfloat16>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes, st);
+    case MGB_F32:
+      return ln_bwd<float>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes, st);
+    default:
+      return fail(MGB_EDTYPE, "layer_norm_bwd: unsupported dtype code %d", dtype);
+  }
+}

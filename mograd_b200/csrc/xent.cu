@@ -1,0 +1,460 @@
+// Softmax cross-entropy: fused forward+backward with index labels, and the
+// reference-shaped dense-label forward / backward entry points.
+//
+// Bandwidth-bound design: one CTA owns one row.  Pass 1 streams the row from
+// HBM with 16-byte loads (four in flight per thread), keeps a copy in shared
+// memory and folds it into an online (max, sum-exp) pair; pass 2 re-reads the
+// row from shared memory and writes (softmax - label) * g with 16-byte
+// stores.  The logits therefore cross HBM exactly once in each direction and
+// the probabilities never exist in memory.  Rows too large for shared memory
+// are re-read through L2 instead.  Short rows (a few KB) use one warp per row.
+// Row losses go to a workspace and are summed by a single block in a fixed
+// order, so the loss is bitwise reproducible.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace mgb {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kRowThreads = 512;
+constexpr int kSmallThreads = 256;  // 8 warps, one row each
+constexpr int kSumThreads = 1024;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// (m, s): running maximum and sum of exp(x - m).
+__device__ __forceinline__ void ms_merge(float& m, float& s, float m2, float s2) {
+  const float nm = fmaxf(m, m2);
+  const float a = (m == -INFINITY) ? 0.f : s * ex2((m - nm) * kLog2e);
+  const float b = (m2 == -INFINITY) ? 0.f : s2 * ex2((m2 - nm) * kLog2e);
+  m = nm;
+  s = a + b;
+}
+
+template <typename T>
+struct XentParams {
+  const T* logits;
+  const T* dense;         // dense labels (N x C) or nullptr
+  const int64_t* index;   // class index per row or nullptr
+  T* dlogits;             // nullptr: forward only
+  float* row_loss;        // nullptr: backward only
+  const T* upstream_dev;  // one element, or nullptr -> upstream_host
+  float upstream_host;
+  int64_t N, C, ldx, ldl, lddx;
+  int staged;                    // row copy kept in shared memory
+  int vec_in, vec_lbl, vec_out;  // 16-byte access allowed for logits / labels / dlogits
+};
+
+template <int V>
+__device__ __forceinline__ void fold_vec(const float (&v)[V], float& m, float& s) {
+  float vm = v[0];
+#pragma unroll
+  for (int j = 1; j < V; ++j) vm = fmaxf(vm, v[j]);
+  if (vm > m) {
+    s *= ex2((m - vm) * kLog2e);  // first vector: m = -inf, s = 0 -> 0
+    m = vm;
+  }
+  if (m != -INFINITY) {
+    const float mb = m * kLog2e;
+#pragma unroll
+    for (int j = 0; j < V; ++j) s += ex2(fmaf(v[j], kLog2e, -mb));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void load_labels(const T* lbl, int64_t i, bool vec, float (&l)[Vec<T>::N]) {
+  constexpr int V = Vec<T>::N;
+  if (vec) {
+    load_vec(lbl + i * V, l);
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) l[j] = to_f32(lbl[i * V + j]);
+  }
+}
+
+template <typename T, bool DENSE>
+__global__ void __launch_bounds__(kRowThreads) xent_row_kernel(const XentParams<T> p) {
+  constexpr int V = Vec<T>::N;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* row_s = reinterpret_cast<T*>(smem_raw);
+  __shared__ float red[4][kRowThreads / 32];
+  __shared__ float bcast[4];
+
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const T* x = p.logits + row * p.ldx;
+  const T* lbl = DENSE ? p.dense + row * p.ldl : nullptr;
+  const int64_t nvec = p.vec_in ? p.C / V : 0;
+
+  float m = -INFINITY, s = 0.f, slx = 0.f, sl = 0.f;
+
+  // ---- pass 1: HBM -> registers (-> shared), online max / sum-exp
+  for (int64_t i0 = 0; i0 < nvec; i0 += 4 * kRowThreads) {
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t i = i0 + u * kRowThreads + tid;
+      if (i < nvec) raw[u] = __ldcs(reinterpret_cast<const uint4*>(x) + i);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t i = i0 + u * kRowThreads + tid;
+      if (i < nvec) {
+        if (p.staged) reinterpret_cast<uint4*>(row_s)[i] = raw[u];
+        float v[V];
+        load_vec(reinterpret_cast<const T*>(&raw[u]), v);
+        fold_vec<V>(v, m, s);
+        if (DENSE) {
+          float l[V];
+          load_labels<T>(lbl, i, p.vec_lbl, l);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            slx = fmaf(l[j], v[j], slx);
+            sl += l[j];
+          }
+        }
+      }
+    }
+  }
+  for (int64_t c = nvec * V + tid; c < p.C; c += kRowThreads) {  // scalar tail / unaligned rows
+    const T raw = x[c];
+    if (p.staged) row_s[c] = raw;
+    const float v = to_f32(raw);
+    ms_merge(m, s, v, 1.f);
+    if (DENSE) {
+      const float l = to_f32(lbl[c]);
+      slx = fmaf(l, v, slx);
+      sl += l;
+    }
+  }
+
+  // ---- block reduction of (m, s) and the label sums
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    ms_merge(m, s, m2, s2);
+  }
+  if (DENSE) {
+    slx = warp_sum(slx);
+    sl = warp_sum(sl);
+  }
+  const int warp = tid >> 5, lane = tid & 31;
+  if (lane == 0) {
+    red[0][warp] = m;
+    red[1][warp] = s;
+    red[2][warp] = slx;
+    red[3][warp] = sl;
+  }
+  __syncthreads();  // also publishes row_s
+  if (warp == 0) {
+    constexpr int W = kRowThreads / 32;
+    float mm = lane < W ? red[0][lane] : -INFINITY;
+    float ss = lane < W ? red[1][lane] : 0.f;
+    float a = lane < W ? red[2][lane] : 0.f;
+    float b = lane < W ? red[3][lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, mm, o);
+      const float s2 = __shfl_xor_sync(0xffffffffu, ss, o);
+      ms_merge(mm, ss, m2, s2);
+    }
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) {
+      bcast[0] = mm;
+      bcast[1] = ss;
+      bcast[2] = a;
+      bcast[3] = b;
+    }
+  }
+  __syncthreads();
+  m = bcast[0];
+  s = bcast[1];
+
+  int64_t t = -1;
+  if (!DENSE) t = p.index[row];
+  if (tid == 0 && p.row_loss) {
+    const float lse = m + logf(s);
+    float l;
+    if (DENSE) {
+      l = -(bcast[2] - lse * bcast[3]);
+    } else {
+      const float xt = (t >= 0 && t < p.C) ? to_f32(p.staged ? row_s[t] : x[t]) : lse;
+      l = -(xt - lse);
+    }
+    p.row_loss[row] = l / static_cast<float>(p.N);
+  }
+  if (!p.dlogits) return;
+
+  // ---- pass 2: shared (or L2) -> (softmax - label) * g -> HBM
+  const float up = p.upstream_dev ? to_f32(p.upstream_dev[0]) : p.upstream_host;
+  const float g = up / static_cast<float>(p.N);
+  const float inv_s = 1.f / s;
+  const float mb = m * kLog2e;
+  T* out = p.dlogits + row * p.lddx;
+  const T* src = p.staged ? row_s : x;
+  const int64_t nvec2 = (p.vec_out && (p.staged || p.vec_in)) ? p.C / V : 0;
+  for (int64_t i = tid; i < nvec2; i += kRowThreads) {
+    float v[V], o[V];
+    load_vec(src + i * V, v);
+    if (DENSE) {
+      float l[V];
+      load_labels<T>(lbl, i, p.vec_lbl, l);
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = (ex2(fmaf(v[j], kLog2e, -mb)) * inv_s - l[j]) * g;
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float onehot = (i * V + j == t) ? 1.f : 0.f;
+        o[j] = (ex2(fmaf(v[j], kLog2e, -mb)) * inv_s - onehot) * g;
+      }
+    }
+    store_vec(out + i * V, o);
+  }
+  for (int64_t c = nvec2 * V + tid; c < p.C; c += kRowThreads) {
+    const float v = to_f32(src[c]);
+    const float l = DENSE ? to_f32(lbl[c]) : (c == t ? 1.f : 0.f);
+    out[c] = from_f32<T>((ex2(fmaf(v, kLog2e, -mb)) * inv_s - l) * g);
+  }
+}
+
+// One warp per row for short rows; the row is re-read from L1/L2 in pass 2.
+template <typename T, bool DENSE>
+__global__ void __launch_bounds__(kSmallThreads) xent_small_kernel(const XentParams<T> p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kSmallThreads / 32) + (threadIdx.x >> 5);
+  if (row >= p.N) return;
+  const T* x = p.logits + row * p.ldx;
+  const T* lbl = DENSE ? p.dense + row * p.ldl : nullptr;
+  float m = -INFINITY, s = 0.f, slx = 0.f, sl = 0.f;
+  for (int64_t c = lane; c < p.C; c += 32) {
+    const float v = to_f32(x[c]);
+    ms_merge(m, s, v, 1.f);
+    if (DENSE) {
+      const float l = to_f32(lbl[c]);
+      slx = fmaf(l, v, slx);
+      sl += l;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    ms_merge(m, s, m2, s2);
+  }
+  if (DENSE) {
+    slx = warp_sum(slx);
+    sl = warp_sum(sl);
+  }
+  int64_t t = -1;
+  if (!DENSE) t = p.index[row];
+  if (lane == 0 && p.row_loss) {
+    const float lse = m + logf(s);
+    float l;
+    if (DENSE) {
+      l = -(slx - lse * sl);
+    } else {
+      const float xt = (t >= 0 && t < p.C) ? to_f32(x[t]) : lse;
+      l = -(xt - lse);
+    }
+    p.row_loss[row] = l / static_cast<float>(p.N);
+  }
+  if (!p.dlogits) return;
+  const float up = p.upstream_dev ? to_f32(p.upstream_dev[0]) : p.upstream_host;
+  const float g = up / static_cast<float>(p.N);
+  const float inv_s = 1.f / s;
+  const float mb = m * kLog2e;
+  T* out = p.dlogits + row * p.lddx;
+  for (int64_t c = lane; c < p.C; c += 32) {
+    const float v = to_f32(x[c]);
+    const float l = DENSE ? to_f32(lbl[c]) : (c == t ? 1.f : 0.f);
+    out[c] = from_f32<T>((ex2(fmaf(v, kLog2e, -mb)) * inv_s - l) * g);
+  }
+}
+
+// Fixed-order sum of the per-row losses (already divided by N).
+template <typename TOut>
+__global__ void __launch_bounds__(kSumThreads) xent_sum_rows_kernel(const float* row_loss, int64_t N, TOut* loss) {
+  __shared__ float red[kSumThreads / 32];
+  float acc = 0.f;
+  for (int64_t i = threadIdx.x; i < N; i += kSumThreads) acc += row_loss[i];
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < kSumThreads / 32 ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) loss[0] = from_f32<TOut>(v);
+  }
+}
+
+template <typename T, bool DENSE>
+int launch_xent(XentParams<T> p, cudaStream_t st) {
+  constexpr int V = Vec<T>::N;
+  p.vec_in = aligned16(p.logits) && (p.ldx % V == 0);
+  p.vec_lbl = DENSE && aligned16(p.dense) && (p.ldl % V == 0);
+  p.vec_out = p.dlogits && aligned16(p.dlogits) && (p.lddx % V == 0);
+  const size_t row_bytes = static_cast<size_t>(p.C) * sizeof(T);
+  if (row_bytes <= 4096) {
+    p.staged = 0;
+    const int rows_per_block = kSmallThreads / 32;
+    const unsigned grid = static_cast<unsigned>((p.N + rows_per_block - 1) / rows_per_block);
+    xent_small_kernel<T, DENSE><<<grid, kSmallThreads, 0, st>>>(p);
+    return check_launch("xent_small_kernel");
+  }
+  const size_t smem_cap = static_cast<size_t>(max_smem_optin()) - 1024;  // static reductions live there too
+  const size_t smem = round_up(row_bytes, 16);
+  p.staged = smem <= smem_cap;
+  const size_t dyn = p.staged ? smem : 0;
+  auto kern = xent_row_kernel<T, DENSE>;
+  if (dyn > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dyn));
+    if (e != cudaSuccess) return fail(MGB_ECUDA, "xent smem opt-in (%zu B): %s", dyn, cudaGetErrorString(e));
+  }
+  kern<<<static_cast<unsigned>(p.N), kRowThreads, dyn, st>>>(p);
+  return check_launch("xent_row_kernel");
+}
+
+template <typename T>
+int xent_index(const void* logits, const int64_t* labels, float* loss, void* dlogits, int64_t N, int64_t C,
+               int64_t ldx, int64_t lddx, float upstream, void* ws, cudaStream_t st) {
+  XentParams<T> p{};
+  p.logits = static_cast<const T*>(logits);
+  p.index = labels;
+  p.dlogits = static_cast<T*>(dlogits);
+  p.row_loss = loss ? static_cast<float*>(ws) : nullptr;
+  p.upstream_host = upstream;
+  p.N = N;
+  p.C = C;
+  p.ldx = ldx;
+  p.lddx = lddx;
+  int rc = launch_xent<T, false>(p, st);
+  if (rc != MGB_OK) return rc;
+  if (loss) {
+    xent_sum_rows_kernel<float><<<1, kSumThreads, 0, st>>>(p.row_loss, N, loss);
+    rc = check_launch("xent_sum_rows_kernel");
+  }
+  return rc;
+}
+
+template <typename T>
+int xent_dense_fwd(const void* logits, const void* labels, void* loss, int64_t N, int64_t C, int64_t ldx,
+                   int64_t ldl, void* ws, cudaStream_t st) {
+  XentParams<T> p{};
+  p.logits = static_cast<const T*>(logits);
+  p.dense = static_cast<const T*>(labels);
+  p.row_loss = static_cast<float*>(ws);
+  p.N = N;
+  p.C = C;
+  p.ldx = ldx;
+  p.ldl = ldl;
+  int rc = launch_xent<T, true>(p, st);
+  if (rc != MGB_OK) return rc;
+  xent_sum_rows_kernel<T><<<1, kSumThreads, 0, st>>>(p.row_loss, N, static_cast<T*>(loss));
+  return check_launch("xent_sum_rows_kernel");
+}
+
+template <typename T>
+int xent_dense_bwd(const void* upstream, const void* logits, const void* labels, void* dst, int64_t N, int64_t C,
+                   int64_t ldx, int64_t ldl, int64_t lddst, cudaStream_t st) {
+  XentParams<T> p{};
+  p.logits = static_cast<const T*>(logits);
+  p.dense = static_cast<const T*>(labels);
+  p.dlogits = static_cast<T*>(dst);
+  p.upstream_dev = static_cast<const T*>(upstream);
+  p.N = N;
+  p.C = C;
+  p.ldx = ldx;
+  p.ldl = ldl;
+  p.lddx = lddst;
+  return launch_xent<T, true>(p, st);
+}
+
+int check_shape(int64_t N, int64_t C, int64_t ldx) {
+  MGB_REQUIRE(N > 0 && C > 0, MGB_EINVAL, "cross_entropy: N=%lld C=%lld must be positive", (long long)N, (long long)C);
+  MGB_REQUIRE(N <= 0x7fffffffLL, MGB_EUNSUPPORTED, "cross_entropy: N=%lld exceeds the grid limit", (long long)N);
+  MGB_REQUIRE(ldx >= C, MGB_EINVAL, "cross_entropy: row stride %lld < C=%lld", (long long)ldx, (long long)C);
+  return MGB_OK;
+}
+
+}  // namespace
+}  // namespace mgb
+
+using namespace mgb;
+
+MGB_EXPORT size_t mograd_b200_softmax_xent_workspace_bytes(int64_t N, int64_t, int) {
+  return N > 0 ? round_up(static_cast<size_t>(N) * sizeof(float), 256) : 0;
+}
+MGB_EXPORT size_t mograd_b200_cross_entropy_workspace_bytes(int64_t N, int64_t C, int dtype) {
+  return mograd_b200_softmax_xent_workspace_bytes(N, C, dtype);
+}
+
+MGB_EXPORT int mograd_b200_softmax_xent_fwd_bwd(const void* logits, const int64_t* labels, float* loss,
+                                                void* dlogits, int64_t N, int64_t C, int64_t ldx, int64_t lddx,
+                                                float upstream, int dtype, void* workspace,
+                                                size_t workspace_bytes, void* stream) {
+  MGB_REQUIRE(logits && labels, MGB_EINVAL, "softmax_xent_fwd_bwd: logits / labels is NULL");
+  MGB_REQUIRE(loss || dlogits, MGB_EINVAL, "softmax_xent_fwd_bwd: both outputs are NULL");
+  int rc = check_shape(N, C, ldx);
+  if (rc != MGB_OK) return rc;
+  MGB_REQUIRE(!dlogits || lddx >= C, MGB_EINVAL, "softmax_xent_fwd_bwd: lddx %lld < C", (long long)lddx);
+  if (loss)
+    MGB_REQUIRE(workspace && workspace_bytes >= mograd_b200_softmax_xent_workspace_bytes(N, C, dtype),
+                MGB_EWORKSPACE, "softmax_xent_fwd_bwd: workspace of %zu bytes needed, %zu given",
+                mograd_b200_softmax_xent_workspace_bytes(N, C, dtype), workspace ? workspace_bytes : (size_t)0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MGB_BF16:
+      return xent_index<__nv_bfloat16>(logits, labels, loss, dlogits, N, C, ldx, lddx, upstream, workspace, st);
+    case MGB_F32:
+      return xent_index<float>(logits, labels, loss, dlogits, N, C, ldx, lddx, upstream, workspace, st);
+    default:
+      return fail(MGB_EDTYPE, "softmax_xent_fwd_bwd: unsupported dtype code %d", dtype);
+  }
+}
+
+MGB_EXPORT int mograd_b200_cross_entropy(const void* logits, const void* labels, void* loss, int64_t N, int64_t C,
+                                         int64_t ldx, int64_t ldl, int dtype, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  MGB_REQUIRE(logits && labels && loss, MGB_EINVAL, "cross_entropy: NULL argument");
+  int rc = check_shape(N, C, ldx);
+  if (rc != MGB_OK) return rc;
+  MGB_REQUIRE(ldl >= C, MGB_EINVAL, "cross_entropy: label row stride %lld < C", (long long)ldl);
+  MGB_REQUIRE(workspace && workspace_bytes >= mograd_b200_cross_entropy_workspace_bytes(N, C, dtype),
+              MGB_EWORKSPACE, "cross_entropy: workspace of %zu bytes needed, %zu given",
+              mograd_b200_cross_entropy_workspace_bytes(N, C, dtype), workspace ? workspace_bytes : (size_t)0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MGB_BF16:
+      return xent_dense_fwd<__nv_bfloat16>(logits, labels, loss, N, C, ldx, ldl, workspace, st);
+    case MGB_F32:
+      return xent_dense_fwd<float>(logits, labels, loss, N, C, ldx, ldl, workspace, st);
+    default:
+      return fail(MGB_EDTYPE, "cross_entropy: unsupported dtype code %d", dtype);
+  }
+}
+
+MGB_EXPORT int mograd_b200_cross_entropy_grad(const void* upstream, const void* logits, const void* labels,
+                                              void* dst, int64_t N, int64_t C, int64_t ldx, int64_t ldl,
+                                              int64_t lddst, int dtype, void* stream) {
+  MGB_REQUIRE(upstream && logits && labels && dst, MGB_EINVAL, "cross_entropy_grad: NULL argument");
+  int rc = check_shape(N, C, ldx);
+  if (rc != MGB_OK) return rc;
+  MGB_REQUIRE(ldl >= C && lddst >= C, MGB_EINVAL, "cross_entropy_grad: row stride < C");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MGB_BF16:
+      return xent_dense_bwd<__nv_bfloat16>(upstream, logits, labels, dst, N, C, ldx, ldl, lddst, st);
+    case MGB_F32:
+      return xent_dense_bwd<float>(upstream, logits, labels, dst, N, C, ldx, ldl, lddst, st);
+    default:
+      return fail(MGB_EDTYPE, "cross_entropy_grad: unsupported dtype code %d", dtype);
+  }
+}

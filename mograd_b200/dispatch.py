@@ -1,0 +1,233 @@
+"""Host-side mirror of mograd's kernel dispatch for the training hot path.
+
+Each function here plays the part of one exec rule / dispatch helper of the
+reference (mograd/runtime/gpu/kernels/dispatch.mojo): it reads the shapes,
+allocates the outputs (torch.empty stands in for AnyBuffer.create and the
+caching pool of mograd/memory.mojo), takes kernel scratch from a per-stream
+workspace (scratch_take, memory.mojo:340-345), and calls the C ABI with raw
+device pointers and the current CUDA stream.  Tensors are torch CUDA tensors
+used purely as device buffers; no arithmetic happens in PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import KernelError, call, query
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+_workspaces: dict = {}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    """Erase a tensor dtype into the ABI's dtype code (dispatch.mojo:564-576)."""
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError("dispatch_dtype", _lib.EDTYPE, f"unsupported dtype {t.dtype}") from None
+
+
+def _ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("dispatch", _lib.EINVAL, "mograd_b200 kernels take device buffers; got a host tensor")
+
+
+def scratch_take(nbytes: int, device) -> torch.Tensor:
+    """Per-(device, stream) scratch buffer, reused across calls in stream order."""
+    key = (torch.device(device).index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _rows2d(t: torch.Tensor) -> tuple[int, int, int]:
+    """(rows, cols, row stride) of a tensor whose leading dims collapse into rows."""
+    cols = t.shape[-1]
+    rows = t.numel() // cols
+    if t.stride(-1) != 1:
+        raise KernelError("dispatch", _lib.EINVAL, "last axis must be contiguous")
+    if t.dim() == 1:
+        return 1, cols, cols
+    ld = t.stride(-2)
+    expect = ld
+    for d in range(t.dim() - 2, -1, -1):
+        if t.shape[d] != 1 and t.stride(d) != expect:
+            raise KernelError("dispatch", _lib.EINVAL, "batch dims are not collapsible")
+        expect = t.stride(d) * t.shape[d]
+    return rows, cols, ld
+
+
+# ----------------------------------------------------------------------------
+# matmul_bias_bt (dispatch.mojo:247-278)
+# ----------------------------------------------------------------------------
+def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None):
+    """Y = A @ W.T (+ bias) (, ReLU): exec rule `matmul_bias_bt` / `matmul_bt`."""
+    _require_cuda(a, w, bias)
+    M, K, lda = _rows2d(a)
+    N, K2, ldw = _rows2d(w)
+    if K2 != K:
+        raise KernelError("matmul_bias_bt", _lib.EINVAL, f"inner dims differ: {K} vs {K2}")
+    if out is None:
+        out = torch.empty(a.shape[:-1] + (N,), dtype=a.dtype, device=a.device)
+    _, _, ldy = _rows2d(out)
+    call("mograd_b200_matmul_bias_bt", _ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, lda, ldw, ldy, int(act),
+         dtype_code(a), _stream())
+    return out
+
+
+def matmul_bias_bt_bwd(dy, x, w, need_dx=True, need_dw=True, need_db=True, dx_out=None, dw_out=None, db_out=None):
+    """(dX, dW, db) of Y = X @ W.T + b in one call; outputs not needed are None."""
+    _require_cuda(dy, x, w)
+    M, N, lddy = _rows2d(dy)
+    M2, K, ldx = _rows2d(x)
+    N2, K2, ldw = _rows2d(w)
+    if M2 != M or N2 != N or K2 != K:
+        raise KernelError("matmul_bias_bt_bwd", _lib.EINVAL, "shape mismatch between dY, X and W")
+    dx = dx_out if dx_out is not None else (torch.empty_like(x) if need_dx else None)
+    dw = dw_out if dw_out is not None else (torch.empty((N, K), dtype=w.dtype, device=w.device) if need_dw else None)
+    db = db_out if db_out is not None else (torch.empty((N,), dtype=w.dtype, device=w.device) if need_db else None)
+    code = dtype_code(dy)
+    nbytes = query("mograd_b200_matmul_bias_bt_bwd_workspace_bytes", M, N, K, code)
+    ws = scratch_take(nbytes, dy.device)
+    lddx = _rows2d(dx)[2] if dx is not None else K
+    lddw = dw.stride(0) if dw is not None else K
+    call("mograd_b200_matmul_bias_bt_bwd", _ptr(dy), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), M, N, K, lddy,
+         ldx, ldw, lddx, lddw, code, _ptr(ws), ws.numel(), _stream())
+    return dx, dw, db
+
+
+# ----------------------------------------------------------------------------
+# LayerNorm (dispatch.mojo:281-358)
+# ----------------------------------------------------------------------------
+def layer_norm_fwd_dispatch(x, gamma, beta, eps: float = 1e-5, save_stats: bool = False):
+    _require_cuda(x, gamma, beta)
+    x = x if x.is_contiguous() else x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    out = torch.empty_like(x)
+    mean = rstd = None
+    if save_stats:
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    call("mograd_b200_layer_norm_fwd", _ptr(x), _ptr(gamma), _ptr(beta), _ptr(out), _ptr(mean), _ptr(rstd), rows,
+         cols, float(eps), dtype_code(x), _stream())
+    return (out, mean, rstd) if save_stats else out
+
+
+def layer_norm_bwd_dispatch(dy, x, gamma, eps: float = 1e-5):
+    """inputs [dy, x, gamma] -> [dx, dgamma, dbeta] (dispatch.mojo:332-358)."""
+    _require_cuda(dy, x, gamma)
+    x = x if x.is_contiguous() else x.contiguous()
+    dy = dy if dy.is_contiguous() else dy.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    dx = torch.empty_like(x)
+    dgamma = torch.empty_like(gamma)
+    dbeta = torch.empty_like(gamma)
+    code = dtype_code(x)
+    nbytes = query("mograd_b200_layer_norm_bwd_workspace_bytes", rows, cols, code)
+    ws = scratch_take(nbytes, x.device)
+    call("mograd_b200_layer_norm_bwd", _ptr(dy), _ptr(x), _ptr(gamma), _ptr(dx), _ptr(dgamma), _ptr(dbeta), rows,
+         cols, float(eps), code, _ptr(ws), ws.numel(), _stream())
+    return [dx, dgamma, dbeta]
+
+
+# ----------------------------------------------------------------------------
+# Cross-entropy (runtime/__init__.mojo:530-533, 563-580)
+# ----------------------------------------------------------------------------
+def cross_entropy(logits, labels):
+    """Mean cross-entropy with dense float labels -> one-element tensor of the logits' dtype."""
+    _require_cuda(logits, labels)
+    N, C, ldx = _rows2d(logits)
+    N2, C2, ldl = _rows2d(labels)
+    if (N2, C2) != (N, C) or labels.dtype != logits.dtype:
+        raise KernelError("cross_entropy", _lib.EINVAL, "labels must have the logits' shape and dtype")
+    loss = torch.empty(1, dtype=logits.dtype, device=logits.device)
+    code = dtype_code(logits)
+    ws = scratch_take(query("mograd_b200_cross_entropy_workspace_bytes", N, C, code), logits.device)
+    call("mograd_b200_cross_entropy", _ptr(logits), _ptr(labels), _ptr(loss), N, C, ldx, ldl, code, _ptr(ws),
+         ws.numel(), _stream())
+    return loss
+
+
+def cross_entropy_grad(upstream, logits, labels):
+    """(softmax(logits) - labels) * upstream / N."""
+    _require_cuda(upstream, logits, labels)
+    N, C, ldx = _rows2d(logits)
+    _, _, ldl = _rows2d(labels)
+    dst = torch.empty((N, C), dtype=logits.dtype, device=logits.device)
+    call("mograd_b200_cross_entropy_grad", _ptr(upstream), _ptr(logits), _ptr(labels), _ptr(dst), N, C, ldx, ldl, C,
+         dtype_code(logits), _stream())
+    return dst.view(logits.shape)
+
+
+def softmax_xent_fwd_bwd(logits, index, upstream: float = 1.0, want_loss=True, want_grad=True, inplace=False):
+    """Fused loss + dlogits for one class index per row. Returns (loss fp32 scalar tensor, dlogits)."""
+    _require_cuda(logits, index)
+    if index.dtype != torch.int64:
+        raise KernelError("softmax_xent_fwd_bwd", _lib.EDTYPE, "class indices must be int64")
+    N, C, ldx = _rows2d(logits)
+    loss = torch.empty((), dtype=torch.float32, device=logits.device) if want_loss else None
+    dl = None
+    lddx = ldx
+    if want_grad:
+        dl = logits if inplace else torch.empty_like(logits)
+        lddx = _rows2d(dl)[2]
+    code = dtype_code(logits)
+    ws = scratch_take(query("mograd_b200_softmax_xent_workspace_bytes", N, C, code), logits.device)
+    call("mograd_b200_softmax_xent_fwd_bwd", _ptr(logits), _ptr(index), _ptr(loss), _ptr(dl), N, C, ldx, lddx,
+         float(upstream), code, _ptr(ws), ws.numel(), _stream())
+    return loss, dl
+
+
+# ----------------------------------------------------------------------------
+# Attention (dispatch.mojo:380-481)
+# ----------------------------------------------------------------------------
+def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_bias=None):
+    """srcs [Q, K, V, mask] all BSHD -> [O (BHSD), LSE (B,H,S) float32]."""
+    _require_cuda(q, k, v, mask)
+    B, S, H, D = q.shape
+    if has_bias is None:
+        has_bias = mask is not None and not is_causal
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
+    dst = torch.empty((B, H, S, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    call("mograd_b200_flash_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(dst), _ptr(lse), B, S, H, D,
+         float(scale), int(bool(is_causal)), int(bool(has_bias)), dtype_code(q), _stream())
+    return [dst, lse]
+
+
+def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=True, has_bias=None):
+    """srcs [dO, O, Q, K, V, mask, LSE] -> [dQ, dK, dV] (BSHD)."""
+    _require_cuda(dy, o, q, k, v, mask, lse)
+    B, S, H, D = q.shape
+    if has_bias is None:
+        has_bias = mask is not None and not is_causal
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    dy = dy if dy.is_contiguous() else dy.contiguous()  # the rule makes dO contiguous (grad.mojo:336-339)
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(q)
+    dv = torch.empty_like(q)
+    code = dtype_code(q)
+    ws = scratch_take(query("mograd_b200_flash_attn_bwd_workspace_bytes", B, S, H, D, code), q.device)
+    call("mograd_b200_flash_attn_bwd", _ptr(dy), _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(lse), _ptr(dq),
+         _ptr(dk), _ptr(dv), B, S, H, D, float(scale), int(bool(is_causal)), int(bool(has_bias)), code, _ptr(ws),
+         ws.numel(), _stream())
+    return [dq, dk, dv]
