@@ -1,0 +1,125 @@
+"""matmul_bias_bt forward and backward (tcgen05 path and CUDA-core path) vs the CPU oracle."""
+import numpy as np
+import pytest
+
+from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err
+
+pytestmark = pytest.mark.gpu
+
+# (M, N, K): aligned shapes run on tensor cores; N=10 / 65 and K=100 exercise ragged tiles and the fallback
+SHAPES = [(128, 256, 64), (128, 128, 128), (256, 512, 256), (100, 72, 136), (384, 384, 784), (130, 10, 256),
+          (257, 65, 384), (64, 1000, 100), (512, 768, 768), (1024, 3072, 768), (3, 8, 8)]
+
+
+def _mk(M, N, K, dt, seed):
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    dy = rng.standard_normal((M, N)).astype(np.float32)
+    if dt == "bf16":
+        a, w, b, dy = (bf16_round(t) for t in (a, w, b, dy))
+    return a, w, b, dy
+
+
+def _dev(t, cuda, dt):
+    import torch
+
+    return torch.from_numpy(t).to(cuda).to(torch.float32 if dt == "f32" else torch.bfloat16)
+
+
+def _status():
+    import ctypes
+    from mograd_b200 import _lib
+
+    code, detail = ctypes.c_int(0), ctypes.c_int(0)
+    assert _lib.load().mograd_b200_device_status(ctypes.byref(code), ctypes.byref(detail)) == 0
+    return code.value
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_forward(cuda, oracle, M, N, K, dt):
+    from mograd_b200 import dispatch as Kx
+
+    a, w, b, _ = _mk(M, N, K, dt, M + N + K)
+    want = oracle.matmul_bias_bt(a, w, b)
+    y = Kx.matmul_bias_strided(_dev(a, cuda, dt), _dev(w, cuda, dt), _dev(b, cuda, dt))
+    assert _status() == 0
+    assert rel_err(y.float().cpu().numpy(), want) <= (TOL_F32 if dt == "f32" else TOL_BF16)
+    # no bias + fused ReLU
+    y2 = Kx.matmul_bias_strided(_dev(a, cuda, dt), _dev(w, cuda, dt), None, act=1)
+    want2 = np.maximum(oracle.matmul_bias_bt(a, w), 0)
+    assert rel_err(y2.float().cpu().numpy(), want2) <= (TOL_F32 if dt == "f32" else TOL_BF16)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_backward(cuda, oracle, M, N, K, dt):
+    from mograd_b200 import dispatch as Kx
+
+    x, w, _, dy = _mk(M, N, K, dt, 3 * M + N + K)
+    wdx, wdw, wdb = oracle.matmul_bias_bt_bwd(dy, x, w)
+    dx, dw, db = Kx.matmul_bias_bt_bwd(_dev(dy, cuda, dt), _dev(x, cuda, dt), _dev(w, cuda, dt))
+    assert _status() == 0
+    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    assert rel_err(dx.float().cpu().numpy(), wdx) <= tol
+    assert rel_err(dw.float().cpu().numpy(), wdw) <= tol
+    assert rel_err(db.float().cpu().numpy(), wdb) <= tol
+
+
+def test_identity_and_known_values(cuda):
+    """tests/test_ops.mojo:27-94 style identity / known-value products."""
+    import torch
+    from mograd_b200 import dispatch as Kx
+
+    a = torch.arange(12, dtype=torch.float32, device=cuda).reshape(3, 4)
+    y = Kx.matmul_bias_strided(a, torch.eye(4, device=cuda))
+    assert torch.equal(y, a)
+    y = Kx.matmul_bias_strided(torch.tensor([[1.0, 2], [3, 4]], device=cuda), torch.tensor([[5.0, 6], [7, 8]], device=cuda))
+    assert torch.equal(y.cpu(), torch.tensor([[17.0, 23], [39, 53]]))
+    ab = torch.eye(256, device=cuda).bfloat16()
+    xb = torch.randn((128, 256), device=cuda).bfloat16()
+    assert torch.equal(Kx.matmul_bias_strided(xb, ab), xb)  # X @ I^T on the tensor-core path is exact
+
+
+def test_split_contraction_dw(cuda, oracle):
+    """dW of a tall batch (contraction 8192) takes the split-contraction path; deterministic."""
+    import torch
+    from mograd_b200 import dispatch as Kx
+
+    x, w, _, dy = _mk(8192, 256, 384, "bf16", 5)
+    _, wdw, wdb = oracle.matmul_bias_bt_bwd(dy, x, w)
+    args = (_dev(dy, cuda, "bf16"), _dev(x, cuda, "bf16"), _dev(w, cuda, "bf16"))
+    _, dw1, db1 = Kx.matmul_bias_bt_bwd(*args, need_dx=False)
+    _, dw2, _ = Kx.matmul_bias_bt_bwd(*args, need_dx=False)
+    assert _status() == 0
+    assert rel_err(dw1.float().cpu().numpy(), wdw) <= TOL_BF16
+    assert rel_err(db1.float().cpu().numpy(), wdb) <= TOL_BF16
+    assert torch.equal(dw1, dw2)
+
+
+def test_batch_dims_collapse(cuda, oracle):
+    import torch
+    from mograd_b200 import dispatch as Kx
+
+    a, w, b, _ = _mk(6 * 64, 128, 64, "bf16", 8)
+    y = Kx.matmul_bias_strided(_dev(a, cuda, "bf16").view(6, 64, 64), _dev(w, cuda, "bf16"), _dev(b, cuda, "bf16"))
+    assert y.shape == (6, 64, 128)
+    assert rel_err(y.float().cpu().numpy().reshape(-1, 128), oracle.matmul_bias_bt(a, w, b)) <= TOL_BF16
+
+
+def test_large_linearity(cuda):
+    """Full-size product (16384 x 768 x 3072): linear in A, checked without a CPU GEMM."""
+    import torch
+    from mograd_b200 import dispatch as Kx
+
+    g = torch.Generator(device=cuda).manual_seed(2)
+    a1 = torch.randn((16384, 768), generator=g, device=cuda).bfloat16()
+    w = (torch.randn((3072, 768), generator=g, device=cuda) / 28).bfloat16()
+    y1 = Kx.matmul_bias_strided(a1, w).float()
+    y2 = Kx.matmul_bias_strided((a1.float() * 2).bfloat16(), w).float()  # exact doubling in bf16
+    assert _status() == 0
+    assert torch.equal(y2, y1 * 2)
+    ref = (a1[:256].float() @ w.float().T)
+    assert rel_err(y1[:256].cpu().numpy(), ref.cpu().numpy()) <= TOL_BF16
