@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the mograd training hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A "step" is one full train step (forward, backward, gradient exchange when
+N > 1, AdamW) on one batch of seeded synthetic data.  One JSON line is printed
+by rank 0:
+
+  value        whole-job tokens/s with the batch already resident in HBM,
+               timed with CUDA events over exactly K steps, max over ranks
+  e2e          the same metric through the host-facing call Model.step(): the
+               batch comes from pinned host memory every step and the loss is
+               read back to the host every step
+  roofline     the dominant kernel of the step, timed live here with CUDA
+               events on the launching stream
+  kernels      the standalone kernels the metric names (flash-attention
+               backward, LayerNorm backward, fused cross-entropy), N = 1 only
+  cpu_baseline the CPU restatement of the reference's math (oracle/) timed on
+               this box's host cores on a bounded sample, N = 1 only
+
+`--impl reference` times only that CPU restatement (the reference itself is
+Mojo on Modular MAX and cannot be built or run on this box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE config 2: README MLP
+    "readme_mlp": dict(kind="mlp", dims=[4096, 4096, 4096, 10], batch=2048, tokens_per_step=2048,
+                       desc="README MLP 4096-4096(ReLU)-LN-4096(ReLU)-10, batch 2048, bf16 (1 sample = 1 token)"),
+    # BASELINE config 3: char-level transformer
+    "char_transformer": dict(kind="tf", vocab=65, d_model=384, d_ff=1536, n_layers=6, n_heads=6, batch=64, seq=256,
+                             tokens_per_step=64 * 256,
+                             desc="char transformer vocab 65 ctx 256 L6 H6 d384, batch 64, bf16"),
+    # BASELINE config 5: GPT-2-small-shaped decoder
+    "gpt2_small": dict(kind="tf", vocab=50304, d_model=768, d_ff=3072, n_layers=12, n_heads=12, batch=16, seq=1024,
+                       tokens_per_step=16 * 1024,
+                       desc="GPT-2-small-shaped decoder L12 H12 d768 ctx 1024 vocab 50304, per-GPU batch 16, bf16"),
+}
+DEFAULT_WORKLOAD = "readme_mlp"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d["bf16_tflops"], tflops_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                clocks.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=statistics.median(clocks) if clocks else None, sm_max_mhz=mx, reasons=sorted(reasons),
+                    samples=len(clocks))
+
+
+# ----------------------------------------------------------------------------- model + data
+def build_model(cfg, device, world, pg, seed):
+    import torch
+    from mograd_b200.train import MLP, TinyTransformer
+
+    if cfg["kind"] == "mlp":
+        return MLP(cfg["dims"], cfg["batch"], dtype=torch.bfloat16, device=device, seed=seed, world_size=world,
+                   process_group=pg)
+    return TinyTransformer(cfg["vocab"], cfg["d_model"], cfg["d_ff"], cfg["n_layers"], cfg["n_heads"], cfg["batch"],
+                           cfg["seq"], dtype=torch.bfloat16, device=device, seed=seed, world_size=world,
+                           process_group=pg)
+
+
+def make_batch(cfg, seed, pinned=True):
+    """Seeded synthetic batch with the config's shapes and distributions, on the host."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    if cfg["kind"] == "mlp":
+        x = torch.randn((cfg["batch"], cfg["dims"][0]), generator=g).to(torch.bfloat16)
+        y = torch.randint(0, cfg["dims"][-1], (cfg["batch"],), generator=g, dtype=torch.int64)
+    else:
+        x = torch.randint(0, cfg["vocab"], (cfg["batch"], cfg["seq"]), generator=g, dtype=torch.int64)
+        y = torch.randint(0, cfg["vocab"], (cfg["batch"], cfg["seq"]), generator=g, dtype=torch.int64)
+    if pinned:
+        x, y = x.pin_memory(), y.pin_memory()
+    return x, y
+
+
+# ----------------------------------------------------------------------------- kernel micro-benchmarks
+def time_launches(fn, reps, flush=None):
+    """Average device time of fn() in ms, CUDA events on the current stream, L2 flushed before each launch."""
+    import torch
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(reps):
+        if flush is not None:
+            flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / reps
+
+
+def dominant_gemm_roofline(cfg, peaks, device):
+    """Times the step's largest matmul_bias_bt launch; returns the roofline object."""
+    import torch
+    from mograd_b200 import dispatch as K
+
+    if cfg["kind"] == "mlp":
+        M, N, Kd = cfg["batch"], cfg["dims"][1], cfg["dims"][0]
+    else:
+        M, N, Kd = cfg["batch"] * cfg["seq"], cfg["vocab"], cfg["d_model"]
+    g = torch.Generator(device=device).manual_seed(1)
+    a = torch.randn((M, Kd), generator=g, device=device).bfloat16()
+    w = (torch.randn((N, Kd), generator=g, device=device) / Kd ** 0.5).bfloat16()
+    ldy = (N + 7) // 8 * 8
+    out = torch.empty((M, ldy), dtype=torch.bfloat16, device=device)[:, :N]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    ms = time_launches(lambda: K.matmul_bias_strided(a, w, None, out=out), 10, flush)
+    flops = 2.0 * M * N * Kd
+    ach = flops / (ms * 1e-3) / 1e12
+    return dict(bound="tensor", kernel=f"gemm_tc_kernel (matmul_bias_bt {M}x{N}x{Kd})", achieved=round(ach, 1),
+                peak=peaks["tflops"], unit="TFLOP/s", frac=round(ach / peaks["tflops"], 4), traffic=None,
+                peak_source=peaks["source"], ms_per_launch=round(ms, 4))
+
+
+def standalone_kernels(peaks, device):
+    """The kernels BASELINE's metric names, at its standalone shapes (config 4)."""
+    import torch
+    from mograd_b200 import dispatch as K
+
+    out = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    g = torch.Generator(device=device).manual_seed(3)
+    # fused softmax-cross-entropy fwd+bwd, (16384 x 50304) bf16, index labels
+    N, C = 16384, 50304
+    x = (torch.randn((N, C), generator=g, device=device) * 2).bfloat16()
+    idx = torch.randint(0, C, (N,), generator=g, device=device)
+    dl = torch.empty_like(x)
+
+    def ce():
+        from mograd_b200.dispatch import call, _ptr, _stream, scratch_take, query
+        ws = scratch_take(query("mograd_b200_softmax_xent_workspace_bytes", N, C, 0), device)
+        call("mograd_b200_softmax_xent_fwd_bwd", _ptr(x), _ptr(idx), _ptr(loss), _ptr(dl), N, C, C, C, 1.0, 0,
+             _ptr(ws), ws.numel(), _stream())
+
+    loss = torch.empty((), dtype=torch.float32, device=device)
+    ms = time_launches(ce, 10, flush)
+    nbytes = 2.0 * N * C * 2 + 8 * N + 4
+    out["softmax_xent_fwd_bwd_16384x50304_bf16"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                                                         frac_hbm=round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4),
+                                                         algorithmic_bytes=nbytes)
+    del x, dl
+    # LayerNorm backward
+    for rows, cols in ((16384, 768), (65536, 4096)):
+        xx = torch.randn((rows, cols), generator=g, device=device).bfloat16()
+        dy = torch.randn((rows, cols), generator=g, device=device).bfloat16()
+        gm = torch.ones(cols, device=device).bfloat16()
+        dx, dg, db = torch.empty_like(xx), torch.empty_like(gm), torch.empty_like(gm)
+        ms = time_launches(lambda: K.layer_norm_bwd_dispatch(dy, xx, gm, dx_out=dx, dgamma_out=dg, dbeta_out=db), 10,
+                           flush)
+        nbytes = (3.0 * rows * cols + 3 * cols) * 2
+        out[f"layer_norm_bwd_{rows}x{cols}_bf16"] = dict(ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1),
+                                                         frac_hbm=round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4),
+                                                         algorithmic_bytes=nbytes)
+        del xx, dy, dx
+    # flash-attention backward, B=4 H=16 S=4096 D=128 causal
+    try:
+        B, S, H, D = 4, 4096, 16, 128
+        q, k, v = (torch.randn((B, S, H, D), generator=g, device=device).bfloat16() for _ in range(3))
+        do = torch.randn((B, H, S, D), generator=g, device=device).bfloat16()
+        o, lse = K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False)
+        outs = (torch.empty_like(q), torch.empty_like(q), torch.empty_like(q))
+        ms_f = time_launches(lambda: K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False, out=o, lse_out=lse), 5,
+                             flush)
+        ms_b = time_launches(lambda: K.flash_attn_bwd_dispatch(do, o, q, k, v, None, lse, None, True, False, out=outs),
+                             5, flush)
+        ff, fb = 2.0 * B * H * S * S * D, 5.0 * B * H * S * S * D
+        out["flash_attn_fwd_B4_H16_S4096_D128_causal"] = dict(ms=round(ms_f, 4), tflops=round(ff / ms_f / 1e9, 1),
+                                                              frac_tensor=round(ff / ms_f / 1e9 / peaks["tflops"], 4))
+        out["flash_attn_bwd_B4_H16_S4096_D128_causal"] = dict(ms=round(ms_b, 4), tflops=round(fb / ms_b / 1e9, 1),
+                                                              frac_tensor=round(fb / ms_b / 1e9 / peaks["tflops"], 4))
+    except Exception as e:  # reported, never hidden
+        out["flash_attn"] = dict(error=str(e)[:200])
+    return out
+
+
+# ----------------------------------------------------------------------------- CPU baseline (oracle)
+def cpu_baseline(cfg, budget_s=20.0):
+    """Times the CPU restatement of the same train step on a bounded sample of the batch."""
+    import numpy as np
+    import oracle
+    from oracle import ref_model
+
+    oracle.build()
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(0)
+    if cfg["kind"] == "mlp":
+        dims = cfg["dims"]
+        params = {}
+        for i in range(len(dims) - 1):
+            b = 1.0 / dims[i] ** 0.5
+            params[f"W{i}"] = rng.uniform(-b, b, (dims[i + 1], dims[i])).astype(np.float32)
+            params[f"b{i}"] = rng.uniform(-b, b, dims[i + 1]).astype(np.float32)
+        params["ln_g"] = np.ones(dims[1], np.float32)
+        params["ln_b"] = np.zeros(dims[1], np.float32)
+        n = 16
+        while True:
+            x = rng.standard_normal((n, dims[0])).astype(np.float32)
+            y = rng.integers(0, dims[-1], n)
+            t0 = time.perf_counter()
+            ref_model.mlp_step(params, x, y)
+            dt = time.perf_counter() - t0
+            if dt > budget_s / 4 or n >= cfg["batch"]:
+                break
+            n = min(cfg["batch"], n * 4)
+        return dict(value=round(n / dt, 2), unit="tokens/s", cores=cores, kind="port",
+                    sample=f"{n} of {cfg['batch']} samples, one full fwd+bwd train step in {dt:.2f} s (OpenMP, f64 math)")
+    V, d = cfg["vocab"], cfg["d_model"]
+    params = {"embed": (rng.standard_normal((V, d)) * 0.02).astype(np.float32),
+              "lm_head": (rng.standard_normal((V, d)) * 0.02).astype(np.float32)}
+    for l in range(cfg["n_layers"]):
+        for nm in ("Wq", "Wk", "Wv", "Wo"):
+            params[f"{nm}{l}"] = (rng.standard_normal((d, d)) * 0.02).astype(np.float32)
+        params[f"W1_{l}"] = (rng.standard_normal((cfg["d_ff"], d)) * 0.02).astype(np.float32)
+        params[f"b1_{l}"] = np.zeros(cfg["d_ff"], np.float32)
+        params[f"W2_{l}"] = (rng.standard_normal((d, cfg["d_ff"])) * 0.02).astype(np.float32)
+        for nm in ("g1", "g2"):
+            params[f"{nm}_{l}"] = np.ones(d, np.float32)
+        for nm in ("be1", "be2"):
+            params[f"{nm}_{l}"] = np.zeros(d, np.float32)
+    S = min(cfg["seq"], 128)
+    tok = rng.integers(0, V, (1, S))
+    tgt = rng.integers(0, V, (1, S))
+    t0 = time.perf_counter()
+    ref_model.transformer_step(params, tok, tgt, cfg["n_layers"], cfg["n_heads"])
+    dt = time.perf_counter() - t0
+    return dict(value=round(S / dt, 2), unit="tokens/s", cores=cores, kind="port",
+                sample=f"1 sequence of {S} tokens (of {cfg['batch']}x{cfg['seq']}), one full fwd+bwd step in {dt:.2f} s "
+                       "(OpenMP, f64 math; shorter context understates attention cost)")
+
+
+# ----------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-kernels", action="store_true", help="skip the standalone kernel section")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    base = dict(metric="train_step_tokens_per_s", unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                data="synthetic",
+                config=dict(workload=args.workload, description=cfg["desc"], per_gpu_tokens=cfg["tokens_per_step"],
+                            parallelism=f"dp{args.gpus}", l2="working set (weights, grads, AdamW state, activations) "
+                                                             "exceeds the 126 MB L2 every step"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        t0 = time.perf_counter()
+        vals = []
+        cb = None
+        for _ in range(max(1, min(args.steps, 3))):
+            cb = cpu_baseline(cfg, budget_s=15.0)
+            vals.append(cb["value"])
+            if time.perf_counter() - t0 > 120:
+                break
+        v = statistics.median(vals)
+        cb["value"] = v
+        line = dict(base, impl="reference", value=v, ms_per_step=round(1e3 * cfg["tokens_per_step"] / v, 1),
+                    dtype="f32", cpu_baseline=cb, gpu_launches=0,
+                    e2e=dict(value=v, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                    note="reference = CPU restatement of mograd's math (oracle/); mograd itself is Mojo/MAX and has no "
+                         "CPU runtime; ms_per_step extrapolates the sample to the full batch")
+        print(json.dumps(line), flush=True)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    import mograd_b200
+
+    lib = mograd_b200.load()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    pg = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        pg = dist.group.WORLD
+    peaks = load_peaks()
+    model = build_model(cfg, device, world, pg, seed=0)
+    hx, hy = make_batch(cfg, seed=100 + rank)
+    model.d_inputs.copy_(hx)
+    model.d_targets.copy_(hy)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        model.step_device()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = lib.mograd_b200_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = model.step_device()
+    e1.record()
+    barrier()
+    launches = lib.mograd_b200_launch_count() - l0
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = cfg["tokens_per_step"] * world / (ms_per_step * 1e-3)
+
+    # end to end through the host-facing call: host batch in, loss out, every step
+    for _ in range(2):
+        model.step(hx, hy)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        last = model.step(hx, hy)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = t.item()
+    e2e_val = cfg["tokens_per_step"] * world * args.steps / e2e_s
+    h2d = hx.numel() * hx.element_size() + hy.numel() * hy.element_size()
+
+    if rank == 0:
+        line = dict(base, value=round(value, 1), ms_per_step=round(ms_per_step, 4), clocks=clocks,
+                    e2e=dict(value=round(e2e_val, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4),
+                    gpu_launches=int(launches), loss=round(float(last), 4))
+        line["roofline"] = dominant_gemm_roofline(cfg, peaks, device)
+        if world == 1:
+            if not args.no_kernels:
+                line["kernels"] = standalone_kernels(peaks, device)
+            line["cpu_baseline"] = cpu_baseline(cfg)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -54,6 +54,11 @@ enum mgb_dtype {
  * locked to the toolchain version instead (scripts/build_gpu.sh:46-48). */
 int mograd_b200_abi_version(void);
 
+/* Number of kernels this library has launched in this process so far (all
+ * threads and devices).  No counterpart in the reference; its tracer counts
+ * kernels per run in DebugStats (mograd/debug.mojo:23-46). */
+unsigned long long mograd_b200_launch_count(void);
+
 /* Message for the last negative status returned on this host thread. */
 const char* mograd_b200_last_error(void);
 
@@ -183,6 +188,39 @@ int mograd_b200_flash_attn_bwd(const void* dy, const void* o, const void* q, con
                                const void* mask, const float* lse, void* dq, void* dk, void* dv, int64_t B,
                                int64_t S, int64_t H, int64_t D, float scale, int causal, int has_bias,
                                int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Callers of the hot path inside a train step (elementwise, one pass each).
+ * ---------------------------------------------------------------------- */
+
+/* dx = dy where y > 0 else 0; y is the ReLU OUTPUT, as the reference's rule
+ * passes it (relu_grad, mograd/grad.mojo:130-131; mograd_relu_grad,
+ * __init__.mojo:546-560).  dx may alias dy. */
+int mograd_b200_relu_grad(const void* y, const void* dy, void* dx, int64_t numel, int dtype, void* stream);
+
+/* dst = a + b (residual connections and gradient accumulation; mograd_add,
+ * mograd/runtime/gpu/kernels/elementwise.mojo).  dst may alias a or b. */
+int mograd_b200_add(const void* a, const void* b, void* dst, int64_t numel, int dtype, void* stream);
+
+/* out[t,:] = table[idx[t],:] (Embedding forward; mograd_gather,
+ * mograd/runtime/gpu/kernels/gather_scatter.mojo:14-40).  idx is int64. */
+int mograd_b200_gather_rows(const void* table, const int64_t* idx, void* out, int64_t rows, int64_t vocab, int64_t d,
+                            int dtype, void* stream);
+
+/* dtable[v,:] = sum_{t: idx[t]==v} dout[t,:] (Embedding backward;
+ * mograd_scatter_add, gather_scatter.mojo:43-71).  Accumulates in fp32
+ * (atomics; the summation order is not fixed), writes every row of dtable. */
+size_t mograd_b200_scatter_add_rows_workspace_bytes(int64_t vocab, int64_t d, int dtype);
+int mograd_b200_scatter_add_rows(const void* dout, const int64_t* idx, void* dtable, int64_t rows, int64_t vocab,
+                                 int64_t d, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* One AdamW update with bias correction and decoupled weight decay, the
+ * arithmetic of mograd/nn/optim/adam.mojo:6-58 in a single pass: m, v (and
+ * the optional master copy of w) are float32, g is multiplied by grad_scale
+ * first (1/world_size after a sum-allreduce), step counts from 1. */
+int mograd_b200_adamw_step(void* w, const void* g, float* m, float* v, float* master, int64_t numel, float lr,
+                           float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale,
+                           int dtype, void* stream);
 
 #ifdef __cplusplus
 }

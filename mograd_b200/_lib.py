@@ -32,6 +32,7 @@ EUNSUPPORTED = -6
 # name -> (restype, argtypes); mirrors include/mograd_b200.h declaration by declaration
 SIGNATURES = {
     "mograd_b200_abi_version": (_int, []),
+    "mograd_b200_launch_count": (ctypes.c_ulonglong, []),
     "mograd_b200_last_error": (ctypes.c_char_p, []),
     "mograd_b200_device_status": (_int, [ctypes.POINTER(_int), ctypes.POINTER(_int)]),
     "mograd_b200_matmul_bias_bt": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
@@ -51,6 +52,12 @@ SIGNATURES = {
     "mograd_b200_flash_attn_bwd_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),
     "mograd_b200_flash_attn_bwd": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32,
                                           _int, _int, _int, _p, _sz, _p]),
+    "mograd_b200_relu_grad": (_int, [_p, _p, _p, _i64, _int, _p]),
+    "mograd_b200_add": (_int, [_p, _p, _p, _i64, _int, _p]),
+    "mograd_b200_gather_rows": (_int, [_p, _p, _p, _i64, _i64, _i64, _int, _p]),
+    "mograd_b200_scatter_add_rows_workspace_bytes": (_sz, [_i64, _i64, _int]),
+    "mograd_b200_scatter_add_rows": (_int, [_p, _p, _p, _i64, _i64, _i64, _int, _p, _sz, _p]),
+    "mograd_b200_adamw_step": (_int, [_p, _p, _p, _p, _p, _i64, _f32, _f32, _f32, _f32, _f32, _int, _f32, _int, _p]),
 }
 
 

@@ -1,4 +1,5 @@
 // Library identity, thread-local error text and cached device attributes.
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -16,7 +17,10 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+
 int check_launch(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(MGB_ECUDA, "%s: %s", what, cudaGetErrorString(e));
   return MGB_OK;
@@ -110,6 +114,7 @@ int* device_status_ptr() {
 }  // namespace mgb
 
 MGB_EXPORT int mograd_b200_abi_version(void) { return MOGRAD_B200_ABI_VERSION; }
+MGB_EXPORT unsigned long long mograd_b200_launch_count(void) { return mgb::g_launches.load(std::memory_order_relaxed); }
 MGB_EXPORT const char* mograd_b200_last_error(void) { return mgb::g_err; }
 
 MGB_EXPORT int mograd_b200_device_status(int* code, int* detail) {

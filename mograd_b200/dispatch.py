@@ -113,12 +113,12 @@ def matmul_bias_bt_bwd(dy, x, w, need_dx=True, need_dw=True, need_db=True, dx_ou
 # ----------------------------------------------------------------------------
 # LayerNorm (dispatch.mojo:281-358)
 # ----------------------------------------------------------------------------
-def layer_norm_fwd_dispatch(x, gamma, beta, eps: float = 1e-5, save_stats: bool = False):
+def layer_norm_fwd_dispatch(x, gamma, beta, eps: float = 1e-5, save_stats: bool = False, out=None):
     _require_cuda(x, gamma, beta)
     x = x if x.is_contiguous() else x.contiguous()
     cols = x.shape[-1]
     rows = x.numel() // cols
-    out = torch.empty_like(x)
+    out = torch.empty_like(x) if out is None else out
     mean = rstd = None
     if save_stats:
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
@@ -128,16 +128,16 @@ def layer_norm_fwd_dispatch(x, gamma, beta, eps: float = 1e-5, save_stats: bool 
     return (out, mean, rstd) if save_stats else out
 
 
-def layer_norm_bwd_dispatch(dy, x, gamma, eps: float = 1e-5):
+def layer_norm_bwd_dispatch(dy, x, gamma, eps: float = 1e-5, dx_out=None, dgamma_out=None, dbeta_out=None):
     """inputs [dy, x, gamma] -> [dx, dgamma, dbeta] (dispatch.mojo:332-358)."""
     _require_cuda(dy, x, gamma)
     x = x if x.is_contiguous() else x.contiguous()
     dy = dy if dy.is_contiguous() else dy.contiguous()
     cols = x.shape[-1]
     rows = x.numel() // cols
-    dx = torch.empty_like(x)
-    dgamma = torch.empty_like(gamma)
-    dbeta = torch.empty_like(gamma)
+    dx = torch.empty_like(x) if dx_out is None else dx_out
+    dgamma = torch.empty_like(gamma) if dgamma_out is None else dgamma_out
+    dbeta = torch.empty_like(gamma) if dbeta_out is None else dbeta_out
     code = dtype_code(x)
     nbytes = query("mograd_b200_layer_norm_bwd_workspace_bytes", rows, cols, code)
     ws = scratch_take(nbytes, x.device)
@@ -197,7 +197,7 @@ def softmax_xent_fwd_bwd(logits, index, upstream: float = 1.0, want_loss=True, w
 # ----------------------------------------------------------------------------
 # Attention (dispatch.mojo:380-481)
 # ----------------------------------------------------------------------------
-def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_bias=None):
+def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_bias=None, out=None, lse_out=None):
     """srcs [Q, K, V, mask] all BSHD -> [O (BHSD), LSE (B,H,S) float32]."""
     _require_cuda(q, k, v, mask)
     B, S, H, D = q.shape
@@ -206,14 +206,14 @@ def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
-    dst = torch.empty((B, H, S, D), dtype=q.dtype, device=q.device)
-    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    dst = torch.empty((B, H, S, D), dtype=q.dtype, device=q.device) if out is None else out
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if lse_out is None else lse_out
     call("mograd_b200_flash_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(dst), _ptr(lse), B, S, H, D,
          float(scale), int(bool(is_causal)), int(bool(has_bias)), dtype_code(q), _stream())
     return [dst, lse]
 
 
-def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=True, has_bias=None):
+def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=True, has_bias=None, out=None):
     """srcs [dO, O, Q, K, V, mask, LSE] -> [dQ, dK, dV] (BSHD)."""
     _require_cuda(dy, o, q, k, v, mask, lse)
     B, S, H, D = q.shape
@@ -222,12 +222,56 @@ def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=Tru
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dy = dy if dy.is_contiguous() else dy.contiguous()  # the rule makes dO contiguous (grad.mojo:336-339)
-    dq = torch.empty_like(q)
-    dk = torch.empty_like(q)
-    dv = torch.empty_like(q)
+    dq, dk, dv = out if out is not None else (torch.empty_like(q), torch.empty_like(q), torch.empty_like(q))
     code = dtype_code(q)
     ws = scratch_take(query("mograd_b200_flash_attn_bwd_workspace_bytes", B, S, H, D, code), q.device)
     call("mograd_b200_flash_attn_bwd", _ptr(dy), _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(lse), _ptr(dq),
          _ptr(dk), _ptr(dv), B, S, H, D, float(scale), int(bool(is_causal)), int(bool(has_bias)), code, _ptr(ws),
          ws.numel(), _stream())
     return [dq, dk, dv]
+
+
+# ----------------------------------------------------------------------------
+# Callers of the hot path inside a train step
+# ----------------------------------------------------------------------------
+def relu_grad(y, dy, out=None):
+    """RELU_GRAD(node=relu output, upstream) (runtime/__init__.mojo:351-352)."""
+    _require_cuda(y, dy)
+    out = dy if out is None else out
+    call("mograd_b200_relu_grad", _ptr(y), _ptr(dy), _ptr(out), y.numel(), dtype_code(y), _stream())
+    return out
+
+
+def add(a, b, out=None):
+    _require_cuda(a, b)
+    out = torch.empty_like(a) if out is None else out
+    call("mograd_b200_add", _ptr(a), _ptr(b), _ptr(out), a.numel(), dtype_code(a), _stream())
+    return out
+
+
+def gather_rows(table, idx, out=None):
+    """Embedding forward: out[t] = table[idx[t]]."""
+    _require_cuda(table, idx)
+    V, d = table.shape
+    T = idx.numel()
+    out = torch.empty((T, d), dtype=table.dtype, device=table.device) if out is None else out
+    call("mograd_b200_gather_rows", _ptr(table), _ptr(idx), _ptr(out), T, V, d, dtype_code(table), _stream())
+    return out
+
+
+def scatter_add_rows(dout, idx, vocab, out=None):
+    """Embedding backward: dtable[v] = sum of dout rows whose index is v."""
+    _require_cuda(dout, idx)
+    T, d = dout.shape
+    out = torch.empty((vocab, d), dtype=dout.dtype, device=dout.device) if out is None else out
+    code = dtype_code(dout)
+    ws = scratch_take(query("mograd_b200_scatter_add_rows_workspace_bytes", vocab, d, code), dout.device)
+    call("mograd_b200_scatter_add_rows", _ptr(dout), _ptr(idx), _ptr(out), T, vocab, d, code, _ptr(ws), ws.numel(),
+         _stream())
+    return out
+
+
+def adamw_step(w, g, m, v, master, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0):
+    _require_cuda(w, g, m, v, master)
+    call("mograd_b200_adamw_step", _ptr(w), _ptr(g), _ptr(m), _ptr(v), _ptr(master), w.numel(), float(lr), float(beta1),
+         float(beta2), float(eps), float(weight_decay), int(step), float(grad_scale), dtype_code(w), _stream())

@@ -1,0 +1,342 @@
+"""Train-step runner over the C-ABI kernels: the two model families of the
+reference's examples, executed the way mograd's scheduler would execute the
+simplified forward graph and the gradient sub-graph its rules build.
+
+  * MLP              -- examples/mnist (Linear/ReLU/LayerNorm/Linear + CE)
+  * TinyTransformer  -- examples/tinyshakespear/model.mojo:10-130 (Embedding,
+    pre-LayerNorm blocks with bias-free Q/K/V/O, ReLU FFN with a bias on W1
+    only, untied bias-free lm_head, no positional embedding, no final norm)
+
+All parameters live in one flat buffer (and their gradients in another laid
+out the same way), so the optimiser is a single AdamW launch and the
+data-parallel exchange is a handful of large NCCL all-reduces over contiguous
+slices that are issued while the rest of the backward pass is still running.
+PyTorch supplies device memory, streams and the NCCL process group only.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import dispatch as K
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+class ParamStore:
+    """Flat parameter / gradient / optimiser-state buffers with named views."""
+
+    def __init__(self, dtype, device):
+        self.dtype = dtype
+        self.device = device
+        self.specs = []  # (name, shape, offset)
+        self.size = 0
+
+    def declare(self, name, shape):
+        n = 1
+        for s in shape:
+            n *= s
+        off = self.size
+        self.specs.append((name, tuple(shape), off))
+        self.size = off + (n + 127) // 128 * 128  # keep every tensor 256-byte aligned
+        return name
+
+    def allocate(self):
+        self.w = torch.zeros(self.size, dtype=self.dtype, device=self.device)
+        self.g = torch.zeros(self.size, dtype=self.dtype, device=self.device)
+        self.m = torch.zeros(self.size, dtype=torch.float32, device=self.device)
+        self.v = torch.zeros(self.size, dtype=torch.float32, device=self.device)
+        self.master = torch.zeros(self.size, dtype=torch.float32, device=self.device)
+        self.P, self.G, self.range = {}, {}, {}
+        for name, shape, off in self.specs:
+            n = 1
+            for s in shape:
+                n *= s
+            self.P[name] = self.w[off:off + n].view(shape)
+            self.G[name] = self.g[off:off + n].view(shape)
+            self.range[name] = (off, off + n)
+
+    def load(self, values: dict):
+        """values: name -> float32 CPU tensor; fills master and the working copy."""
+        for name, t in values.items():
+            off, end = self.range[name]
+            self.master[off:end].copy_(t.reshape(-1).to(self.device, torch.float32))
+        self.w.copy_(self.master.to(self.dtype))
+        self.master.copy_(self.w.float())  # the master starts as the rounded working copy
+
+
+@dataclass
+class AdamWConfig:
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+
+
+class _Model:
+    """Shared plumbing: flat params, bucketed gradient exchange, optimiser, host-facing step()."""
+
+    def __init__(self, dtype, device, opt: AdamWConfig | None, world_size=1, process_group=None,
+                 bucket_bytes=64 << 20):
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.opt = opt or AdamWConfig()
+        self.world_size = world_size
+        self.pg = process_group
+        self.bucket_bytes = bucket_bytes
+        self.store = ParamStore(dtype, self.device)
+        self.step_count = 0
+        self.comm_stream = None
+        self._bucket_lo = None
+        self.launches = 0
+
+    # ---- data-parallel gradient exchange -------------------------------------------------
+    def _setup_buckets(self):
+        if self.world_size > 1:
+            self.comm_stream = torch.cuda.Stream(device=self.device)
+        esz = self.store.g.element_size()
+        per = max(1, self.bucket_bytes // esz)
+        # buckets are contiguous slices; gradients are produced from the end of the buffer backwards
+        self.buckets = []
+        hi = self.store.size
+        while hi > 0:
+            lo = max(0, hi - per)
+            self.buckets.append((lo, hi))
+            hi = lo
+        self._next_bucket = 0
+
+    def _grads_ready_down_to(self, offset: int):
+        """Everything in the flat gradient buffer at or above `offset` is final: exchange the buckets it covers."""
+        if self.world_size == 1:
+            return
+        import torch.distributed as dist
+
+        while self._next_bucket < len(self.buckets) and self.buckets[self._next_bucket][0] >= offset:
+            lo, hi = self.buckets[self._next_bucket]
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
+            self._next_bucket += 1
+
+    def _finish_exchange(self):
+        if self.world_size == 1:
+            return
+        self._grads_ready_down_to(0)
+        torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        self._next_bucket = 0
+
+    def optimizer_step(self):
+        self.step_count += 1
+        o = self.opt
+        s = self.store
+        K.adamw_step(s.w, s.g, s.m, s.v, s.master, o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, self.step_count,
+                     grad_scale=1.0 / self.world_size)
+
+    # ---- host-facing call: host buffers in, loss out -------------------------------------
+    def step(self, host_inputs, host_targets) -> float:
+        """One train step from pinned host tensors; returns the loss as a Python float (device->host read)."""
+        self.d_inputs.copy_(host_inputs, non_blocking=True)
+        self.d_targets.copy_(host_targets, non_blocking=True)
+        loss = self.step_device()
+        self.h_loss.copy_(loss, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return float(self.h_loss.item())
+
+    def step_device(self):
+        loss = self.forward_backward()
+        self._finish_exchange()
+        self.optimizer_step()
+        return loss
+
+
+class MLP(_Model):
+    """Linear(d0->d1)+ReLU -> LayerNorm(d1) -> [Linear+ReLU]* -> Linear(->classes), cross-entropy loss."""
+
+    def __init__(self, dims, batch, dtype=torch.bfloat16, device="cuda", opt=None, seed=0, **kw):
+        super().__init__(dtype, device, opt, **kw)
+        self.dims = list(dims)
+        self.batch = batch
+        self.nl = len(dims) - 1
+        st = self.store
+        for i in range(self.nl):
+            st.declare(f"W{i}", (dims[i + 1], dims[i]))
+            st.declare(f"b{i}", (dims[i + 1],))
+            if i == 0:
+                st.declare("ln_g", (dims[1],))
+                st.declare("ln_b", (dims[1],))
+        st.allocate()
+        g = torch.Generator().manual_seed(seed)
+        vals = {}
+        for i in range(self.nl):
+            bound = 1.0 / math.sqrt(dims[i])
+            vals[f"W{i}"] = (torch.rand((dims[i + 1], dims[i]), generator=g) * 2 - 1) * bound
+            vals[f"b{i}"] = (torch.rand((dims[i + 1],), generator=g) * 2 - 1) * bound
+        vals["ln_g"] = torch.ones(dims[1])
+        vals["ln_b"] = torch.zeros(dims[1])
+        st.load(vals)
+        self._setup_buckets()
+        dev, B = self.device, batch
+        self.d_inputs = torch.empty((B, dims[0]), dtype=dtype, device=dev)
+        self.d_targets = torch.empty((B,), dtype=torch.int64, device=dev)
+        self.h_loss = torch.empty((), dtype=torch.float32).pin_memory() if dev.type == "cuda" else torch.empty(())
+        self.act = [torch.empty((B, dims[i + 1]), dtype=dtype, device=dev) for i in range(self.nl - 1)]
+        self.ln_out = torch.empty((B, dims[1]), dtype=dtype, device=dev)
+        self.C = dims[-1]
+        self.logits_buf = torch.empty((B, _pad8(self.C)), dtype=dtype, device=dev)
+        self.logits = self.logits_buf[:, :self.C]
+        self.dact = [torch.empty((B, dims[i + 1]), dtype=dtype, device=dev) for i in range(self.nl - 1)]
+        self.dln = torch.empty((B, dims[1]), dtype=dtype, device=dev)
+
+    def forward_backward(self):
+        P, G = self.store.P, self.store.G
+        x = self.d_inputs
+        # forward
+        K.matmul_bias_strided(x, P["W0"], P["b0"], act=1, out=self.act[0])
+        K.layer_norm_fwd_dispatch(self.act[0], P["ln_g"], P["ln_b"], out=self.ln_out)
+        h = self.ln_out
+        for i in range(1, self.nl - 1):
+            K.matmul_bias_strided(h, P[f"W{i}"], P[f"b{i}"], act=1, out=self.act[i])
+            h = self.act[i]
+        K.matmul_bias_strided(h, P[f"W{self.nl - 1}"], P[f"b{self.nl - 1}"], out=self.logits)
+        loss, dl = K.softmax_xent_fwd_bwd(self.logits, self.d_targets, inplace=True)
+        # backward
+        dy = dl
+        for i in range(self.nl - 1, 0, -1):
+            inp = self.act[i - 1] if i > 1 else self.ln_out
+            dst = self.dact[i - 1] if i > 1 else self.dln
+            K.matmul_bias_bt_bwd(dy, inp, P[f"W{i}"], dx_out=dst, dw_out=G[f"W{i}"], db_out=G[f"b{i}"])
+            self._grads_ready_down_to(self.store.range[f"W{i}"][0])
+            if i > 1:
+                K.relu_grad(self.act[i - 1], dst)
+            dy = dst
+        K.layer_norm_bwd_dispatch(self.dln, self.act[0], P["ln_g"], dx_out=self.dln, dgamma_out=G["ln_g"],
+                                  dbeta_out=G["ln_b"])
+        K.relu_grad(self.act[0], self.dln)
+        K.matmul_bias_bt_bwd(self.dln, x, P["W0"], need_dx=False, dw_out=G["W0"], db_out=G["b0"])
+        return loss
+
+
+class TinyTransformer(_Model):
+    """Decoder-only transformer of examples/tinyshakespear/model.mojo, one train step at a time."""
+
+    def __init__(self, vocab, d_model, d_ff, n_layers, n_heads, batch, seq, dtype=torch.bfloat16, device="cuda",
+                 opt=None, seed=0, init_std=0.02, **kw):
+        super().__init__(dtype, device, opt, **kw)
+        self.V, self.d, self.dff, self.L, self.H = vocab, d_model, d_ff, n_layers, n_heads
+        self.B, self.S = batch, seq
+        self.Dh = d_model // n_heads
+        self.T = batch * seq
+        st = self.store
+        st.declare("embed", (vocab, d_model))
+        for l in range(n_layers):
+            for nm in ("Wq", "Wk", "Wv", "Wo"):
+                st.declare(f"{nm}{l}", (d_model, d_model))
+            st.declare(f"W1_{l}", (d_ff, d_model))
+            st.declare(f"b1_{l}", (d_ff,))
+            st.declare(f"W2_{l}", (d_model, d_ff))
+            for nm in ("g1", "be1", "g2", "be2"):
+                st.declare(f"{nm}_{l}", (d_model,))
+        st.declare("lm_head", (vocab, d_model))
+        st.allocate()
+        g = torch.Generator().manual_seed(seed)
+        vals = {}
+        for name, shape, _ in st.specs:
+            if name.startswith(("g1_", "g2_")):
+                vals[name] = torch.ones(shape)
+            elif name.startswith(("be1_", "be2_", "b1_")):
+                vals[name] = torch.zeros(shape)
+            else:
+                vals[name] = torch.randn(shape, generator=g) * init_std
+        st.load(vals)
+        self._setup_buckets()
+        dev, T, d = self.device, self.T, d_model
+        new = lambda *shape: torch.empty(shape, dtype=dtype, device=dev)
+        self.d_inputs = torch.empty((batch, seq), dtype=torch.int64, device=dev)
+        self.d_targets = torch.empty((batch, seq), dtype=torch.int64, device=dev)
+        self.h_loss = torch.empty((), dtype=torch.float32).pin_memory() if dev.type == "cuda" else torch.empty(())
+        self.x = [new(T, d) for _ in range(n_layers + 1)]  # block inputs, x[L] = final hidden state
+        self.saved = []
+        for _ in range(n_layers):
+            self.saved.append(dict(ln1=new(T, d), q=new(T, d), k=new(T, d), v=new(T, d),
+                                   o=new(batch, n_heads, seq, self.Dh),
+                                   lse=torch.empty((batch, n_heads, seq), dtype=torch.float32, device=dev),
+                                   ctx=new(T, d), h=new(T, d), ln2=new(T, d), f1=new(T, d_ff)))
+        self.Vp = _pad8(vocab)
+        self.logits_buf = new(T, self.Vp)
+        self.logits = self.logits_buf[:, :vocab]
+        # backward scratch, reused by every block
+        self.t_a, self.t_b, self.t_c, self.t_d = new(T, d), new(T, d), new(T, d), new(T, d)
+        self.t_ff = new(T, d_ff)
+        self.dO = new(batch, n_heads, seq, self.Dh)
+
+    # BSHD <-> BHSD copies (the reference's .transpose(1, 2) + contiguous around the attention node)
+    def _to_bshd(self, src_bhsd, dst_td):
+        dst_td.view(self.B, self.S, self.H, self.Dh).copy_(src_bhsd.permute(0, 2, 1, 3))
+
+    def _to_bhsd(self, src_td, dst_bhsd):
+        dst_bhsd.copy_(src_td.view(self.B, self.S, self.H, self.Dh).permute(0, 2, 1, 3))
+
+    def forward_backward(self):
+        P, G, st = self.store.P, self.store.G, self.store
+        B, S, H, Dh, L = self.B, self.S, self.H, self.Dh, self.L
+        tok = self.d_inputs.view(-1)
+        K.gather_rows(P["embed"], tok, out=self.x[0])
+        for l in range(L):
+            sv, x = self.saved[l], self.x[l]
+            K.layer_norm_fwd_dispatch(x, P[f"g1_{l}"], P[f"be1_{l}"], out=sv["ln1"])
+            K.matmul_bias_strided(sv["ln1"], P[f"Wq{l}"], out=sv["q"])
+            K.matmul_bias_strided(sv["ln1"], P[f"Wk{l}"], out=sv["k"])
+            K.matmul_bias_strided(sv["ln1"], P[f"Wv{l}"], out=sv["v"])
+            q4, k4, v4 = (sv[n].view(B, S, H, Dh) for n in ("q", "k", "v"))
+            K.flash_attn_fwd_dispatch(q4, k4, v4, None, None, True, False, out=sv["o"], lse_out=sv["lse"])
+            self._to_bshd(sv["o"], sv["ctx"])
+            K.matmul_bias_strided(sv["ctx"], P[f"Wo{l}"], out=self.t_a)
+            K.add(x, self.t_a, out=sv["h"])
+            K.layer_norm_fwd_dispatch(sv["h"], P[f"g2_{l}"], P[f"be2_{l}"], out=sv["ln2"])
+            K.matmul_bias_strided(sv["ln2"], P[f"W1_{l}"], P[f"b1_{l}"], act=1, out=sv["f1"])
+            K.matmul_bias_strided(sv["f1"], P[f"W2_{l}"], out=self.t_a)
+            K.add(sv["h"], self.t_a, out=self.x[l + 1])
+        K.matmul_bias_strided(self.x[L], P["lm_head"], out=self.logits)
+        loss, dl = K.softmax_xent_fwd_bwd(self.logits, self.d_targets.view(-1), inplace=True)
+
+        # ---- backward
+        dx = self.t_a  # gradient w.r.t. the current block's output
+        K.matmul_bias_bt_bwd(dl, self.x[L], P["lm_head"], dx_out=dx, dw_out=G["lm_head"], need_db=False)
+        self._grads_ready_down_to(st.range["lm_head"][0])
+        for l in range(L - 1, -1, -1):
+            sv, x = self.saved[l], self.x[l]
+            # FFN: out = h + W2 relu(W1 ln2 + b1)
+            K.matmul_bias_bt_bwd(dx, sv["f1"], P[f"W2_{l}"], dx_out=self.t_ff, dw_out=G[f"W2_{l}"], need_db=False)
+            K.relu_grad(sv["f1"], self.t_ff)
+            K.matmul_bias_bt_bwd(self.t_ff, sv["ln2"], P[f"W1_{l}"], dx_out=self.t_b, dw_out=G[f"W1_{l}"],
+                                 db_out=G[f"b1_{l}"])
+            K.layer_norm_bwd_dispatch(self.t_b, sv["h"], P[f"g2_{l}"], dx_out=self.t_c, dgamma_out=G[f"g2_{l}"],
+                                      dbeta_out=G[f"be2_{l}"])
+            K.add(dx, self.t_c, out=dx)  # dh
+            # attention: h = x + Wo ctx
+            K.matmul_bias_bt_bwd(dx, sv["ctx"], P[f"Wo{l}"], dx_out=self.t_b, dw_out=G[f"Wo{l}"], need_db=False)
+            self._to_bhsd(self.t_b, self.dO)
+            q4, k4, v4 = (sv[n].view(B, S, H, Dh) for n in ("q", "k", "v"))
+            dq, dk, dv = self.t_b.view(B, S, H, Dh), self.t_c.view(B, S, H, Dh), self.t_d.view(B, S, H, Dh)
+            K.flash_attn_bwd_dispatch(self.dO, sv["o"], q4, k4, v4, None, sv["lse"], None, True, False,
+                                      out=(dq, dk, dv))
+            # ln1 feeds Q, K and V
+            dln1 = sv["ctx"]  # free to overwrite now
+            K.matmul_bias_bt_bwd(self.t_b, sv["ln1"], P[f"Wq{l}"], dx_out=dln1, dw_out=G[f"Wq{l}"], need_db=False)
+            K.matmul_bias_bt_bwd(self.t_c, sv["ln1"], P[f"Wk{l}"], dx_out=self.t_b, dw_out=G[f"Wk{l}"], need_db=False)
+            K.add(dln1, self.t_b, out=dln1)
+            K.matmul_bias_bt_bwd(self.t_d, sv["ln1"], P[f"Wv{l}"], dx_out=self.t_b, dw_out=G[f"Wv{l}"], need_db=False)
+            K.add(dln1, self.t_b, out=dln1)
+            K.layer_norm_bwd_dispatch(dln1, x, P[f"g1_{l}"], dx_out=self.t_c, dgamma_out=G[f"g1_{l}"],
+                                      dbeta_out=G[f"be1_{l}"])
+            K.add(dx, self.t_c, out=dx)
+            self._grads_ready_down_to(st.range[f"Wq{l}"][0])
+        K.scatter_add_rows(dx, tok, self.V, out=G["embed"])
+        return loss
