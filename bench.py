@@ -246,6 +246,50 @@ def standalone_kernels(peaks, device):
     return out
 
 
+def profile_case(name, reps, device):
+    """Runs one kernel a few times on a small case (inputs > L2, < 2 GB) so a profiler capture stays short."""
+    import torch
+    from mograd_b200 import dispatch as K
+
+    g = torch.Generator(device=device).manual_seed(5)
+    if name == "xent":
+        N, C = 4096, 50304
+        x = (torch.randn((N, C), generator=g, device=device) * 2).bfloat16()
+        idx = torch.randint(0, C, (N,), generator=g, device=device)
+        fn = lambda: K.softmax_xent_fwd_bwd(x, idx)
+    elif name == "ln_bwd":
+        rows, cols = 16384, 4096
+        xx = torch.randn((rows, cols), generator=g, device=device).bfloat16()
+        dy = torch.randn((rows, cols), generator=g, device=device).bfloat16()
+        gm = torch.ones(cols, device=device).bfloat16()
+        fn = lambda: K.layer_norm_bwd_dispatch(dy, xx, gm)
+    elif name == "ln_bwd_768":
+        rows, cols = 131072, 768
+        xx = torch.randn((rows, cols), generator=g, device=device).bfloat16()
+        dy = torch.randn((rows, cols), generator=g, device=device).bfloat16()
+        gm = torch.ones(cols, device=device).bfloat16()
+        fn = lambda: K.layer_norm_bwd_dispatch(dy, xx, gm)
+    elif name == "gemm":
+        a = torch.randn((8192, 4096), generator=g, device=device).bfloat16()
+        w = (torch.randn((4096, 4096), generator=g, device=device) / 64).bfloat16()
+        fn = lambda: K.matmul_bias_strided(a, w)
+    elif name in ("flash_fwd", "flash_bwd"):
+        B, S, H, D = 1, 4096, 16, 128
+        q, k, v = (torch.randn((B, S, H, D), generator=g, device=device).bfloat16() for _ in range(3))
+        do = torch.randn((B, H, S, D), generator=g, device=device).bfloat16()
+        o, lse = K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False)
+        if name == "flash_fwd":
+            fn = lambda: K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False)
+        else:
+            fn = lambda: K.flash_attn_bwd_dispatch(do, o, q, k, v, None, lse, None, True, False)
+    else:
+        raise SystemExit(f"unknown case {name}")
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    print(json.dumps(dict(case=name, reps=reps, status="ok")), flush=True)
+
+
 # ----------------------------------------------------------------------------- CPU baseline (oracle)
 def cpu_baseline(cfg, budget_s=20.0):
     """Times the CPU restatement of the same train step on a bounded sample of the batch."""
@@ -310,7 +354,16 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-kernels", action="store_true", help="skip the standalone kernel section")
+    ap.add_argument("--case", default=None, help="run one small kernel case --reps times and exit (for profiling)")
+    ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
+    if args.case:
+        import torch
+        import mograd_b200
+
+        mograd_b200.load()
+        profile_case(args.case, args.reps, torch.device("cuda", 0))
+        return 0
     cfg = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -367,12 +420,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
-        model.step_device()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(3, args.warmup)):
+        model.step_device()
+    barrier()
     l0 = lib.mograd_b200_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -386,7 +439,6 @@ def main():
         t = torch.tensor([ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = t.item()
-    clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
     value = cfg["tokens_per_step"] * world / (ms_per_step * 1e-3)
 
@@ -403,6 +455,7 @@ def main():
         t = torch.tensor([e2e_s], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = t.item()
+    clocks = sampler.stop() if rank == 0 else None  # samples span warm-up, the timed steps and the end-to-end steps
     e2e_val = cfg["tokens_per_step"] * world * args.steps / e2e_s
     h2d = hx.numel() * hx.element_size() + hy.numel() * hy.element_size()
 
