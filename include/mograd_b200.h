@@ -124,6 +124,27 @@ int mograd_b200_layer_norm_bwd(const void* dy, const void* x, const void* gamma,
                                void* dbeta, int64_t rows, int64_t cols, float eps, int dtype, void* workspace,
                                size_t workspace_bytes, void* stream);
 
+/* LayerNorm backward without a workspace argument.  It has no counterpart in
+ * the reference.  It is for hosts that cannot hand the kernel a scratch
+ * buffer because they are not allowed to allocate device memory at the point
+ * of the call: a plugin running inside someone else's stream capture, a
+ * runtime whose memory pool is frozen after start-up, or a callback that must
+ * not re-enter the allocator.  The partial dgamma / dbeta rows go to an array
+ * of 9.25 MiB that is part of the library image on every GPU that loads it.
+ * On a B200 every shape with cols <= 4096 fits; wider rows fit only while
+ * rows is small.  A request that needs more returns MGB_EUNSUPPORTED with the
+ * sizes in the error text.  Inputs, outputs and results
+ * are those of mograd_b200_layer_norm_bwd, bit for bit.
+ *   - The first call on each device looks the array's address up (with that
+ *     device current); make that first call outside any stream capture.
+ *   - Neither this call nor anything it uses calls cudaMalloc / cudaFree.
+ *   - All calls on a device share the one array.  Nothing in it has to be
+ *     zero beforehand (every element that is read was written earlier in the
+ *     same call), but two calls whose kernels overlap on the GPU (different
+ *     streams, no dependency) race on it: keep them ordered. */
+int mograd_b200_layer_norm_bwd_static(const void* dy, const void* x, const void* gamma, void* dx, void* dgamma,
+                                      void* dbeta, int64_t rows, int64_t cols, float eps, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------
  * Cross-entropy with dense float labels of the logits' shape, mean over
  * rows; loss is one element of `dtype`.  Replaces mograd_cross_entropy /

@@ -42,6 +42,7 @@ SIGNATURES = {
     "mograd_b200_layer_norm_fwd": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _int, _p]),
     "mograd_b200_layer_norm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "mograd_b200_layer_norm_bwd": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _int, _p, _sz, _p]),
+    "mograd_b200_layer_norm_bwd_static": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _int, _p]),
     "mograd_b200_cross_entropy_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "mograd_b200_cross_entropy": (_int, [_p, _p, _p, _i64, _i64, _i64, _i64, _int, _p, _sz, _p]),
     "mograd_b200_cross_entropy_grad": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _int, _p]),

@@ -426,6 +426,34 @@ int ln_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dga
   return check_launch("ln_bwd_finalize_kernel");
 }
 
+// Scratch for mograd_b200_layer_norm_bwd_static: room for the per-CTA dgamma /
+// dbeta partial rows of a launch of up to 296 CTAs at cols <= 4096
+// (296 * 2 * 4096 floats, 9.25 MiB).  It lives in every CUDA context that loads
+// this library, from load until the process exits.
+constexpr size_t kStaticScratchFloats = static_cast<size_t>(296) * 2 * 4096;
+static __device__ __align__(256) float g_ln_bwd_static_scratch[kStaticScratchFloats];
+
+// Device address of the array on the current device.  The array's name is only
+// a host-side handle here, so it is resolved once per device through the
+// runtime and cached; the resolved pointer is what the kernels receive.
+int static_scratch_ptr(float** out) {
+  constexpr int kDevs = 64;
+  static float* cache[kDevs] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MGB_ECUDA, "layer_norm_bwd_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  MGB_REQUIRE(dev >= 0 && dev < kDevs, MGB_EUNSUPPORTED, "layer_norm_bwd_static: device ordinal %d out of range", dev);
+  if (!cache[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_bwd_static_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(MGB_ECUDA, "layer_norm_bwd_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    cache[dev] = p;
+  }
+  *out = cache[dev];
+  return MGB_OK;
+}
+
 int check_ln(const char* who, int64_t rows, int64_t cols) {
   MGB_REQUIRE(rows > 0 && cols > 0, MGB_EINVAL, "%s: rows=%lld cols=%lld must be positive", who, (long long)rows,
               (long long)cols);
@@ -478,4 +506,30 @@ MGB_EXPORT int mograd_b200_layer_norm_bwd(const void* dy, const void* x, const v
     default:
       return fail(MGB_EDTYPE, "layer_norm_bwd: unsupported dtype code %d", dtype);
   }
+}
+
+// Same computation and kernels as mograd_b200_layer_norm_bwd, for callers that
+// have no allocator to take a workspace from: the partial rows go to the
+// library's own statically allocated device array instead.
+MGB_EXPORT int mograd_b200_layer_norm_bwd_static(const void* dy, const void* x, const void* gamma, void* dx,
+                                                 void* dgamma, void* dbeta, int64_t rows, int64_t cols, float eps,
+                                                 int dtype, void* stream) {
+  MGB_REQUIRE(dy && x && gamma && dx && dgamma && dbeta, MGB_EINVAL, "layer_norm_bwd_static: NULL argument");
+  int rc = check_ln("layer_norm_bwd_static", rows, cols);
+  if (rc != MGB_OK) return rc;
+  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32, MGB_EDTYPE, "layer_norm_bwd_static: unsupported dtype code %d",
+              dtype);
+  const size_t need = mograd_b200_layer_norm_bwd_workspace_bytes(rows, cols, dtype);
+  const size_t have = kStaticScratchFloats * sizeof(float);
+  MGB_REQUIRE(need > 0 && need <= have, MGB_EUNSUPPORTED,
+              "layer_norm_bwd_static: rows=%lld cols=%lld needs %zu bytes of scratch, the built-in array holds %zu "
+              "(cols <= 4096 always fits); use layer_norm_bwd with a caller workspace",
+              (long long)rows, (long long)cols, need, have);
+  float* scratch = nullptr;
+  rc = static_scratch_ptr(&scratch);
+  if (rc != MGB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MGB_BF16)
+    return ln_bwd<__nv_bfloat16>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
+  return ln_bwd<float>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
 }
