@@ -1,13 +1,78 @@
-// Attention entry points (placeholder until the kernels land).
+// Attention entry points: argument checks and routing between the tcgen05
+// kernels (bf16, D = 64 / 128, no bias) and the CUDA-core kernels (the rest).
+#include "attn.cuh"
 #include "common.cuh"
+
 using namespace mgb;
-MGB_EXPORT int mograd_b200_flash_attn_fwd(const void*, const void*, const void*, const void*, void*, float*, int64_t,
-                                          int64_t, int64_t, int64_t, float, int, int, int, void*) {
-  return fail(MGB_EUNSUPPORTED, "flash_attn_fwd: not built yet");
+
+namespace {
+
+int check_attn(const char* who, int64_t B, int64_t S, int64_t H, int64_t D, int causal, int has_bias, int dtype) {
+  MGB_REQUIRE(B > 0 && S > 0 && H > 0, MGB_EINVAL, "%s: B=%lld S=%lld H=%lld must be positive", who, (long long)B,
+              (long long)S, (long long)H);
+  MGB_REQUIRE(D >= 1 && D <= 512, MGB_EUNSUPPORTED, "%s: head dim %lld outside [1, 512]", who, (long long)D);
+  MGB_REQUIRE(!(causal && has_bias), MGB_EINVAL, "%s: causal and has_bias cannot both be set", who);
+  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32, MGB_EDTYPE, "%s: unsupported dtype code %d", who, dtype);
+  MGB_REQUIRE(B * H * S < (1LL << 31) && S < (1 << 30), MGB_EUNSUPPORTED, "%s: B*H*S exceeds 2^31", who);
+  return MGB_OK;
 }
-MGB_EXPORT size_t mograd_b200_flash_attn_bwd_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int) { return 0; }
-MGB_EXPORT int mograd_b200_flash_attn_bwd(const void*, const void*, const void*, const void*, const void*, const void*,
-                                          const float*, void*, void*, void*, int64_t, int64_t, int64_t, int64_t, float,
-                                          int, int, int, void*, size_t, void*) {
-  return fail(MGB_EUNSUPPORTED, "flash_attn_bwd: not built yet");
+
+size_t delta_bytes(int64_t B, int64_t S, int64_t H) { return round_up(static_cast<size_t>(B * H * S) * sizeof(float), 256); }
+size_t dq_acc_bytes(int64_t B, int64_t S, int64_t H, int64_t D) {
+  return round_up(static_cast<size_t>(B * S * H * D) * sizeof(float), 256);
+}
+
+}  // namespace
+
+MGB_EXPORT int mograd_b200_flash_attn_fwd(const void* q, const void* k, const void* v, const void* mask, void* dst,
+                                          float* lse, int64_t B, int64_t S, int64_t H, int64_t D, float scale,
+                                          int causal, int has_bias, int dtype, void* stream) {
+  MGB_REQUIRE(q && k && v && dst && lse, MGB_EINVAL, "flash_attn_fwd: NULL argument");
+  MGB_REQUIRE(!has_bias || mask, MGB_EINVAL, "flash_attn_fwd: has_bias set but mask is NULL");
+  int rc = check_attn("flash_attn_fwd", B, S, H, D, causal, has_bias, dtype);
+  if (rc != MGB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int b = static_cast<int>(B), s = static_cast<int>(S), h = static_cast<int>(H), d = static_cast<int>(D);
+  if (dtype == MGB_F32) return attn::generic_fwd<float>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, st);
+  const void* ptrs[] = {q, k, v, dst};
+  if (attn::tc_supported(d, has_bias, ptrs, 4)) return attn::tc_fwd(q, k, v, dst, lse, b, s, h, d, scale, causal, st);
+  return attn::generic_fwd<__nv_bfloat16>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, st);
+}
+
+MGB_EXPORT size_t mograd_b200_flash_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype) {
+  if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return 0;
+  size_t n = delta_bytes(B, S, H);
+  if (dtype == MGB_BF16 && (D == 64 || D == 128)) n += dq_acc_bytes(B, S, H, D);
+  return n;
+}
+
+MGB_EXPORT int mograd_b200_flash_attn_bwd(const void* dy, const void* o, const void* q, const void* k, const void* v,
+                                          const void* mask, const float* lse, void* dq, void* dk, void* dv, int64_t B,
+                                          int64_t S, int64_t H, int64_t D, float scale, int causal, int has_bias,
+                                          int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  MGB_REQUIRE(dy && o && q && k && v && lse && dq && dk && dv, MGB_EINVAL, "flash_attn_bwd: NULL argument");
+  MGB_REQUIRE(!has_bias || mask, MGB_EINVAL, "flash_attn_bwd: has_bias set but mask is NULL");
+  int rc = check_attn("flash_attn_bwd", B, S, H, D, causal, has_bias, dtype);
+  if (rc != MGB_OK) return rc;
+  const size_t need = mograd_b200_flash_attn_bwd_workspace_bytes(B, S, H, D, dtype);
+  MGB_REQUIRE(workspace && workspace_bytes >= need, MGB_EWORKSPACE,
+              "flash_attn_bwd: workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int b = static_cast<int>(B), s = static_cast<int>(S), h = static_cast<int>(H), d = static_cast<int>(D);
+  float* delta = static_cast<float*>(workspace);
+  const int64_t rows = B * H * S;
+  if (dtype == MGB_F32) {
+    rc = attn::launch_delta<float>(o, dy, delta, rows, d, st);
+    if (rc != MGB_OK) return rc;
+    return attn::generic_bwd<float>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal, has_bias, st);
+  }
+  rc = attn::launch_delta<__nv_bfloat16>(o, dy, delta, rows, d, st);
+  if (rc != MGB_OK) return rc;
+  const void* ptrs[] = {dy, q, k, v, dq, dk, dv};
+  if (attn::tc_supported(d, has_bias, ptrs, 7)) {
+    float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes(B, S, H));
+    return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, dq, dk, dv, b, s, h, d, scale, causal, st);
+  }
+  return attn::generic_bwd<__nv_bfloat16>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal,
+                                          has_bias, st);
 }

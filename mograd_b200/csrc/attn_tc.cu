@@ -1,0 +1,717 @@
+// Flash-attention forward and backward on the tcgen05 tensor cores
+// (bf16 storage, fp32 accumulation in TMEM, D = 64 or 128, causal or full).
+//
+// Tiles are 128 query rows x 128 key rows.  Q / K / V / dO tiles are brought
+// in by TMA as [128 rows][D] bf16 with the 128-byte swizzle (one 16 KB box per
+// 64 columns); the same shared-memory tile serves as a K-major operand
+// (contraction over D) and as an MN-major operand (contraction over rows), so
+// nothing is transposed.  The TMEM accumulator puts score row r in lane r, so
+// the thread that owns lane r sees a whole row: softmax statistics need no
+// shuffles.
+//
+// Backward, per CTA = one key tile j of one (batch, head), looping over query
+// tiles i (i >= j when causal; tiles above the diagonal are skipped):
+//     S  = Q_i K_j^T          dP = dO_i V_j^T              (tensor cores -> TMEM)
+//     P  = exp2(S*scale*log2e - lse*log2e),  dS = P*(dP - delta)*scale
+//                                                          (8 warps, TMEM -> bf16 in shared)
+//     dV += P^T dO_i          dK += dS^T Q_i               (accumulate in TMEM over i)
+//     dQ_i partial = dS K_j   -> fp32 vector reductions into the dQ accumulator
+// dK / dV leave TMEM once per CTA; dQ is converted to bf16 by a last kernel.
+// TMEM columns: S 128 | dP 128 | dV D | dK D | dQ D (D = 128: dQ reuses S).
+//
+// Forward, per CTA = one query tile: S_j = Q K_j^T double-buffered in TMEM so
+// the next tile's scores are computed while 4 softmax warps work on this one;
+// P goes to shared memory as bf16, O += P V_j accumulates in TMEM and is
+// rescaled in place when a row maximum moves.
+#include <math.h>
+
+#include "attn.cuh"
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace mgb {
+namespace attn {
+namespace {
+
+using namespace sm100;
+using bf16 = __nv_bfloat16;
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kHalfBytes = 128 * 128;  // [128 rows][64 bf16] box
+constexpr int kPsBytes = 128 * 128 * 2;
+
+enum : int { kErrBwdTma = 201, kErrBwdMma = 202, kErrBwdCompute = 203, kErrFwdTma = 211, kErrFwdMma = 212, kErrFwdSoftmax = 213 };
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// K-major slice k (16 contraction elements) of a [128][cols] swizzled tile.
+__device__ __forceinline__ uint64_t desc_k(uint32_t tile, int k) {
+  return smem_desc_sw128(tile + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
+}
+// MN-major slice k (16 contraction rows) of a [128 rows][cols] swizzled tile.
+__device__ __forceinline__ uint64_t desc_mn(uint32_t tile, int k) {
+  return smem_desc_sw128(tile + k * 2048, kHalfBytes, 1024);
+}
+// Byte offset of the 16-byte chunk holding columns [c8*8, c8*8+8) of row r in a [128][128] bf16 swizzled tile.
+__device__ __forceinline__ uint32_t ps_chunk_off(int r, int c8) {
+  return (c8 >> 3) * kHalfBytes + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
+}
+
+struct AttnParams {
+  const float* lse;
+  const float* delta;
+  float* dq_acc;
+  bf16* dk;
+  bf16* dv;
+  bf16* out;
+  float* lse_out;
+  int B, S, H;
+  float scale;
+  int causal;
+  int* status;
+};
+
+// ============================================================== backward
+template <int D>
+struct BwdCfg {
+  static constexpr int HALVES = D / 64;
+  static constexpr int TILE_BYTES = 128 * D * 2;
+  static constexpr int QSTAGES = (D == 64) ? 2 : 1;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE_BYTES;
+  static constexpr int OFF_Q = 2 * TILE_BYTES;
+  static constexpr int OFF_DO = OFF_Q + QSTAGES * TILE_BYTES;
+  static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;
+  static constexpr int OFF_DS = OFF_P + kPsBytes;
+  static constexpr int OFF_BAR = OFF_DS + kPsBytes;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
+  static constexpr int COL_DQ = (D == 64) ? 384 : 0;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int THREADS = 320;
+};
+
+template <int D>
+__global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
+    attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                       const AttnParams p) {
+  using C = BwdCfg<D>;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
+  const uint32_t bar = base + C::OFF_BAR;
+  const uint32_t bar_kv = bar, bar_sdp = bar + 8, bar_pds = bar + 16, bar_dqf = bar + 24, bar_dqd = bar + 32;
+  auto bar_qf = [&](int s) { return bar + 40 + 8u * s; };
+  auto bar_qe = [&](int s) { return bar + 56 + 8u * s; };
+  const uint32_t tmem_slot = bar + 72;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 72);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x;  // key tile
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int nq = (p.S + 127) / 128;
+  const int i0 = p.causal ? j : 0;
+  const int iters = nq - i0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_sdp, 1);
+    mbar_init(bar_pds, 8);
+    mbar_init(bar_dqf, 1);
+    mbar_init(bar_dqd, 8);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_qf(s), 1);
+      mbar_init(bar_qe(s), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      mbar_expect_tx(bar_kv, 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::HALVES; ++c) {
+        tma_load_4d(base + C::OFF_K + c * kHalfBytes, &tm_k, bar_kv, c * 64, h, j * 128, b);
+        tma_load_4d(base + C::OFF_V + c * kHalfBytes, &tm_v, bar_kv, c * 64, h, j * 128, b);
+      }
+      for (int it = 0; it < iters; ++it) {
+        const int s = it % C::QSTAGES;
+        const uint32_t ph = (it / C::QSTAGES) & 1u;
+        if (!mbar_wait(bar_qe(s), ph ^ 1u)) {
+          atomicExch(p.status, kErrBwdTma);
+          break;
+        }
+        const int i = i0 + it;
+        mbar_expect_tx(bar_qf(s), 2 * C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::HALVES; ++c) {
+          tma_load_4d(base + C::OFF_Q + s * C::TILE_BYTES + c * kHalfBytes, &tm_q, bar_qf(s), c * 64, h, i * 128, b);
+          tma_load_3d(base + C::OFF_DO + s * C::TILE_BYTES + c * kHalfBytes, &tm_do, bar_qf(s), c * 64, i * 128, bh);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA
+    if (lane == 0) {
+      constexpr uint32_t id_ss = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t id_mm = umma_idesc_bf16(128, D, 1, 1);
+      constexpr uint32_t id_km = umma_idesc_bf16(128, D, 0, 1);
+      const uint32_t sK = base + C::OFF_K, sV = base + C::OFF_V, sP = base + C::OFF_P, sDS = base + C::OFF_DS;
+      bool ok = mbar_wait(bar_kv, 0);
+      if (!ok) atomicExch(p.status, kErrBwdMma);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it % C::QSTAGES;
+        const uint32_t ph = (it / C::QSTAGES) & 1u;
+        const uint32_t sQ = base + C::OFF_Q + s * C::TILE_BYTES, sDO = base + C::OFF_DO + s * C::TILE_BYTES;
+        ok = mbar_wait(bar_qf(s), ph);
+        if (ok && D == 128 && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ lives in the S columns
+        if (!ok) {
+          atomicExch(p.status, kErrBwdMma);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S, desc_k(sQ, k), desc_k(sK, k), id_ss, k > 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_DP, desc_k(sDO, k), desc_k(sV, k), id_ss, k > 0);
+        umma_commit(bar_sdp);
+        if (!mbar_wait(bar_pds, it & 1u)) {
+          atomicExch(p.status, kErrBwdMma);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DV, desc_mn(sP, k), desc_mn(sDO, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DK, desc_mn(sDS, k), desc_mn(sQ, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar_qe(s));
+        if (D == 64 && it > 0) {
+          if (!mbar_wait(bar_dqd, (it - 1) & 1u)) {
+            atomicExch(p.status, kErrBwdMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_DQ, desc_k(sDS, k), desc_mn(sK, k), id_km, k > 0);
+        umma_commit(bar_dqf);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ compute
+    const int cw = warp - 2;
+    const int quarter = warp & 3;
+    const int ch = cw >> 2;  // which 64-column half of S / dP this warp handles
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const float scale_log2 = p.scale * kLog2e;
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      const int i = i0 + it;
+      const int qrow = i * 128 + r;
+      const bool vq = qrow < p.S;
+      const float lse2 = vq ? p.lse[static_cast<int64_t>(bh) * p.S + qrow] * kLog2e : 0.f;
+      const float dlt = vq ? p.delta[static_cast<int64_t>(bh) * p.S + qrow] : 0.f;
+      if (!mbar_wait(bar_sdp, it & 1u)) {
+        if (lane == 0) atomicExch(p.status, kErrBwdCompute);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool diag = p.causal && (i == j);
+#pragma unroll 1
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        const int col0 = ch * 64 + c0;
+        uint32_t s[32], dp[32];
+        tmem_ld32(tmem + lane_base + C::COL_S + col0, s);
+        tmem_ld32(tmem + lane_base + C::COL_DP + col0, dp);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kvrow = j * 128 + col0 + e + u;
+            const bool keep = vq && kvrow < p.S && (!diag || kvrow <= qrow);
+            const float pe = keep ? ex2(fmaf(__uint_as_float(s[e + u]), scale_log2, -lse2)) : 0.f;
+            pv[u] = pe;
+            dv[u] = pe * (__uint_as_float(dp[e + u]) - dlt) * p.scale;
+          }
+          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+          dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const uint32_t off = ps_chunk_off(r, (col0 >> 3) + t);
+          *reinterpret_cast<uint4*>(gen + C::OFF_P + off) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+          *reinterpret_cast<uint4*>(gen + C::OFF_DS + off) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pds);
+      // drain this tile's dQ contribution
+      if (!mbar_wait(bar_dqf, it & 1u)) {
+        if (lane == 0) atomicExch(p.status, kErrBwdCompute);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float* dq_row = p.dq_acc + ((static_cast<int64_t>(b) * p.S + (vq ? qrow : 0)) * p.H + h) * D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        const int dcol = ch * (D / 2) + c0;
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + C::COL_DQ + dcol, v);
+        tmem_ld_wait();
+        if (vq) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            red_add_v4(dq_row + dcol + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                       __uint_as_float(v[e + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_dqd);
+    }
+    // dK / dV: every MMA was complete when the last bar_dqf fired
+    if (ok) {
+      const int kvrow = j * 128 + r;
+      if (iters > 0) {
+        bf16* dk_row = p.dk + ((static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0)) * p.H + h) * D;
+        bf16* dv_row = p.dv + ((static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0)) * p.H + h) * D;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+          const int dcol = ch * (D / 2) + c0;
+          uint32_t a[32], c[32];
+          tmem_ld32(tmem + lane_base + C::COL_DK + dcol, a);
+          tmem_ld32(tmem + lane_base + C::COL_DV + dcol, c);
+          tmem_ld_wait();
+          if (kvrow < p.S) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 o1, o2;
+              o1.x = pack_bf16x2(__uint_as_float(a[e]), __uint_as_float(a[e + 1]));
+              o1.y = pack_bf16x2(__uint_as_float(a[e + 2]), __uint_as_float(a[e + 3]));
+              o1.z = pack_bf16x2(__uint_as_float(a[e + 4]), __uint_as_float(a[e + 5]));
+              o1.w = pack_bf16x2(__uint_as_float(a[e + 6]), __uint_as_float(a[e + 7]));
+              o2.x = pack_bf16x2(__uint_as_float(c[e]), __uint_as_float(c[e + 1]));
+              o2.y = pack_bf16x2(__uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
+              o2.z = pack_bf16x2(__uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
+              o2.w = pack_bf16x2(__uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
+              *reinterpret_cast<uint4*>(dk_row + dcol + e) = o1;
+              *reinterpret_cast<uint4*>(dv_row + dcol + e) = o2;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+__global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < n8; i += stride) {
+    const float4 a = reinterpret_cast<const float4*>(acc)[2 * i];
+    const float4 c = reinterpret_cast<const float4*>(acc)[2 * i + 1];
+    uint4 o;
+    o.x = pack_bf16x2(a.x, a.y);
+    o.y = pack_bf16x2(a.z, a.w);
+    o.z = pack_bf16x2(c.x, c.y);
+    o.w = pack_bf16x2(c.z, c.w);
+    reinterpret_cast<uint4*>(dq)[i] = o;
+  }
+}
+
+// =============================================================== forward
+template <int D>
+struct FwdCfg {
+  static constexpr int HALVES = D / 64;
+  static constexpr int TILE_BYTES = 128 * D * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = TILE_BYTES;       // 2 stages
+  static constexpr int OFF_V = 3 * TILE_BYTES;   // 2 stages
+  static constexpr int OFF_P = 5 * TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_P + kPsBytes;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int COL_S = 0;    // two buffers of 128 columns
+  static constexpr int COL_O = 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int THREADS = 192;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
+    attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  using C = FwdCfg<D>;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
+  const uint32_t bar = base + C::OFF_BAR;
+  const uint32_t bar_q = bar;
+  auto bar_kf = [&](int s) { return bar + 8 + 8u * s; };
+  auto bar_ke = [&](int s) { return bar + 24 + 8u * s; };
+  auto bar_vf = [&](int s) { return bar + 40 + 8u * s; };
+  auto bar_ve = [&](int s) { return bar + 56 + 8u * s; };
+  auto bar_sf = [&](int s) { return bar + 72 + 8u * s; };   // S buffer full
+  auto bar_sr = [&](int s) { return bar + 88 + 8u * s; };   // S buffer read (free)
+  const uint32_t bar_pr = bar + 104;                        // P written (and O rescaled)
+  const uint32_t bar_pv = bar + 112;                        // O += P V complete
+  const uint32_t tmem_slot = bar + 120;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 120);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.S + 127) / 128;
+  const int i = nq - 1 - static_cast<int>(blockIdx.x);  // heavy (late) query tiles first
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int nkv = p.causal ? i + 1 : nq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_kf(s), 1);
+      mbar_init(bar_ke(s), 1);
+      mbar_init(bar_vf(s), 1);
+      mbar_init(bar_ve(s), 1);
+      mbar_init(bar_sf(s), 1);
+      mbar_init(bar_sr(s), 4);
+    }
+    mbar_init(bar_pr, 4);
+    mbar_init(bar_pv, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_gen;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(bar_q, C::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::HALVES; ++c) tma_load_4d(base + C::OFF_Q + c * kHalfBytes, &tm_q, bar_q, c * 64, h, i * 128, b);
+      for (int jt = 0; jt < nkv; ++jt) {
+        const int s = jt & 1;
+        const uint32_t ph = (jt >> 1) & 1u;
+        if (!mbar_wait(bar_ke(s), ph ^ 1u)) {
+          atomicExch(p.status, kErrFwdTma);
+          break;
+        }
+        mbar_expect_tx(bar_kf(s), C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::HALVES; ++c)
+          tma_load_4d(base + C::OFF_K + s * C::TILE_BYTES + c * kHalfBytes, &tm_k, bar_kf(s), c * 64, h, jt * 128, b);
+        if (!mbar_wait(bar_ve(s), ph ^ 1u)) {
+          atomicExch(p.status, kErrFwdTma);
+          break;
+        }
+        mbar_expect_tx(bar_vf(s), C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::HALVES; ++c)
+          tma_load_4d(base + C::OFF_V + s * C::TILE_BYTES + c * kHalfBytes, &tm_v, bar_vf(s), c * 64, h, jt * 128, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
+      const uint32_t sQ = base + C::OFF_Q, sP = base + C::OFF_P;
+      auto issue_s = [&](int jt) -> bool {
+        const int s = jt & 1;
+        const uint32_t ph = (jt >> 1) & 1u;
+        if (!mbar_wait(bar_kf(s), ph)) return false;
+        if (jt >= 2 && !mbar_wait(bar_sr(s), ((jt - 2) >> 1) & 1u)) return false;
+        tc_fence_after();
+        const uint32_t sK = base + C::OFF_K + s * C::TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S + s * 128, desc_k(sQ, k), desc_k(sK, k), id_s, k > 0);
+        umma_commit(bar_ke(s));
+        umma_commit(bar_sf(s));
+        return true;
+      };
+      bool ok = mbar_wait(bar_q, 0) && issue_s(0);
+      for (int jt = 0; jt < nkv && ok; ++jt) {
+        if (jt + 1 < nkv) ok = issue_s(jt + 1);
+        const int s = jt & 1;
+        const uint32_t ph = (jt >> 1) & 1u;
+        ok = ok && mbar_wait(bar_pr, jt & 1u) && mbar_wait(bar_vf(s), ph);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sV = base + C::OFF_V + s * C::TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_O, desc_k(sP, k), desc_mn(sV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar_ve(s));
+        umma_commit(bar_pv);
+      }
+      if (!ok) atomicExch(p.status, kErrFwdMma);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const int qrow = i * 128 + r;
+    const float scale_log2 = p.scale * kLog2e;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int jt = 0; jt < nkv && ok; ++jt) {
+      const int s = jt & 1;
+      if (!mbar_wait(bar_sf(s), (jt >> 1) & 1u)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool diag = p.causal && (jt == i);
+      const int kv0 = jt * 128;
+      // pass 1: row maximum of the kept entries
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + C::COL_S + s * 128 + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int kvrow = kv0 + c0 + e;
+          const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
+          mx = fmaxf(mx, keep ? __uint_as_float(v[e]) : -INFINITY);
+        }
+      }
+      const float m_new = fmaxf(m, mx * scale_log2);
+      const float corr = (m == -INFINITY) ? 0.f : ex2(m - m_new);
+      // the previous P V product must be complete before P is overwritten or O rescaled
+      if (jt > 0 && !mbar_wait(bar_pv, (jt - 1) & 1u)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (jt > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+          tmem_st16(tmem + lane_base + C::COL_O + c0, o);
+        }
+        tmem_st_wait();
+      }
+      // pass 2: P = exp2(S*scale*log2e - m_new) -> bf16 in shared memory
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + C::COL_S + s * 128 + c0, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kvrow = kv0 + c0 + e + u;
+            const bool keep = kvrow < p.S && (!diag || kvrow <= qrow) && m_new != -INFINITY;
+            pv[u] = keep ? ex2(fmaf(__uint_as_float(v[e + u]), scale_log2, -m_new)) : 0.f;
+            rs += pv[u];
+          }
+          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          *reinterpret_cast<uint4*>(gen + C::OFF_P + ps_chunk_off(r, (c0 >> 3) + t)) =
+              make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+      }
+      l = l * corr + rs;
+      m = m_new;
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar_sr(s));
+        mbar_arrive(bar_pr);
+      }
+    }
+    if (ok && !mbar_wait(bar_pv, (nkv - 1) & 1u)) ok = false;
+    if (!ok) {
+      if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
+    } else {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* orow = p.out + (static_cast<int64_t>(bh) * p.S + (qrow < p.S ? qrow : 0)) * D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_base + C::COL_O + c0, v);
+        tmem_ld_wait();
+        if (qrow < p.S) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + e) = o;
+          }
+        }
+      }
+      if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host
+bool map_bshd(CUtensorMap* m, const void* ptr, int B, int S, int H, int D) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
+                            static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(H) * D * 2,
+                               static_cast<uint64_t>(S) * H * D * 2};
+  const uint32_t box[4] = {64, 1, 128, 1};
+  return encode_tmap_bf16(m, ptr, 4, dims, strides, box);
+}
+bool map_bhsd(CUtensorMap* m, const void* ptr, int B, int S, int H, int D) {
+  const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(S), static_cast<uint64_t>(B) * H};
+  const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(S) * D * 2};
+  const uint32_t box[3] = {64, 128, 1};
+  return encode_tmap_bf16(m, ptr, 3, dims, strides, box);
+}
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return fail(MGB_ECUDA, "attention smem opt-in (%d B): %s", bytes, cudaGetErrorString(e));
+  return MGB_OK;
+}
+
+template <int D>
+int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnParams p, cudaStream_t st) {
+  using C = BwdCfg<D>;
+  CUtensorMap mq, mk, mv, mdo;
+  if (!map_bshd(&mq, q, p.B, p.S, p.H, D) || !map_bshd(&mk, k, p.B, p.S, p.H, D) ||
+      !map_bshd(&mv, v, p.B, p.S, p.H, D) || !map_bhsd(&mdo, dy, p.B, p.S, p.H, D))
+    return MGB_ECUDA;
+  auto kern = attn_bwd_tc_kernel<D>;
+  int rc = set_smem(kern, C::SMEM);
+  if (rc != MGB_OK) return rc;
+  dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
+  kern<<<grid, C::THREADS, C::SMEM, st>>>(mq, mk, mv, mdo, p);
+  return check_launch("attn_bwd_tc_kernel");
+}
+
+template <int D>
+int run_fwd(const void* q, const void* k, const void* v, AttnParams p, cudaStream_t st) {
+  using C = FwdCfg<D>;
+  CUtensorMap mq, mk, mv;
+  if (!map_bshd(&mq, q, p.B, p.S, p.H, D) || !map_bshd(&mk, k, p.B, p.S, p.H, D) || !map_bshd(&mv, v, p.B, p.S, p.H, D))
+    return MGB_ECUDA;
+  auto kern = attn_fwd_tc_kernel<D>;
+  int rc = set_smem(kern, C::SMEM);
+  if (rc != MGB_OK) return rc;
+  dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
+  kern<<<grid, C::THREADS, C::SMEM, st>>>(mq, mk, mv, p);
+  return check_launch("attn_fwd_tc_kernel");
+}
+
+}  // namespace
+
+bool tc_supported(int D, int has_bias, const void* const* ptrs, int nptrs) {
+  if (has_bias || (D != 64 && D != 128)) return false;
+  for (int i = 0; i < nptrs; ++i)
+    if (!aligned16(ptrs[i])) return false;
+  return true;
+}
+
+int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, int B, int S, int H, int D, float scale,
+           int causal, cudaStream_t st) {
+  AttnParams p{};
+  p.out = static_cast<bf16*>(dst);
+  p.lse_out = lse;
+  p.B = B, p.S = S, p.H = H, p.scale = scale, p.causal = causal;
+  p.status = device_status_ptr();
+  if (!p.status) return fail(MGB_ECUDA, "flash_attn_fwd: device status word unavailable");
+  MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_fwd: B*H=%d exceeds 65535", B * H);
+  return D == 64 ? run_fwd<64>(q, k, v, p, st) : run_fwd<128>(q, k, v, p, st);
+}
+
+int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
+           float* dq_acc, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale, int causal,
+           cudaStream_t st) {
+  AttnParams p{};
+  p.lse = lse;
+  p.delta = delta;
+  p.dq_acc = dq_acc;
+  p.dk = static_cast<bf16*>(dk);
+  p.dv = static_cast<bf16*>(dv);
+  p.B = B, p.S = S, p.H = H, p.scale = scale, p.causal = causal;
+  p.status = device_status_ptr();
+  if (!p.status) return fail(MGB_ECUDA, "flash_attn_bwd: device status word unavailable");
+  MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_bwd: B*H=%d exceeds 65535", B * H);
+  const int64_t n = static_cast<int64_t>(B) * S * H * D;
+  const cudaError_t e = cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n) * sizeof(float), st);
+  if (e != cudaSuccess) return fail(MGB_ECUDA, "flash_attn_bwd: memset of the dQ accumulator: %s", cudaGetErrorString(e));
+  int rc = D == 64 ? run_bwd<64>(dy, q, k, v, p, st) : run_bwd<128>(dy, q, k, v, p, st);
+  if (rc != MGB_OK) return rc;
+  const int64_t n8 = n / 8;
+  int grid = static_cast<int>((n8 + 255) / 256);
+  if (grid > sm_count() * 8) grid = sm_count() * 8;
+  cast_dq_kernel<<<grid, 256, 0, st>>>(dq_acc, static_cast<bf16*>(dq), n8);
+  return check_launch("cast_dq_kernel");
+}
+
+}  // namespace attn
+}  // namespace mgb
