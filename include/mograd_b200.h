@@ -211,6 +211,55 @@ int mograd_b200_flash_attn_bwd(const void* dy, const void* o, const void* q, con
                                int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Extended forms.  Same kernels and arithmetic as the entry points above with
+ * extra operands that fold a neighbouring elementwise node of the reference's
+ * graph into the kernel, or describe a non-default memory layout.  They have
+ * no single counterpart in the reference: each note names the separate
+ * reference launches it absorbs.  The plain entry points call these with the
+ * extra operands NULL / default.
+ * ---------------------------------------------------------------------- */
+
+/* Y = act(A W^T + bias) + residual.  residual (M x N, row stride ldr, may be
+ * NULL, may alias y) absorbs the mograd_add of a residual connection
+ * (examples/tinyshakespear/model.mojo:64-66). */
+int mograd_b200_matmul_bias_bt_ex(const void* a, const void* w, const void* bias, const void* residual, void* y,
+                                  int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldr, int64_t ldy,
+                                  int act, int dtype, void* stream);
+
+/* dX = ((dY W) where relu_y > 0 else 0) + dx_residual.  relu_y (M x K: the
+ * ReLU output that produced X, may be NULL) absorbs mograd_relu_grad
+ * (mograd/grad.mojo:130-131); dx_residual (M x K, may be NULL, may alias dx)
+ * absorbs the mograd_add that accumulates gradients reaching the same tensor
+ * (accum, mograd/grad.mojo:93-95).  dW and db as in matmul_bias_bt_bwd. */
+int mograd_b200_matmul_bias_bt_bwd_ex(const void* dy, const void* x, const void* w, const void* relu_y,
+                                      const void* dx_residual, void* dx, void* dw, void* db, int64_t M, int64_t N,
+                                      int64_t K, int64_t lddy, int64_t ldx, int64_t ldw, int64_t ld_relu_y,
+                                      int64_t ld_dx_residual, int64_t lddx, int64_t lddw, int dtype, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
+/* dx = layer_norm_bwd(...) + dx_residual (rows x cols, may be NULL, may alias
+ * dx): absorbs the mograd_add of the residual branch's gradient. */
+int mograd_b200_layer_norm_bwd_ex(const void* dy, const void* x, const void* gamma, const void* dx_residual, void* dx,
+                                  void* dgamma, void* dbeta, int64_t rows, int64_t cols, float eps, int dtype,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* Attention with explicit layouts.  ld_qkv / ld_dqkv: elements between
+ * consecutive tokens of Q, K, V / dQ, dK, dV (H*D when each tensor is packed;
+ * 3*H*D when they are the three column blocks of one fused projection
+ * output).  o_layout: 0 = O and dO are BHSD as in the reference, 1 = BSHD,
+ * which absorbs the reference's transpose(1,2)+contiguous copies around the
+ * attention node (examples/tinyshakespear/model.mojo:100-108,
+ * mograd/grad.mojo:336-339). */
+int mograd_b200_flash_attn_fwd_ex(const void* q, const void* k, const void* v, const void* mask, void* dst, float* lse,
+                                  int64_t B, int64_t S, int64_t H, int64_t D, float scale, int causal, int has_bias,
+                                  int64_t ld_qkv, int o_layout, int dtype, void* stream);
+int mograd_b200_flash_attn_bwd_ex(const void* dy, const void* o, const void* q, const void* k, const void* v,
+                                  const void* mask, const float* lse, void* dq, void* dk, void* dv, int64_t B,
+                                  int64_t S, int64_t H, int64_t D, float scale, int causal, int has_bias,
+                                  int64_t ld_qkv, int64_t ld_dqkv, int o_layout, int dtype, void* workspace,
+                                  size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
  * Callers of the hot path inside a train step (elementwise, one pass each).
  * ---------------------------------------------------------------------- */
 

@@ -53,6 +53,15 @@ SIGNATURES = {
     "mograd_b200_flash_attn_bwd_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),
     "mograd_b200_flash_attn_bwd": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32,
                                           _int, _int, _int, _p, _sz, _p]),
+    "mograd_b200_matmul_bias_bt_ex": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int,
+                                             _p]),
+    "mograd_b200_matmul_bias_bt_bwd_ex": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
+                                                 _i64, _i64, _i64, _i64, _int, _p, _sz, _p]),
+    "mograd_b200_layer_norm_bwd_ex": (_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _int, _p, _sz, _p]),
+    "mograd_b200_flash_attn_fwd_ex": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32, _int, _int, _i64,
+                                             _int, _int, _p]),
+    "mograd_b200_flash_attn_bwd_ex": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32,
+                                             _int, _int, _i64, _i64, _int, _int, _p, _sz, _p]),
     "mograd_b200_relu_grad": (_int, [_p, _p, _p, _i64, _int, _p]),
     "mograd_b200_add": (_int, [_p, _p, _p, _i64, _int, _p]),
     "mograd_b200_gather_rows": (_int, [_p, _p, _p, _i64, _i64, _i64, _int, _p]),

@@ -27,11 +27,18 @@ struct GArgs {
   int B, S, H, D;
   float scale;
   int causal, has_bias;
+  int64_t ld_qkv;   // elements between consecutive tokens of q / k / v (H*D when packed)
+  int64_t ld_dqkv;  // same for dq / dk / dv
+  int o_bshd;       // 0: O and dO are (B,H,S,D); 1: (B,S,H,D)
 };
 
 template <typename T>
-__device__ __forceinline__ const T* row_bshd(const T* p, int b, int s, int h, int S, int H, int D) {
-  return p + ((static_cast<int64_t>(b) * S + s) * H + h) * D;
+__device__ __forceinline__ const T* row_bshd(const T* p, int b, int s, int h, int S, int64_t ld, int D) {
+  return p + (static_cast<int64_t>(b) * S + s) * ld + static_cast<int64_t>(h) * D;
+}
+// element offset of row (b, h, s) of O / dO
+__device__ __forceinline__ int64_t o_row_off(int o_bshd, int b, int h, int s, int S, int H, int D) {
+  return o_bshd ? ((static_cast<int64_t>(b) * S + s) * H + h) * D : ((static_cast<int64_t>(b) * H + h) * S + s) * D;
 }
 
 // dot(q_row (shared, fp32), k_row (global))
@@ -54,7 +61,7 @@ __global__ void __launch_bounds__(kWarps * 32) generic_fwd_kernel(const GArgs<T>
   const int bh = static_cast<int>(row / a.S);
   const int b = bh / a.H, h = bh % a.H;
   float* qs = smem + warp * a.D;
-  const T* qr = row_bshd(a.q, b, i, h, a.S, a.H, a.D);
+  const T* qr = row_bshd(a.q, b, i, h, a.S, a.ld_qkv, a.D);
   for (int d = lane; d < a.D; d += 32) qs[d] = to_f32(qr[d]);
   __syncwarp();
   float acc[kMaxDPerLane];
@@ -66,7 +73,7 @@ __global__ void __launch_bounds__(kWarps * 32) generic_fwd_kernel(const GArgs<T>
     const int j = j0 + lane;
     float s = -INFINITY;
     if (j < j_end) {
-      s = dot_row(qs, row_bshd(a.k, b, j, h, a.S, a.H, a.D), a.D) * a.scale;
+      s = dot_row(qs, row_bshd(a.k, b, j, h, a.S, a.ld_qkv, a.D), a.D) * a.scale;
       if (a.has_bias) s += to_f32(a.mask[(static_cast<int64_t>(bh) * a.S + i) * a.S + j]);
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -79,7 +86,7 @@ __global__ void __launch_bounds__(kWarps * 32) generic_fwd_kernel(const GArgs<T>
     for (int u = 0; u < kMaxDPerLane; ++u) acc[u] *= corr;
     for (int jj = 0; jj < cnt; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const T* vr = row_bshd(a.v, b, j0 + jj, h, a.S, a.H, a.D);
+      const T* vr = row_bshd(a.v, b, j0 + jj, h, a.S, a.ld_qkv, a.D);
 #pragma unroll
       for (int u = 0; u < kMaxDPerLane; ++u) {
         const int d = lane + 32 * u;
@@ -88,7 +95,7 @@ __global__ void __launch_bounds__(kWarps * 32) generic_fwd_kernel(const GArgs<T>
     }
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
-  T* orow = a.out + row * a.D;  // BHSD
+  T* orow = a.out + o_row_off(a.o_bshd, b, h, i, a.S, a.H, a.D);
 #pragma unroll
   for (int u = 0; u < kMaxDPerLane; ++u) {
     const int d = lane + 32 * u;
@@ -110,8 +117,8 @@ __global__ void __launch_bounds__(kWarps * 32) generic_dq_kernel(const GArgs<T> 
   const int b = bh / a.H, h = bh % a.H;
   float* qs = smem + warp * 2 * a.D;
   float* dos = qs + a.D;
-  const T* qr = row_bshd(a.q, b, i, h, a.S, a.H, a.D);
-  const T* dor = a.dy + row * a.D;
+  const T* qr = row_bshd(a.q, b, i, h, a.S, a.ld_qkv, a.D);
+  const T* dor = a.dy + o_row_off(a.o_bshd, b, h, i, a.S, a.H, a.D);
   for (int d = lane; d < a.D; d += 32) {
     qs[d] = to_f32(qr[d]);
     dos[d] = to_f32(dor[d]);
@@ -126,16 +133,16 @@ __global__ void __launch_bounds__(kWarps * 32) generic_dq_kernel(const GArgs<T> 
     const int j = j0 + lane;
     float ds = 0.f;
     if (j < j_end) {
-      float s = dot_row(qs, row_bshd(a.k, b, j, h, a.S, a.H, a.D), a.D) * a.scale;
+      float s = dot_row(qs, row_bshd(a.k, b, j, h, a.S, a.ld_qkv, a.D), a.D) * a.scale;
       if (a.has_bias) s += to_f32(a.mask[(static_cast<int64_t>(bh) * a.S + i) * a.S + j]);
       const float p = expf(s - lse);
-      const float dp = dot_row(dos, row_bshd(a.v, b, j, h, a.S, a.H, a.D), a.D);
+      const float dp = dot_row(dos, row_bshd(a.v, b, j, h, a.S, a.ld_qkv, a.D), a.D);
       ds = p * (dp - delta) * a.scale;
     }
     const int cnt = min(32, j_end - j0);
     for (int jj = 0; jj < cnt; ++jj) {
       const float w = __shfl_sync(0xffffffffu, ds, jj);
-      const T* kr = row_bshd(a.k, b, j0 + jj, h, a.S, a.H, a.D);
+      const T* kr = row_bshd(a.k, b, j0 + jj, h, a.S, a.ld_qkv, a.D);
 #pragma unroll
       for (int u = 0; u < kMaxDPerLane; ++u) {
         const int d = lane + 32 * u;
@@ -143,7 +150,7 @@ __global__ void __launch_bounds__(kWarps * 32) generic_dq_kernel(const GArgs<T> 
       }
     }
   }
-  T* dqr = a.dq + ((static_cast<int64_t>(b) * a.S + i) * a.H + h) * a.D;
+  T* dqr = a.dq + (static_cast<int64_t>(b) * a.S + i) * a.ld_dqkv + static_cast<int64_t>(h) * a.D;
 #pragma unroll
   for (int u = 0; u < kMaxDPerLane; ++u) {
     const int d = lane + 32 * u;
@@ -164,8 +171,8 @@ __global__ void __launch_bounds__(kWarps * 32) generic_dkdv_kernel(const GArgs<T
   const int b = bh / a.H, h = bh % a.H;
   float* ks = smem + warp * 2 * a.D;
   float* vs = ks + a.D;
-  const T* kr = row_bshd(a.k, b, j, h, a.S, a.H, a.D);
-  const T* vr = row_bshd(a.v, b, j, h, a.S, a.H, a.D);
+  const T* kr = row_bshd(a.k, b, j, h, a.S, a.ld_qkv, a.D);
+  const T* vr = row_bshd(a.v, b, j, h, a.S, a.ld_qkv, a.D);
   for (int d = lane; d < a.D; d += 32) {
     ks[d] = to_f32(kr[d]);
     vs[d] = to_f32(vr[d]);
@@ -180,18 +187,18 @@ __global__ void __launch_bounds__(kWarps * 32) generic_dkdv_kernel(const GArgs<T
     float p = 0.f, ds = 0.f;
     if (i < a.S) {
       const int64_t qrow = static_cast<int64_t>(bh) * a.S + i;
-      float s = dot_row(ks, row_bshd(a.q, b, i, h, a.S, a.H, a.D), a.D) * a.scale;
+      float s = dot_row(ks, row_bshd(a.q, b, i, h, a.S, a.ld_qkv, a.D), a.D) * a.scale;
       if (a.has_bias) s += to_f32(a.mask[qrow * a.S + j]);
       p = expf(s - a.lse[qrow]);
-      const float dp = dot_row(vs, a.dy + qrow * a.D, a.D);
+      const float dp = dot_row(vs, a.dy + o_row_off(a.o_bshd, b, h, i, a.S, a.H, a.D), a.D);
       ds = p * (dp - a.delta[qrow]) * a.scale;
     }
     const int cnt = min(32, a.S - i0);
     for (int ii = 0; ii < cnt; ++ii) {
       const float pw = __shfl_sync(0xffffffffu, p, ii);
       const float dw = __shfl_sync(0xffffffffu, ds, ii);
-      const T* qr = row_bshd(a.q, b, i0 + ii, h, a.S, a.H, a.D);
-      const T* dor = a.dy + (static_cast<int64_t>(bh) * a.S + i0 + ii) * a.D;
+      const T* qr = row_bshd(a.q, b, i0 + ii, h, a.S, a.ld_qkv, a.D);
+      const T* dor = a.dy + o_row_off(a.o_bshd, b, h, i0 + ii, a.S, a.H, a.D);
 #pragma unroll
       for (int u = 0; u < kMaxDPerLane; ++u) {
         const int d = lane + 32 * u;
@@ -202,8 +209,8 @@ __global__ void __launch_bounds__(kWarps * 32) generic_dkdv_kernel(const GArgs<T
       }
     }
   }
-  T* dkr = a.dk + ((static_cast<int64_t>(b) * a.S + j) * a.H + h) * a.D;
-  T* dvr = a.dv + ((static_cast<int64_t>(b) * a.S + j) * a.H + h) * a.D;
+  T* dkr = a.dk + (static_cast<int64_t>(b) * a.S + j) * a.ld_dqkv + static_cast<int64_t>(h) * a.D;
+  T* dvr = a.dv + (static_cast<int64_t>(b) * a.S + j) * a.ld_dqkv + static_cast<int64_t>(h) * a.D;
 #pragma unroll
   for (int u = 0; u < kMaxDPerLane; ++u) {
     const int d = lane + 32 * u;
@@ -217,12 +224,16 @@ __global__ void __launch_bounds__(kWarps * 32) generic_dkdv_kernel(const GArgs<T
 // ---- delta[row] = sum_d O[row,d] * dO[row,d]   (both BHSD); warp per row
 template <typename T>
 __global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ o, const T* __restrict__ dy,
-                                                    float* __restrict__ delta, int64_t rows, int D) {
+                                                    float* __restrict__ delta, int64_t rows, int S, int H, int D,
+                                                    int o_bshd) {
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);  // (b, h, s) order
   if (row >= rows) return;
-  const T* orow = o + row * D;
-  const T* drow = dy + row * D;
+  const int s = static_cast<int>(row % S);
+  const int bh = static_cast<int>(row / S);
+  const int64_t off = o_row_off(o_bshd, bh / H, bh % H, s, S, H, D);
+  const T* orow = o + off;
+  const T* drow = dy + off;
   float acc = 0.f;
   for (int d = lane; d < D; d += 32) acc = fmaf(to_f32(orow[d]), to_f32(drow[d]), acc);
   acc = warp_sum(acc);
@@ -232,17 +243,19 @@ __global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ o, con
 }  // namespace
 
 template <typename T>
-int launch_delta(const void* o, const void* dy, float* delta, int64_t rows, int D, cudaStream_t st) {
+int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, cudaStream_t st) {
+  const int64_t rows = static_cast<int64_t>(B) * H * S;
   delta_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(o),
-                                                                       static_cast<const T*>(dy), delta, rows, D);
+                                                                       static_cast<const T*>(dy), delta, rows, S, H, D,
+                                                                       o_bshd);
   return check_launch("delta_kernel");
 }
-template int launch_delta<float>(const void*, const void*, float*, int64_t, int, cudaStream_t);
-template int launch_delta<__nv_bfloat16>(const void*, const void*, float*, int64_t, int, cudaStream_t);
+template int launch_delta<float>(const void*, const void*, float*, int, int, int, int, int, cudaStream_t);
+template int launch_delta<__nv_bfloat16>(const void*, const void*, float*, int, int, int, int, int, cudaStream_t);
 
 template <typename T>
 int generic_fwd(const void* q, const void* k, const void* v, const void* mask, void* dst, float* lse, int B, int S,
-                int H, int D, float scale, int causal, int has_bias, cudaStream_t st) {
+                int H, int D, float scale, int causal, int has_bias, const Layouts& lay, cudaStream_t st) {
   GArgs<T> a{};
   a.q = static_cast<const T*>(q);
   a.k = static_cast<const T*>(k);
@@ -251,20 +264,21 @@ int generic_fwd(const void* q, const void* k, const void* v, const void* mask, v
   a.out = static_cast<T*>(dst);
   a.lse_out = lse;
   a.B = B, a.S = S, a.H = H, a.D = D, a.scale = scale, a.causal = causal, a.has_bias = has_bias;
+  a.ld_qkv = lay.ld_qkv, a.ld_dqkv = lay.ld_dqkv, a.o_bshd = lay.o_bshd;
   const int64_t rows = static_cast<int64_t>(B) * H * S;
   generic_fwd_kernel<T><<<static_cast<unsigned>((rows + kWarps - 1) / kWarps), kWarps * 32,
                           kWarps * D * sizeof(float), st>>>(a);
   return check_launch("generic_fwd_kernel");
 }
 template int generic_fwd<float>(const void*, const void*, const void*, const void*, void*, float*, int, int, int, int,
-                                float, int, int, cudaStream_t);
+                                float, int, int, const Layouts&, cudaStream_t);
 template int generic_fwd<__nv_bfloat16>(const void*, const void*, const void*, const void*, void*, float*, int, int,
-                                        int, int, float, int, int, cudaStream_t);
+                                        int, int, float, int, int, const Layouts&, cudaStream_t);
 
 template <typename T>
 int generic_bwd(const void* dy, const void* q, const void* k, const void* v, const void* mask, const float* lse,
                 const float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale, int causal,
-                int has_bias, cudaStream_t st) {
+                int has_bias, const Layouts& lay, cudaStream_t st) {
   GArgs<T> a{};
   a.q = static_cast<const T*>(q);
   a.k = static_cast<const T*>(k);
@@ -277,6 +291,7 @@ int generic_bwd(const void* dy, const void* q, const void* k, const void* v, con
   a.dk = static_cast<T*>(dk);
   a.dv = static_cast<T*>(dv);
   a.B = B, a.S = S, a.H = H, a.D = D, a.scale = scale, a.causal = causal, a.has_bias = has_bias;
+  a.ld_qkv = lay.ld_qkv, a.ld_dqkv = lay.ld_dqkv, a.o_bshd = lay.o_bshd;
   const int64_t rows = static_cast<int64_t>(B) * H * S;
   const unsigned grid = static_cast<unsigned>((rows + kWarps - 1) / kWarps);
   const size_t smem = kWarps * 2 * D * sizeof(float);
@@ -287,10 +302,11 @@ int generic_bwd(const void* dy, const void* q, const void* k, const void* v, con
   return check_launch("generic_dkdv_kernel");
 }
 template int generic_bwd<float>(const void*, const void*, const void*, const void*, const void*, const float*,
-                                const float*, void*, void*, void*, int, int, int, int, float, int, int, cudaStream_t);
+                                const float*, void*, void*, void*, int, int, int, int, float, int, int, const Layouts&,
+                                cudaStream_t);
 template int generic_bwd<__nv_bfloat16>(const void*, const void*, const void*, const void*, const void*, const float*,
                                         const float*, void*, void*, void*, int, int, int, int, float, int, int,
-                                        cudaStream_t);
+                                        const Layouts&, cudaStream_t);
 
 }  // namespace attn
 }  // namespace mgb

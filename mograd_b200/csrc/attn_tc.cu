@@ -75,6 +75,8 @@ struct AttnParams {
   int B, S, H;
   float scale;
   int causal;
+  int64_t ld_dqkv;  // elements between consecutive tokens of dK / dV
+  int o_bshd;       // layout of O (forward output)
   int* status;
 };
 
@@ -168,7 +170,10 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
 #pragma unroll
         for (int c = 0; c < C::HALVES; ++c) {
           tma_load_4d(base + C::OFF_Q + s * C::TILE_BYTES + c * kHalfBytes, &tm_q, bar_qf(s), c * 64, h, i * 128, b);
-          tma_load_3d(base + C::OFF_DO + s * C::TILE_BYTES + c * kHalfBytes, &tm_do, bar_qf(s), c * 64, i * 128, bh);
+          if (p.o_bshd)
+            tma_load_4d(base + C::OFF_DO + s * C::TILE_BYTES + c * kHalfBytes, &tm_do, bar_qf(s), c * 64, h, i * 128, b);
+          else
+            tma_load_3d(base + C::OFF_DO + s * C::TILE_BYTES + c * kHalfBytes, &tm_do, bar_qf(s), c * 64, i * 128, bh);
         }
       }
     }
@@ -309,8 +314,9 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     if (ok) {
       const int kvrow = j * 128 + r;
       if (iters > 0) {
-        bf16* dk_row = p.dk + ((static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0)) * p.H + h) * D;
-        bf16* dv_row = p.dv + ((static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0)) * p.H + h) * D;
+        const int64_t tok = static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0);
+        bf16* dk_row = p.dk + tok * p.ld_dqkv + static_cast<int64_t>(h) * D;
+        bf16* dv_row = p.dv + tok * p.ld_dqkv + static_cast<int64_t>(h) * D;
 #pragma unroll 1
         for (int c0 = 0; c0 < D / 2; c0 += 32) {
           const int dcol = ch * (D / 2) + c0;
@@ -346,9 +352,13 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   }
 }
 
-__global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8) {
+// acc is packed (tokens x HD) fp32; dq rows are ld elements apart.
+__global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8,
+                                                      int hd8, int64_t ld) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < n8; i += stride) {
+    const int64_t tok = i / hd8;
+    const int c8 = static_cast<int>(i - tok * hd8);
     const float4 a = reinterpret_cast<const float4*>(acc)[2 * i];
     const float4 c = reinterpret_cast<const float4*>(acc)[2 * i + 1];
     uint4 o;
@@ -356,7 +366,7 @@ __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ 
     o.y = pack_bf16x2(a.z, a.w);
     o.z = pack_bf16x2(c.x, c.y);
     o.w = pack_bf16x2(c.z, c.w);
-    reinterpret_cast<uint4*>(dq)[i] = o;
+    *reinterpret_cast<uint4*>(dq + tok * ld + c8 * 8) = o;
   }
 }
 
@@ -586,7 +596,9 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
     } else {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* orow = p.out + (static_cast<int64_t>(bh) * p.S + (qrow < p.S ? qrow : 0)) * D;
+      const int qr = qrow < p.S ? qrow : 0;
+      bf16* orow = p.out + (p.o_bshd ? ((static_cast<int64_t>(b) * p.S + qr) * p.H + h) * D
+                                     : (static_cast<int64_t>(bh) * p.S + qr) * D);
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t v[32];
@@ -616,11 +628,11 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
 }
 
 // ------------------------------------------------------------------ host
-bool map_bshd(CUtensorMap* m, const void* ptr, int B, int S, int H, int D) {
+bool map_bshd(CUtensorMap* m, const void* ptr, int B, int S, int H, int D, int64_t ld) {
   const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
                             static_cast<uint64_t>(B)};
-  const uint64_t strides[3] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(H) * D * 2,
-                               static_cast<uint64_t>(S) * H * D * 2};
+  const uint64_t strides[3] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(ld) * 2,
+                               static_cast<uint64_t>(S) * ld * 2};
   const uint32_t box[4] = {64, 1, 128, 1};
   return encode_tmap_bf16(m, ptr, 4, dims, strides, box);
 }
@@ -639,11 +651,15 @@ int set_smem(K kern, int bytes) {
 }
 
 template <int D>
-int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnParams p, cudaStream_t st) {
+int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv,
+            cudaStream_t st) {
   using C = BwdCfg<D>;
   CUtensorMap mq, mk, mv, mdo;
-  if (!map_bshd(&mq, q, p.B, p.S, p.H, D) || !map_bshd(&mk, k, p.B, p.S, p.H, D) ||
-      !map_bshd(&mv, v, p.B, p.S, p.H, D) || !map_bhsd(&mdo, dy, p.B, p.S, p.H, D))
+  if (!map_bshd(&mq, q, p.B, p.S, p.H, D, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, D, ld_qkv) ||
+      !map_bshd(&mv, v, p.B, p.S, p.H, D, ld_qkv))
+    return MGB_ECUDA;
+  if (!(p.o_bshd ? map_bshd(&mdo, dy, p.B, p.S, p.H, D, static_cast<int64_t>(p.H) * D)
+                 : map_bhsd(&mdo, dy, p.B, p.S, p.H, D)))
     return MGB_ECUDA;
   auto kern = attn_bwd_tc_kernel<D>;
   int rc = set_smem(kern, C::SMEM);
@@ -654,10 +670,11 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
 }
 
 template <int D>
-int run_fwd(const void* q, const void* k, const void* v, AttnParams p, cudaStream_t st) {
+int run_fwd(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
   using C = FwdCfg<D>;
   CUtensorMap mq, mk, mv;
-  if (!map_bshd(&mq, q, p.B, p.S, p.H, D) || !map_bshd(&mk, k, p.B, p.S, p.H, D) || !map_bshd(&mv, v, p.B, p.S, p.H, D))
+  if (!map_bshd(&mq, q, p.B, p.S, p.H, D, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, D, ld_qkv) ||
+      !map_bshd(&mv, v, p.B, p.S, p.H, D, ld_qkv))
     return MGB_ECUDA;
   auto kern = attn_fwd_tc_kernel<D>;
   int rc = set_smem(kern, C::SMEM);
@@ -669,28 +686,30 @@ int run_fwd(const void* q, const void* k, const void* v, AttnParams p, cudaStrea
 
 }  // namespace
 
-bool tc_supported(int D, int has_bias, const void* const* ptrs, int nptrs) {
+bool tc_supported(int D, int has_bias, const Layouts& lay, const void* const* ptrs, int nptrs) {
   if (has_bias || (D != 64 && D != 128)) return false;
+  if (lay.ld_qkv % 8 != 0 || lay.ld_dqkv % 8 != 0) return false;
   for (int i = 0; i < nptrs; ++i)
     if (!aligned16(ptrs[i])) return false;
   return true;
 }
 
 int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, int B, int S, int H, int D, float scale,
-           int causal, cudaStream_t st) {
+           int causal, const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
   p.out = static_cast<bf16*>(dst);
   p.lse_out = lse;
   p.B = B, p.S = S, p.H = H, p.scale = scale, p.causal = causal;
+  p.o_bshd = lay.o_bshd;
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_fwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_fwd: B*H=%d exceeds 65535", B * H);
-  return D == 64 ? run_fwd<64>(q, k, v, p, st) : run_fwd<128>(q, k, v, p, st);
+  return D == 64 ? run_fwd<64>(q, k, v, p, lay.ld_qkv, st) : run_fwd<128>(q, k, v, p, lay.ld_qkv, st);
 }
 
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
            float* dq_acc, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale, int causal,
-           cudaStream_t st) {
+           const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
   p.lse = lse;
   p.delta = delta;
@@ -698,18 +717,20 @@ int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const fl
   p.dk = static_cast<bf16*>(dk);
   p.dv = static_cast<bf16*>(dv);
   p.B = B, p.S = S, p.H = H, p.scale = scale, p.causal = causal;
+  p.ld_dqkv = lay.ld_dqkv;
+  p.o_bshd = lay.o_bshd;
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_bwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_bwd: B*H=%d exceeds 65535", B * H);
   const int64_t n = static_cast<int64_t>(B) * S * H * D;
   const cudaError_t e = cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n) * sizeof(float), st);
   if (e != cudaSuccess) return fail(MGB_ECUDA, "flash_attn_bwd: memset of the dQ accumulator: %s", cudaGetErrorString(e));
-  int rc = D == 64 ? run_bwd<64>(dy, q, k, v, p, st) : run_bwd<128>(dy, q, k, v, p, st);
+  int rc = D == 64 ? run_bwd<64>(dy, q, k, v, p, lay.ld_qkv, st) : run_bwd<128>(dy, q, k, v, p, lay.ld_qkv, st);
   if (rc != MGB_OK) return rc;
   const int64_t n8 = n / 8;
   int grid = static_cast<int>((n8 + 255) / 256);
   if (grid > sm_count() * 8) grid = sm_count() * 8;
-  cast_dq_kernel<<<grid, 256, 0, st>>>(dq_acc, static_cast<bf16*>(dq), n8);
+  cast_dq_kernel<<<grid, 256, 0, st>>>(dq_acc, static_cast<bf16*>(dq), n8, H * D / 8, lay.ld_dqkv);
   return check_launch("cast_dq_kernel");
 }
 

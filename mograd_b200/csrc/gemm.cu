@@ -31,7 +31,7 @@ using bf16 = __nv_bfloat16;
 constexpr int BM = 128;
 constexpr int BK = 64;     // bf16 elements per stage along the contraction = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-9 column sums of A (db)
 constexpr int kMaxSplits = 16;
 
 enum : int { kErrTmaWait = 101, kErrMmaWait = 102, kErrEpiWait = 103 };
@@ -56,6 +56,11 @@ struct GemmParams {
   float* partial;              // [splits][M][N] when splits > 1
   const bf16* bias;            // length N or nullptr (splits == 1 only)
   int act;                     // 1 = ReLU
+  const bf16* relu_mask;       // optional M x N: output zeroed where mask <= 0 (ReLU backward), splits == 1 only
+  int64_t ldm;
+  const bf16* residual;        // optional M x N added last (may alias d), splits == 1 only
+  int64_t ldr;
+  float* rowsum_partial;       // optional [splits][M]: sum over the contraction of A(i, :) (db inside the dW GEMM)
   int* status;
 };
 
@@ -81,7 +86,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < T::STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(empty_bar(s), (A_MN && p.rowsum_partial) ? 5 : 1);  // MMA commit (+ the four row-sum warps)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
@@ -193,6 +198,50 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ------------------------------------------- row sums of A (bias gradient)
+    // Only used with an MN-major A (dW = dY^T X, A = dY): every stage's A tile
+    // is [BK rows of the contraction][128 output rows], so the sum over the
+    // contraction of output row t is a column sum of the tile in shared memory.
+    if (A_MN && p.rowsum_partial) {
+      const int t = threadIdx.x - 6 * 32;  // 0..127: output row within the tile
+      const uint32_t col_off = (t >> 6) * (64 * BK * 2);
+      const int chunk = (t & 63) >> 3, elem = t & 7;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int split = tile / tiles_mn;
+        const int rem = tile - split * tiles_mn;
+        const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+        float acc = 0.f;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            atomicExch(p.status, kErrEpiWait);
+            ok = false;
+            break;
+          }
+          if (n_blk == 0) {
+            const unsigned char* tile_a = smem_gen + stage * T::STAGE_BYTES + col_off;
+#pragma unroll 8
+            for (int rr = 0; rr < BK; ++rr) {
+              const bf16 v = *reinterpret_cast<const bf16*>(tile_a + rr * 128 + ((chunk ^ (rr & 7)) << 4) + elem * 2);
+              acc += __bfloat162float(v);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty_bar(stage));
+          if (++stage == T::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        const int row = m_blk * BM + t;
+        if (ok && n_blk == 0 && row < p.M) p.rowsum_partial[static_cast<int64_t>(split) * p.M + row] = acc;
+      }
+    }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
@@ -242,6 +291,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (p.act == 1) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+            if (p.relu_mask) {
+              const bf16* mk = p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0;
+              if (col0 + 32 <= p.N && (p.ldm & 7) == 0 && (reinterpret_cast<uintptr_t>(p.relu_mask) & 15u) == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  float mv[8];
+                  load_vec(mk + j, mv);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[j + e] = mv[e] > 0.f ? v[j + e] : 0.f;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) v[j] = __bfloat162float(mk[j]) > 0.f ? v[j] : 0.f;
+              }
+            }
+            if (p.residual) {
+              const bf16* rs = p.residual + static_cast<int64_t>(row) * p.ldr + col0;
+              if (col0 + 32 <= p.N && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  float rv[8];
+                  load_vec(rs + j, rv);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[j + e] += rv[e];
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
+              }
             }
             bf16* dst = p.d + static_cast<int64_t>(row) * p.ldd + col0;
             if (col0 + 32 <= p.N && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) {
@@ -293,12 +374,23 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// db[i] = sum_s rowsum_partial[s][i], fixed order.
+__global__ void __launch_bounds__(256)
+    rowsum_finalize_kernel(const float* __restrict__ partial, int splits, int M, bf16* __restrict__ out) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= M) return;
+  float acc = 0.f;
+  for (int s = 0; s < splits; ++s) acc += partial[static_cast<int64_t>(s) * M + i];
+  out[i] = __float2bfloat16_rn(acc);
+}
+
 // ------------------------------------------------------- CUDA-core fallback
 // D[i,j] = sum_l A[i*sai + l*sal] * B[j*sbj + l*sbl] (+ bias[j], ReLU), fp32 accumulation.
 template <typename T>
 __global__ void __launch_bounds__(256)
-    gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ bias, T* __restrict__ d,
-                     int M, int N, int K, int64_t sai, int64_t sal, int64_t sbj, int64_t sbl, int64_t ldd, int act) {
+    gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ bias, T* d, int M, int N,
+                     int K, int64_t sai, int64_t sal, int64_t sbj, int64_t sbl, int64_t ldd, int act,
+                     const T* __restrict__ relu_mask, int64_t ldm, const T* residual, int64_t ldr) {
   constexpr int TM = 64, TN = 64, TK = 16;
   __shared__ float As[TK][TM + 1];
   __shared__ float Bs[TK][TN + 1];
@@ -358,6 +450,8 @@ __global__ void __launch_bounds__(256)
       float r = acc[u][v];
       if (bias) r += to_f32(bias[gj]);
       if (act == 1) r = fmaxf(r, 0.f);
+      if (relu_mask && !(to_f32(relu_mask[static_cast<int64_t>(gi) * ldm + gj]) > 0.f)) r = 0.f;
+      if (residual) r += to_f32(residual[static_cast<int64_t>(gi) * ldr + gj]);
       d[static_cast<int64_t>(gi) * ldd + gj] = from_f32<T>(r);
     }
   }
@@ -391,6 +485,16 @@ struct Operand {
   int64_t ld;     // row stride in elements
 };
 
+// What happens to the accumulator on its way out: (+ bias) -> ReLU -> ReLU-backward mask -> + residual.
+struct Epilogue {
+  const void* bias = nullptr;
+  int act = 0;
+  const void* relu_mask = nullptr;
+  int64_t ldm = 0;
+  const void* residual = nullptr;
+  int64_t ldr = 0;
+};
+
 bool tma_ok(const Operand& o) { return aligned16(o.ptr) && (o.ld % 8 == 0) && o.ld >= o.cols; }
 
 // Map over a row-major bf16 matrix; box = box_cols x box_rows.
@@ -404,6 +508,7 @@ bool make_map(CUtensorMap* m, const Operand& o, uint32_t box_cols, uint32_t box_
 size_t splitk_bytes(int64_t M, int64_t N, int splits) {
   return splits > 1 ? round_up(static_cast<size_t>(splits) * M * N * sizeof(float), 256) : 0;
 }
+size_t rowsum_bytes(int64_t M) { return round_up(static_cast<size_t>(kMaxSplits) * M * sizeof(float), 256); }
 
 // Split the contraction when the output has too few tiles to fill the GPU.
 int choose_splits(int64_t M, int64_t N, int64_t K, int BN) {
@@ -443,9 +548,10 @@ int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st)
 }
 
 // D[M,N] = A . B^T style product on tensor cores; operands described as they lie in memory.
+// rowsum_out (A_MN only): bf16[M] = sum over the contraction of A(i, :), produced inside the same kernel.
 template <bool A_MN, bool B_MN>
-int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const bf16* bias, int act, int64_t M, int64_t N,
-            int64_t K, void* ws, size_t ws_bytes, bool allow_split, cudaStream_t st) {
+int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epilogue& ep, bf16* rowsum_out, int64_t M,
+            int64_t N, int64_t K, void* ws, size_t ws_bytes, bool allow_split, cudaStream_t st) {
   const int BN = choose_bn(N);
   GemmParams p{};
   p.M = static_cast<int>(M);
@@ -454,15 +560,27 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const bf16
   p.num_m = static_cast<int>((M + BM - 1) / BM);
   p.num_n = static_cast<int>((N + BN - 1) / BN);
   p.num_kb = static_cast<int>((K + BK - 1) / BK);
-  p.splits = allow_split ? choose_splits(M, N, K, BN) : 1;
-  if (p.splits > 1 && (!ws || ws_bytes < splitk_bytes(M, N, p.splits))) p.splits = 1;
+  const bool plain = !ep.relu_mask && !ep.residual;
+  p.splits = (allow_split && plain) ? choose_splits(M, N, K, BN) : 1;
+  size_t ws_used = 0;
+  if (rowsum_out) {  // the row-sum partials sit at the start of the workspace
+    if (!ws || ws_bytes < rowsum_bytes(M)) return fail(MGB_EWORKSPACE, "gemm: workspace too small for the bias gradient");
+    p.rowsum_partial = static_cast<float*>(ws);
+    ws_used = rowsum_bytes(M);
+  }
+  if (p.splits > 1 && (!ws || ws_bytes < ws_used + splitk_bytes(M, N, p.splits))) p.splits = 1;
   p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
   p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
   p.d = d;
   p.ldd = ldd;
-  p.partial = static_cast<float*>(ws);
+  p.partial = reinterpret_cast<float*>(static_cast<char*>(ws) + ws_used);
+  const bf16* bias = static_cast<const bf16*>(ep.bias);
   p.bias = p.splits > 1 ? nullptr : bias;
-  p.act = p.splits > 1 ? 0 : act;
+  p.act = p.splits > 1 ? 0 : ep.act;
+  p.relu_mask = static_cast<const bf16*>(ep.relu_mask);
+  p.ldm = ep.ldm;
+  p.residual = static_cast<const bf16*>(ep.residual);
+  p.ldr = ep.ldr;
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "gemm: device status word unavailable");
   int rc = BN == 256 ? launch_tc<256, A_MN, B_MN>(a, b, p, st) : launch_tc<128, A_MN, B_MN>(a, b, p, st);
@@ -471,19 +589,26 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const bf16
     const int64_t total = M * N;
     int grid = static_cast<int>((total + 255) / 256);
     if (grid > sm_count() * 8) grid = sm_count() * 8;
-    splitk_finalize_kernel<<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, act);
+    splitk_finalize_kernel<<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
     rc = check_launch("splitk_finalize_kernel");
+    if (rc != MGB_OK) return rc;
+  }
+  if (rowsum_out) {
+    rowsum_finalize_kernel<<<(p.M + 255) / 256, 256, 0, st>>>(p.rowsum_partial, p.splits, p.M, rowsum_out);
+    rc = check_launch("rowsum_finalize_kernel");
   }
   return rc;
 }
 
 template <typename T>
-int gemm_simt(const T* a, const T* b, const T* bias, T* d, int64_t M, int64_t N, int64_t K, int64_t sai, int64_t sal,
-              int64_t sbj, int64_t sbl, int64_t ldd, int act, cudaStream_t st) {
+int gemm_simt(const T* a, const T* b, T* d, int64_t M, int64_t N, int64_t K, int64_t sai, int64_t sal, int64_t sbj,
+              int64_t sbl, int64_t ldd, const Epilogue& ep, cudaStream_t st) {
   dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
   MGB_REQUIRE(grid.y <= 65535, MGB_EUNSUPPORTED, "matmul: M=%lld too large for the CUDA-core kernel", (long long)M);
-  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a, b, bias, d, static_cast<int>(M), static_cast<int>(N),
-                                            static_cast<int>(K), sai, sal, sbj, sbl, ldd, act);
+  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a, b, static_cast<const T*>(ep.bias), d, static_cast<int>(M),
+                                            static_cast<int>(N), static_cast<int>(K), sai, sal, sbj, sbl, ldd, ep.act,
+                                            static_cast<const T*>(ep.relu_mask), ep.ldm,
+                                            static_cast<const T*>(ep.residual), ep.ldr);
   return check_launch("gemm_simt_kernel");
 }
 
@@ -495,74 +620,94 @@ int check_dims(const char* who, int64_t M, int64_t N, int64_t K) {
   return MGB_OK;
 }
 
+template <typename T>
+int colsum(const void* dy, void* db, int64_t M, int64_t N, int64_t ld, cudaStream_t st) {
+  colsum_kernel<T><<<static_cast<unsigned>((N + 31) / 32), 256, 0, st>>>(static_cast<const T*>(dy), static_cast<T*>(db),
+                                                                       static_cast<int>(M), static_cast<int>(N), ld);
+  return check_launch("colsum_kernel");
+}
+
 }  // namespace
 }  // namespace mgb
 
 using namespace mgb;
 
-MGB_EXPORT int mograd_b200_matmul_bias_bt(const void* a, const void* w, const void* bias, void* y, int64_t M,
-                                          int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldy, int act,
-                                          int dtype, void* stream) {
+MGB_EXPORT int mograd_b200_matmul_bias_bt_ex(const void* a, const void* w, const void* bias, const void* residual,
+                                             void* y, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw,
+                                             int64_t ldr, int64_t ldy, int act, int dtype, void* stream) {
   MGB_REQUIRE(a && w && y, MGB_EINVAL, "matmul_bias_bt: NULL argument");
   int rc = check_dims("matmul_bias_bt", M, N, K);
   if (rc != MGB_OK) return rc;
-  MGB_REQUIRE(lda >= K && ldw >= K && ldy >= N, MGB_EINVAL, "matmul_bias_bt: leading dimension too small");
+  MGB_REQUIRE(lda >= K && ldw >= K && ldy >= N && (!residual || ldr >= N), MGB_EINVAL,
+              "matmul_bias_bt: leading dimension too small");
   MGB_REQUIRE(act == 0 || act == 1, MGB_EINVAL, "matmul_bias_bt: act=%d (0 none, 1 relu)", act);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Epilogue ep;
+  ep.bias = bias;
+  ep.act = act;
+  ep.residual = residual;
+  ep.ldr = ldr;
   if (dtype == MGB_F32)
-    return gemm_simt<float>(static_cast<const float*>(a), static_cast<const float*>(w),
-                            static_cast<const float*>(bias), static_cast<float*>(y), M, N, K, lda, 1, ldw, 1, ldy, act,
-                            st);
+    return gemm_simt<float>(static_cast<const float*>(a), static_cast<const float*>(w), static_cast<float*>(y), M, N, K,
+                            lda, 1, ldw, 1, ldy, ep, st);
   MGB_REQUIRE(dtype == MGB_BF16, MGB_EDTYPE, "matmul_bias_bt: unsupported dtype code %d", dtype);
   const Operand oa{a, M, K, lda}, ow{w, N, K, ldw};
   if (tma_ok(oa) && tma_ok(ow))
-    return gemm_tc<false, false>(oa, ow, static_cast<bf16*>(y), ldy, static_cast<const bf16*>(bias), act, M, N, K,
-                                 nullptr, 0, false, st);
-  return gemm_simt<bf16>(static_cast<const bf16*>(a), static_cast<const bf16*>(w), static_cast<const bf16*>(bias),
-                         static_cast<bf16*>(y), M, N, K, lda, 1, ldw, 1, ldy, act, st);
+    return gemm_tc<false, false>(oa, ow, static_cast<bf16*>(y), ldy, ep, nullptr, M, N, K, nullptr, 0, false, st);
+  return gemm_simt<bf16>(static_cast<const bf16*>(a), static_cast<const bf16*>(w), static_cast<bf16*>(y), M, N, K, lda,
+                         1, ldw, 1, ldy, ep, st);
+}
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt(const void* a, const void* w, const void* bias, void* y, int64_t M,
+                                          int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldy, int act,
+                                          int dtype, void* stream) {
+  return mograd_b200_matmul_bias_bt_ex(a, w, bias, nullptr, y, M, N, K, lda, ldw, 0, ldy, act, dtype, stream);
 }
 
 MGB_EXPORT size_t mograd_b200_matmul_bias_bt_bwd_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
   if (dtype != MGB_BF16 || M <= 0 || N <= 0 || K <= 0) return 0;
-  // dW is N x K with contraction M; dX is M x K with contraction N (never split: M is the large dim).
-  const size_t dw = splitk_bytes(N, K, kMaxSplits);
-  return dw;
+  // dW is N x K with contraction M (may be split); db partials ride along.  dX (contraction N) is never split.
+  return rowsum_bytes(N) + splitk_bytes(N, K, kMaxSplits);
 }
 
-MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw,
-                                              void* db, int64_t M, int64_t N, int64_t K, int64_t lddy, int64_t ldx,
-                                              int64_t ldw, int64_t lddx, int64_t lddw, int dtype, void* workspace,
-                                              size_t workspace_bytes, void* stream) {
+MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd_ex(const void* dy, const void* x, const void* w, const void* relu_y,
+                                                 const void* dx_residual, void* dx, void* dw, void* db, int64_t M,
+                                                 int64_t N, int64_t K, int64_t lddy, int64_t ldx, int64_t ldw,
+                                                 int64_t ld_relu_y, int64_t ld_dx_residual, int64_t lddx,
+                                                 int64_t lddw, int dtype, void* workspace, size_t workspace_bytes,
+                                                 void* stream) {
   MGB_REQUIRE(dy, MGB_EINVAL, "matmul_bias_bt_bwd: dy is NULL");
   MGB_REQUIRE(dx || dw || db, MGB_EINVAL, "matmul_bias_bt_bwd: no output requested");
   MGB_REQUIRE(!dx || w, MGB_EINVAL, "matmul_bias_bt_bwd: dX needs W");
   MGB_REQUIRE(!dw || x, MGB_EINVAL, "matmul_bias_bt_bwd: dW needs X");
   int rc = check_dims("matmul_bias_bt_bwd", M, N, K);
   if (rc != MGB_OK) return rc;
-  MGB_REQUIRE(lddy >= N && (!dx || (ldw >= K && lddx >= K)) && (!dw || (ldx >= K && lddw >= K)), MGB_EINVAL,
-              "matmul_bias_bt_bwd: leading dimension too small");
+  MGB_REQUIRE(lddy >= N && (!dx || (ldw >= K && lddx >= K)) && (!dw || (ldx >= K && lddw >= K)) &&
+                  (!relu_y || ld_relu_y >= K) && (!dx_residual || ld_dx_residual >= K),
+              MGB_EINVAL, "matmul_bias_bt_bwd: leading dimension too small");
   MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32, MGB_EDTYPE, "matmul_bias_bt_bwd: unsupported dtype code %d", dtype);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Epilogue epx;  // dX = (dY W) masked by relu_y > 0, plus dx_residual
+  epx.relu_mask = relu_y;
+  epx.ldm = ld_relu_y;
+  epx.residual = dx_residual;
+  epx.ldr = ld_dx_residual;
+  const Epilogue none;
   if (dtype == MGB_F32) {
     const float* dyf = static_cast<const float*>(dy);
     if (dx) {
       // dX[m,k] = sum_n dY[m,n] W[n,k]: A = dY (i=m, l=n), B(j=k, l=n) = W[n*ldw + k]
-      rc = gemm_simt<float>(dyf, static_cast<const float*>(w), nullptr, static_cast<float*>(dx), M, K, N, lddy, 1, 1,
-                            ldw, lddx, 0, st);
+      rc = gemm_simt<float>(dyf, static_cast<const float*>(w), static_cast<float*>(dx), M, K, N, lddy, 1, 1, ldw, lddx,
+                            epx, st);
       if (rc != MGB_OK) return rc;
     }
     if (dw) {
       // dW[n,k] = sum_m dY[m,n] X[m,k]: A(i=n, l=m) = dY[m*lddy + n], B(j=k, l=m) = X[m*ldx + k]
-      rc = gemm_simt<float>(dyf, static_cast<const float*>(x), nullptr, static_cast<float*>(dw), N, K, M, 1, lddy, 1,
-                            ldx, lddw, 0, st);
+      rc = gemm_simt<float>(dyf, static_cast<const float*>(x), static_cast<float*>(dw), N, K, M, 1, lddy, 1, ldx, lddw,
+                            none, st);
       if (rc != MGB_OK) return rc;
     }
-    if (db) {
-      colsum_kernel<float><<<static_cast<unsigned>((N + 31) / 32), 256, 0, st>>>(dyf, static_cast<float*>(db),
-                                                                               static_cast<int>(M),
-                                                                               static_cast<int>(N), lddy);
-      rc = check_launch("colsum_kernel");
-    }
+    if (db) rc = colsum<float>(dy, db, M, N, lddy, st);
     return rc;
   }
   const bf16* dyb = static_cast<const bf16*>(dy);
@@ -570,27 +715,35 @@ MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd(const void* dy, const void* x, con
   if (dx) {
     const Operand ow{w, N, K, ldw};
     if (tma_ok(ody) && tma_ok(ow))
-      rc = gemm_tc<false, true>(ody, ow, static_cast<bf16*>(dx), lddx, nullptr, 0, M, K, N, nullptr, 0, false, st);
+      rc = gemm_tc<false, true>(ody, ow, static_cast<bf16*>(dx), lddx, epx, nullptr, M, K, N, nullptr, 0, false, st);
     else
-      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(w), nullptr, static_cast<bf16*>(dx), M, K, N, lddy, 1, 1, ldw,
-                           lddx, 0, st);
+      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(w), static_cast<bf16*>(dx), M, K, N, lddy, 1, 1, ldw, lddx,
+                           epx, st);
     if (rc != MGB_OK) return rc;
   }
+  bool db_done = false;
   if (dw) {
     const Operand ox{x, M, K, ldx};
-    if (tma_ok(ody) && tma_ok(ox))
-      rc = gemm_tc<true, true>(ody, ox, static_cast<bf16*>(dw), lddw, nullptr, 0, N, K, M, workspace, workspace_bytes,
-                               true, st);
-    else
-      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(x), nullptr, static_cast<bf16*>(dw), N, K, M, 1, lddy, 1, ldx,
-                           lddw, 0, st);
+    if (tma_ok(ody) && tma_ok(ox)) {
+      // db comes out of the same kernel when the workspace has room for its partial sums
+      bf16* db_fused = (db && workspace && workspace_bytes >= rowsum_bytes(N)) ? static_cast<bf16*>(db) : nullptr;
+      rc = gemm_tc<true, true>(ody, ox, static_cast<bf16*>(dw), lddw, none, db_fused, N, K, M, workspace,
+                               workspace_bytes, true, st);
+      db_done = db_fused != nullptr;
+    } else {
+      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(x), static_cast<bf16*>(dw), N, K, M, 1, lddy, 1, ldx, lddw,
+                           none, st);
+    }
     if (rc != MGB_OK) return rc;
   }
-  if (db) {
-    colsum_kernel<bf16><<<static_cast<unsigned>((N + 31) / 32), 256, 0, st>>>(dyb, static_cast<bf16*>(db),
-                                                                            static_cast<int>(M), static_cast<int>(N),
-                                                                            lddy);
-    rc = check_launch("colsum_kernel");
-  }
+  if (db && !db_done) rc = colsum<bf16>(dy, db, M, N, lddy, st);
   return rc;
+}
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw,
+                                              void* db, int64_t M, int64_t N, int64_t K, int64_t lddy, int64_t ldx,
+                                              int64_t ldw, int64_t lddx, int64_t lddw, int dtype, void* workspace,
+                                              size_t workspace_bytes, void* stream) {
+  return mograd_b200_matmul_bias_bt_bwd_ex(dy, x, w, nullptr, nullptr, dx, dw, db, M, N, K, lddy, ldx, ldw, 0, 0, lddx,
+                                           lddw, dtype, workspace, workspace_bytes, stream);
 }

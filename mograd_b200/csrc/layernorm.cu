@@ -178,8 +178,8 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
 
 template <typename T, int WPR, int CHUNKS, bool VEC>
 __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
-    ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
-                  T* __restrict__ dx, float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
+    ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid,
+                  T* dx, float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
   constexpr int V = Vec<T>::N;
   using S = Shape<WPR>;
   extern __shared__ float fold[];  // [2][cols]: dgamma then dbeta, folded over the CTA's teams
@@ -265,6 +265,12 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
           dg[j][e] = fmaf(d[e], xhat, dg[j][e]);
           db[j][e] += d[e];
         }
+        if (resid) {
+          float rv[V];
+          unpack<T>(load_chunk<T, VEC>(resid + row * cols, col, cols), rv);
+#pragma unroll
+          for (int e = 0; e < V; ++e) o[e] += rv[e];
+        }
         store_chunk<T, VEC>(dxr, col, cols, pack<T>(o));
       }
     }
@@ -285,6 +291,173 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
             } else {
               fold[col + e] += dg[j][e];
               fold[cols + col + e] += db[j][e];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* prow = part + static_cast<int64_t>(blockIdx.x) * 2 * cols;
+  for (int64_t c = threadIdx.x; c < 2 * cols; c += S::THREADS) prow[c] = fold[c];
+}
+
+// ---- pipelined variant for 16-byte-aligned rows --------------------------
+// Each warp keeps a ring of kLnStages row slots in shared memory and fills it
+// with cp.async (global -> shared without passing through registers), so up
+// to kLnStages - 1 rows of x and dy per warp are in flight while the current
+// row is being reduced.  A lane only ever reads back the 16-byte chunks it
+// copied itself, so the ring needs no barrier.  Registers hold just gamma and
+// the fp32 dgamma / dbeta partials.
+constexpr int kLnStages = 4;
+
+__device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T, int WPR, int CHUNKS>
+__global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
+    ln_bwd_pipe_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid,
+                       T* dx, float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
+  constexpr int V = Vec<T>::N;
+  using S = Shape<WPR>;
+  constexpr int SLOT = CHUNKS * 512;  // bytes of one array (x or dy) of one row slot of one warp
+  extern __shared__ __align__(16) unsigned char dsm[];
+  float* fold = reinterpret_cast<float*>(dsm);                       // [2][cols]
+  unsigned char* ring_base = dsm + ((2 * cols * sizeof(float) + 15) / 16) * 16;
+  __shared__ float redA[2 * S::WARPS];
+  __shared__ float redB[2 * S::WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int team = warp / WPR;
+  const int lt = (warp % WPR) * 32 + lane;
+  const float inv_n = 1.f / static_cast<float>(cols);
+  unsigned char* ring = ring_base + static_cast<size_t>(warp) * kLnStages * 2 * SLOT;
+  const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+
+  uint4 g_raw[CHUNKS];
+  float dg[CHUNKS][V], db[CHUNKS][V];
+  int64_t colj[CHUNKS];
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    colj[j] = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
+    g_raw[j] = load_chunk<T, true>(gamma, colj[j], cols);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      dg[j][e] = 0.f;
+      db[j][e] = 0.f;
+    }
+  }
+
+  const int64_t r_first = static_cast<int64_t>(blockIdx.x) * S::TEAMS + team;
+  const int64_t r_step = static_cast<int64_t>(gridDim.x) * S::TEAMS;
+  auto issue = [&](int64_t row, int slot) {
+    if (row < rows) {
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        if (colj[j] < cols) {
+          const uint32_t so = ring_s + slot * 2 * SLOT + (j * 32 + lane) * 16;
+          cp_async16(so, x + row * cols + colj[j]);
+          cp_async16(so + SLOT, dy + row * cols + colj[j]);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < kLnStages - 1; ++s) issue(r_first + s * r_step, s);
+
+  int slot = 0;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * S::TEAMS; r0 < rows; r0 += r_step) {
+    const int64_t row = r0 + team;
+    const bool live = row < rows;
+    // keep kLnStages - 1 rows in flight: refill the slot that was consumed in the previous iteration
+    issue(row + (kLnStages - 1) * r_step, (slot + kLnStages - 1) % kLnStages);
+    cp_async_wait<kLnStages - 1>();
+    const uint4* xs = reinterpret_cast<const uint4*>(ring + slot * 2 * SLOT);
+    const uint4* ds = reinterpret_cast<const uint4*>(ring + slot * 2 * SLOT + SLOT);
+    float sx = 0.f, sx2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      if (live && colj[j] < cols) {
+        float v[V];
+        unpack<T>(xs[j * 32 + lane], v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          sx += v[e];
+          sx2 = fmaf(v[e], v[e], sx2);
+        }
+      }
+    }
+    team_sum2<WPR>(sx, sx2, redA, warp, team, lane);
+    const float mu = sx * inv_n;
+    const float rs = rsqrtf(fmaxf(sx2 * inv_n - mu * mu, 0.f) + eps);
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      if (live && colj[j] < cols) {
+        float v[V], d[V], g[V];
+        unpack<T>(xs[j * 32 + lane], v);
+        unpack<T>(ds[j * 32 + lane], d);
+        unpack<T>(g_raw[j], g);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float dyg = d[e] * g[e];
+          c1 += dyg;
+          c2 = fmaf(dyg, (v[e] - mu) * rs, c2);
+        }
+      }
+    }
+    team_sum2<WPR>(c1, c2, redB, warp, team, lane);
+    c1 *= inv_n;
+    c2 *= inv_n;
+    if (live) {
+      T* dxr = dx + row * cols;
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        if (colj[j] < cols) {
+          float v[V], d[V], g[V], o[V];
+          unpack<T>(xs[j * 32 + lane], v);
+          unpack<T>(ds[j * 32 + lane], d);
+          unpack<T>(g_raw[j], g);
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const float xhat = (v[e] - mu) * rs;
+            o[e] = rs * (d[e] * g[e] - c1 - xhat * c2);
+            dg[j][e] = fmaf(d[e], xhat, dg[j][e]);
+            db[j][e] += d[e];
+          }
+          if (resid) {
+            float rv[V];
+            unpack<T>(*reinterpret_cast<const uint4*>(resid + row * cols + colj[j]), rv);
+#pragma unroll
+            for (int e = 0; e < V; ++e) o[e] += rv[e];
+          }
+          *reinterpret_cast<uint4*>(dxr + colj[j]) = pack<T>(o);
+        }
+      }
+    }
+    slot = (slot + 1) % kLnStages;
+  }
+  cp_async_wait<0>();
+
+  for (int t = 0; t < S::TEAMS; ++t) {
+    if (team == t) {
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          if (colj[j] + e < cols) {
+            if (t == 0) {
+              fold[colj[j] + e] = dg[j][e];
+              fold[cols + colj[j] + e] = db[j][e];
+            } else {
+              fold[colj[j] + e] += dg[j][e];
+              fold[cols + colj[j] + e] += db[j][e];
             }
           }
         }
@@ -354,18 +527,28 @@ int launch_fwd(const T* x, const T* g, const T* b, T* y, float* mean, float* rst
 }
 
 template <typename T, int WPR, int CHUNKS>
-int launch_bwd(const T* dy, const T* x, const T* g, T* dx, float* part, int64_t rows, int64_t cols, float eps,
-               bool vec, int grid, cudaStream_t st) {
+int launch_bwd(const T* dy, const T* x, const T* g, const T* resid, T* dx, float* part, int64_t rows, int64_t cols,
+               float eps, bool vec, int grid, cudaStream_t st) {
   constexpr int TH = Shape<WPR>::THREADS;
-  const size_t smem = static_cast<size_t>(2 * cols) * sizeof(float);
-  if (vec) {
-    auto k = ln_bwd_kernel<T, WPR, CHUNKS, true>;
+  const size_t fold_bytes = round_up(static_cast<size_t>(2 * cols) * sizeof(float), 16);
+  const size_t pipe_smem = fold_bytes + static_cast<size_t>(Shape<WPR>::WARPS) * kLnStages * 2 * CHUNKS * 512;
+  if (vec && pipe_smem + 1024 <= static_cast<size_t>(max_smem_optin())) {
+    const size_t smem = pipe_smem;
+    auto k = ln_bwd_pipe_kernel<T, WPR, CHUNKS>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    k<<<grid, TH, smem, st>>>(dy, x, g, dx, part, rows, cols, eps);
+    k<<<grid, TH, smem, st>>>(dy, x, g, resid, dx, part, rows, cols, eps);
+    return check_launch("ln_bwd_pipe_kernel");
+  }
+  if (vec) {  // very wide rows: the ring does not fit next to the fold buffer, keep the row in registers instead
+    auto k = ln_bwd_kernel<T, WPR, CHUNKS, true>;
+    if (fold_bytes > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fold_bytes));
+    k<<<grid, TH, fold_bytes, st>>>(dy, x, g, resid, dx, part, rows, cols, eps);
   } else {
     auto k = ln_bwd_kernel<T, WPR, CHUNKS, false>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    k<<<grid, TH, smem, st>>>(dy, x, g, dx, part, rows, cols, eps);
+    if (fold_bytes > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fold_bytes));
+    k<<<grid, TH, fold_bytes, st>>>(dy, x, g, resid, dx, part, rows, cols, eps);
   }
   return check_launch("ln_bwd_kernel");
 }
@@ -401,16 +584,17 @@ int ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* m
 }
 
 template <typename T>
-int ln_bwd_main(const void* dy, const void* x, const void* gamma, void* dx, float* part, int64_t rows,
-                int64_t cols, float eps, const Plan& pl, cudaStream_t st) {
-  const bool vec = (cols % Vec<T>::N == 0) && aligned16(x) && aligned16(gamma) && aligned16(dy) && aligned16(dx);
+int ln_bwd_main(const void* dy, const void* x, const void* gamma, const void* resid, void* dx, float* part,
+                int64_t rows, int64_t cols, float eps, const Plan& pl, cudaStream_t st) {
+  const bool vec = (cols % Vec<T>::N == 0) && aligned16(x) && aligned16(gamma) && aligned16(dy) && aligned16(dx) &&
+                   aligned16(resid);
   MGB_LN_DISPATCH(launch_bwd, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma),
-                  static_cast<T*>(dx), part, rows, cols, eps, vec, pl.grid, st)
+                  static_cast<const T*>(resid), static_cast<T*>(dx), part, rows, cols, eps, vec, pl.grid, st)
 }
 
 template <typename T>
-int ln_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dgamma, void* dbeta, int64_t rows,
-           int64_t cols, float eps, void* ws, size_t ws_bytes, cudaStream_t st) {
+int ln_bwd(const void* dy, const void* x, const void* gamma, const void* resid, void* dx, void* dgamma, void* dbeta,
+           int64_t rows, int64_t cols, float eps, void* ws, size_t ws_bytes, cudaStream_t st) {
   Plan pl;
   if (!make_plan<T>(rows, cols, pl))
     return fail(MGB_EUNSUPPORTED, "layer_norm_bwd: cols=%lld exceeds 16384", (long long)cols);
@@ -418,7 +602,7 @@ int ln_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dga
   MGB_REQUIRE(ws && ws_bytes >= need, MGB_EWORKSPACE, "layer_norm_bwd: workspace of %zu bytes needed, %zu given", need,
               ws ? ws_bytes : (size_t)0);
   float* part = static_cast<float*>(ws);
-  int rc = ln_bwd_main<T>(dy, x, gamma, dx, part, rows, cols, eps, pl, st);
+  int rc = ln_bwd_main<T>(dy, x, gamma, resid, dx, part, rows, cols, eps, pl, st);
   if (rc != MGB_OK) return rc;
   const unsigned fgrid = static_cast<unsigned>((2 * cols + kFinCols - 1) / kFinCols);
   ln_bwd_finalize_kernel<T><<<fgrid, kFinCols * kFinLanes, 0, st>>>(part, pl.grid, cols, static_cast<T*>(dgamma),
@@ -491,18 +675,33 @@ MGB_EXPORT size_t mograd_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int64
   return round_up(static_cast<size_t>(pl.grid) * 2 * cols * sizeof(float), 256);
 }
 
+MGB_EXPORT int mograd_b200_layer_norm_bwd_ex(const void* dy, const void* x, const void* gamma,
+                                             const void* dx_residual, void* dx, void* dgamma, void* dbeta,
+                                             int64_t rows, int64_t cols, float eps, int dtype, void* workspace,
+                                             size_t workspace_bytes, void* stream);
+
 MGB_EXPORT int mograd_b200_layer_norm_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dgamma,
                                           void* dbeta, int64_t rows, int64_t cols, float eps, int dtype,
                                           void* workspace, size_t workspace_bytes, void* stream) {
+  return mograd_b200_layer_norm_bwd_ex(dy, x, gamma, nullptr, dx, dgamma, dbeta, rows, cols, eps, dtype, workspace,
+                                       workspace_bytes, stream);
+}
+
+MGB_EXPORT int mograd_b200_layer_norm_bwd_ex(const void* dy, const void* x, const void* gamma,
+                                             const void* dx_residual, void* dx, void* dgamma, void* dbeta,
+                                             int64_t rows, int64_t cols, float eps, int dtype, void* workspace,
+                                             size_t workspace_bytes, void* stream) {
+  const void* resid = dx_residual;
   MGB_REQUIRE(dy && x && gamma && dx && dgamma && dbeta, MGB_EINVAL, "layer_norm_bwd: NULL argument");
   int rc = check_ln("layer_norm_bwd", rows, cols);
   if (rc != MGB_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case MGB_BF16:
-      return ln_bwd<__nv_bfloat16>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes, st);
+      return ln_bwd<__nv_bfloat16>(dy, x, gamma, resid, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes,
+                                   st);
     case MGB_F32:
-      return ln_bwd<float>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes, st);
+      return ln_bwd<float>(dy, x, gamma, resid, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes, st);
     default:
       return fail(MGB_EDTYPE, "layer_norm_bwd: unsupported dtype code %d", dtype);
   }
@@ -530,6 +729,6 @@ MGB_EXPORT int mograd_b200_layer_norm_bwd_static(const void* dy, const void* x, 
   if (rc != MGB_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == MGB_BF16)
-    return ln_bwd<__nv_bfloat16>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
-  return ln_bwd<float>(dy, x, gamma, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
+    return ln_bwd<__nv_bfloat16>(dy, x, gamma, nullptr, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
+  return ln_bwd<float>(dy, x, gamma, nullptr, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
 }

@@ -74,9 +74,9 @@ def _rows2d(t: torch.Tensor) -> tuple[int, int, int]:
 # ----------------------------------------------------------------------------
 # matmul_bias_bt (dispatch.mojo:247-278)
 # ----------------------------------------------------------------------------
-def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None):
-    """Y = A @ W.T (+ bias) (, ReLU): exec rule `matmul_bias_bt` / `matmul_bt`."""
-    _require_cuda(a, w, bias)
+def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None, residual=None):
+    """Y = A @ W.T (+ bias) (, ReLU) (+ residual): exec rule `matmul_bias_bt` / `matmul_bt`."""
+    _require_cuda(a, w, bias, residual)
     M, K, lda = _rows2d(a)
     N, K2, ldw = _rows2d(w)
     if K2 != K:
@@ -84,14 +84,17 @@ def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None):
     if out is None:
         out = torch.empty(a.shape[:-1] + (N,), dtype=a.dtype, device=a.device)
     _, _, ldy = _rows2d(out)
-    call("mograd_b200_matmul_bias_bt", _ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, lda, ldw, ldy, int(act),
-         dtype_code(a), _stream())
+    ldr = _rows2d(residual)[2] if residual is not None else 0
+    call("mograd_b200_matmul_bias_bt_ex", _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, lda, ldw,
+         ldr, ldy, int(act), dtype_code(a), _stream())
     return out
 
 
-def matmul_bias_bt_bwd(dy, x, w, need_dx=True, need_dw=True, need_db=True, dx_out=None, dw_out=None, db_out=None):
-    """(dX, dW, db) of Y = X @ W.T + b in one call; outputs not needed are None."""
-    _require_cuda(dy, x, w)
+def matmul_bias_bt_bwd(dy, x, w, need_dx=True, need_dw=True, need_db=True, dx_out=None, dw_out=None, db_out=None,
+                       relu_y=None, dx_residual=None):
+    """(dX, dW, db) of Y = X @ W.T + b in one call; outputs not needed are None.
+    relu_y: ReLU output that produced X (dX is masked by relu_y > 0); dx_residual: added to dX."""
+    _require_cuda(dy, x, w, relu_y, dx_residual)
     M, N, lddy = _rows2d(dy)
     M2, K, ldx = _rows2d(x)
     N2, K2, ldw = _rows2d(w)
@@ -105,8 +108,10 @@ def matmul_bias_bt_bwd(dy, x, w, need_dx=True, need_dw=True, need_db=True, dx_ou
     ws = scratch_take(nbytes, dy.device)
     lddx = _rows2d(dx)[2] if dx is not None else K
     lddw = dw.stride(0) if dw is not None else K
-    call("mograd_b200_matmul_bias_bt_bwd", _ptr(dy), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), M, N, K, lddy,
-         ldx, ldw, lddx, lddw, code, _ptr(ws), ws.numel(), _stream())
+    ldm = _rows2d(relu_y)[2] if relu_y is not None else 0
+    ldr = _rows2d(dx_residual)[2] if dx_residual is not None else 0
+    call("mograd_b200_matmul_bias_bt_bwd_ex", _ptr(dy), _ptr(x), _ptr(w), _ptr(relu_y), _ptr(dx_residual), _ptr(dx),
+         _ptr(dw), _ptr(db), M, N, K, lddy, ldx, ldw, ldm, ldr, lddx, lddw, code, _ptr(ws), ws.numel(), _stream())
     return dx, dw, db
 
 
@@ -128,9 +133,10 @@ def layer_norm_fwd_dispatch(x, gamma, beta, eps: float = 1e-5, save_stats: bool 
     return (out, mean, rstd) if save_stats else out
 
 
-def layer_norm_bwd_dispatch(dy, x, gamma, eps: float = 1e-5, dx_out=None, dgamma_out=None, dbeta_out=None):
-    """inputs [dy, x, gamma] -> [dx, dgamma, dbeta] (dispatch.mojo:332-358)."""
-    _require_cuda(dy, x, gamma)
+def layer_norm_bwd_dispatch(dy, x, gamma, eps: float = 1e-5, dx_out=None, dgamma_out=None, dbeta_out=None,
+                            dx_residual=None):
+    """inputs [dy, x, gamma] -> [dx (+ dx_residual), dgamma, dbeta] (dispatch.mojo:332-358)."""
+    _require_cuda(dy, x, gamma, dx_residual)
     x = x if x.is_contiguous() else x.contiguous()
     dy = dy if dy.is_contiguous() else dy.contiguous()
     cols = x.shape[-1]
@@ -141,8 +147,8 @@ def layer_norm_bwd_dispatch(dy, x, gamma, eps: float = 1e-5, dx_out=None, dgamma
     code = dtype_code(x)
     nbytes = query("mograd_b200_layer_norm_bwd_workspace_bytes", rows, cols, code)
     ws = scratch_take(nbytes, x.device)
-    call("mograd_b200_layer_norm_bwd", _ptr(dy), _ptr(x), _ptr(gamma), _ptr(dx), _ptr(dgamma), _ptr(dbeta), rows,
-         cols, float(eps), code, _ptr(ws), ws.numel(), _stream())
+    call("mograd_b200_layer_norm_bwd_ex", _ptr(dy), _ptr(x), _ptr(gamma), _ptr(dx_residual), _ptr(dx), _ptr(dgamma),
+         _ptr(dbeta), rows, cols, float(eps), code, _ptr(ws), ws.numel(), _stream())
     return [dx, dgamma, dbeta]
 
 
@@ -197,24 +203,38 @@ def softmax_xent_fwd_bwd(logits, index, upstream: float = 1.0, want_loss=True, w
 # ----------------------------------------------------------------------------
 # Attention (dispatch.mojo:380-481)
 # ----------------------------------------------------------------------------
-def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_bias=None, out=None, lse_out=None):
-    """srcs [Q, K, V, mask] all BSHD -> [O (BHSD), LSE (B,H,S) float32]."""
+def _token_stride(t, name):
+    """Elements between consecutive tokens of a (B,S,H,D) tensor whose heads are packed inside a token row."""
+    B, S, H, D = t.shape
+    if t.stride(3) != 1 or t.stride(2) != D or (B > 1 and t.stride(0) != S * t.stride(1)):
+        raise KernelError("flash_attn", _lib.EINVAL, f"{name}: heads must be packed inside each token row")
+    return t.stride(1)
+
+
+def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_bias=None, out=None, lse_out=None,
+                            o_bshd=False):
+    """srcs [Q, K, V, mask] all BSHD -> [O (BHSD, or BSHD when o_bshd), LSE (B,H,S) float32].
+    Q, K, V may be column blocks of one fused projection output (equal token strides)."""
     _require_cuda(q, k, v, mask)
     B, S, H, D = q.shape
     if has_bias is None:
         has_bias = mask is not None and not is_causal
     if scale is None:
         scale = 1.0 / math.sqrt(D)
-    q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
-    dst = torch.empty((B, H, S, D), dtype=q.dtype, device=q.device) if out is None else out
+    ld = _token_stride(q, "q")
+    if _token_stride(k, "k") != ld or _token_stride(v, "v") != ld:
+        raise KernelError("flash_attn_fwd", _lib.EINVAL, "q, k and v must share one token stride")
+    oshape = (B, S, H, D) if o_bshd else (B, H, S, D)
+    dst = torch.empty(oshape, dtype=q.dtype, device=q.device) if out is None else out
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if lse_out is None else lse_out
-    call("mograd_b200_flash_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(dst), _ptr(lse), B, S, H, D,
-         float(scale), int(bool(is_causal)), int(bool(has_bias)), dtype_code(q), _stream())
+    call("mograd_b200_flash_attn_fwd_ex", _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(dst), _ptr(lse), B, S, H, D,
+         float(scale), int(bool(is_causal)), int(bool(has_bias)), ld, int(bool(o_bshd)), dtype_code(q), _stream())
     return [dst, lse]
 
 
-def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=True, has_bias=None, out=None):
-    """srcs [dO, O, Q, K, V, mask, LSE] -> [dQ, dK, dV] (BSHD)."""
+def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=True, has_bias=None, out=None,
+                            o_bshd=False):
+    """srcs [dO, O, Q, K, V, mask, LSE] -> [dQ, dK, dV] (BSHD); dO and O are BHSD, or BSHD when o_bshd."""
     _require_cuda(dy, o, q, k, v, mask, lse)
     B, S, H, D = q.shape
     if has_bias is None:
@@ -222,12 +242,21 @@ def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=Tru
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dy = dy if dy.is_contiguous() else dy.contiguous()  # the rule makes dO contiguous (grad.mojo:336-339)
-    dq, dk, dv = out if out is not None else (torch.empty_like(q), torch.empty_like(q), torch.empty_like(q))
+    ld = _token_stride(q, "q")
+    if _token_stride(k, "k") != ld or _token_stride(v, "v") != ld:
+        raise KernelError("flash_attn_bwd", _lib.EINVAL, "q, k and v must share one token stride")
+    if out is not None:
+        dq, dk, dv = out
+    else:
+        dq, dk, dv = (torch.empty((B, S, H, D), dtype=q.dtype, device=q.device) for _ in range(3))
+    ldd = _token_stride(dq, "dq")
+    if _token_stride(dk, "dk") != ldd or _token_stride(dv, "dv") != ldd:
+        raise KernelError("flash_attn_bwd", _lib.EINVAL, "dq, dk and dv must share one token stride")
     code = dtype_code(q)
     ws = scratch_take(query("mograd_b200_flash_attn_bwd_workspace_bytes", B, S, H, D, code), q.device)
-    call("mograd_b200_flash_attn_bwd", _ptr(dy), _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(lse), _ptr(dq),
-         _ptr(dk), _ptr(dv), B, S, H, D, float(scale), int(bool(is_causal)), int(bool(has_bias)), code, _ptr(ws),
-         ws.numel(), _stream())
+    call("mograd_b200_flash_attn_bwd_ex", _ptr(dy), _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(lse), _ptr(dq),
+         _ptr(dk), _ptr(dv), B, S, H, D, float(scale), int(bool(is_causal)), int(bool(has_bias)), ld, ldd,
+         int(bool(o_bshd)), code, _ptr(ws), ws.numel(), _stream())
     return [dq, dk, dv]
 
 

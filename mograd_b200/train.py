@@ -35,6 +35,8 @@ class ParamStore:
         self.device = device
         self.specs = []  # (name, shape, offset)
         self.size = 0
+        self.aliases = []
+        self.alias_parents = []
 
     def declare(self, name, shape):
         n = 1
@@ -59,6 +61,21 @@ class ParamStore:
             self.P[name] = self.w[off:off + n].view(shape)
             self.G[name] = self.g[off:off + n].view(shape)
             self.range[name] = (off, off + n)
+
+    def alias(self, name, parent, row_lo, row_hi):
+        """Expose rows [row_lo, row_hi) of a declared matrix under a second name (e.g. Wq inside Wqkv)."""
+        off, _ = self.range[parent]
+        cols = self.P[parent].shape[1]
+        self.P[name] = self.P[parent][row_lo:row_hi]
+        self.G[name] = self.G[parent][row_lo:row_hi]
+        self.range[name] = (off + row_lo * cols, off + row_hi * cols)
+        self.aliases.append((name, (row_hi - row_lo, cols)))
+
+    def reference_names(self):
+        """(name, shape) of every parameter under the reference model's own names."""
+        hidden = {p for p, _ in self.alias_parents}
+        out = [(n, shp) for n, shp, _ in self.specs if n not in hidden]
+        return out + list(self.aliases)
 
     def load(self, values: dict):
         """values: name -> float32 CPU tensor; fills master and the working copy."""
@@ -211,10 +228,9 @@ class MLP(_Model):
         for i in range(self.nl - 1, 0, -1):
             inp = self.act[i - 1] if i > 1 else self.ln_out
             dst = self.dact[i - 1] if i > 1 else self.dln
-            K.matmul_bias_bt_bwd(dy, inp, P[f"W{i}"], dx_out=dst, dw_out=G[f"W{i}"], db_out=G[f"b{i}"])
+            K.matmul_bias_bt_bwd(dy, inp, P[f"W{i}"], dx_out=dst, dw_out=G[f"W{i}"], db_out=G[f"b{i}"],
+                                 relu_y=self.act[i - 1] if i > 1 else None)
             self._grads_ready_down_to(self.store.range[f"W{i}"][0])
-            if i > 1:
-                K.relu_grad(self.act[i - 1], dst)
             dy = dst
         K.layer_norm_bwd_dispatch(self.dln, self.act[0], P["ln_g"], dx_out=self.dln, dgamma_out=G["ln_g"],
                                   dbeta_out=G["ln_b"])
@@ -224,7 +240,12 @@ class MLP(_Model):
 
 
 class TinyTransformer(_Model):
-    """Decoder-only transformer of examples/tinyshakespear/model.mojo, one train step at a time."""
+    """Decoder-only transformer of examples/tinyshakespear/model.mojo, one train step at a time.
+
+    W_Q, W_K and W_V of a block are stored as the three row blocks of one (3d, d) matrix, so their three
+    projections (and the three dX / dW products of the backward pass) run as single GEMMs; attention reads Q, K, V
+    as column blocks of that GEMM's output and writes its output token-major, so no transpose copy is needed.
+    """
 
     def __init__(self, vocab, d_model, d_ff, n_layers, n_heads, batch, seq, dtype=torch.bfloat16, device="cuda",
                  opt=None, seed=0, init_std=0.02, **kw):
@@ -236,8 +257,9 @@ class TinyTransformer(_Model):
         st = self.store
         st.declare("embed", (vocab, d_model))
         for l in range(n_layers):
-            for nm in ("Wq", "Wk", "Wv", "Wo"):
-                st.declare(f"{nm}{l}", (d_model, d_model))
+            st.declare(f"Wqkv{l}", (3 * d_model, d_model))
+            st.alias_parents.append((f"Wqkv{l}", l))
+            st.declare(f"Wo{l}", (d_model, d_model))
             st.declare(f"W1_{l}", (d_ff, d_model))
             st.declare(f"b1_{l}", (d_ff,))
             st.declare(f"W2_{l}", (d_model, d_ff))
@@ -245,6 +267,9 @@ class TinyTransformer(_Model):
                 st.declare(f"{nm}_{l}", (d_model,))
         st.declare("lm_head", (vocab, d_model))
         st.allocate()
+        for l in range(n_layers):
+            for r, nm in enumerate(("Wq", "Wk", "Wv")):
+                st.alias(f"{nm}{l}", f"Wqkv{l}", r * d_model, (r + 1) * d_model)
         g = torch.Generator().manual_seed(seed)
         vals = {}
         for name, shape, _ in st.specs:
@@ -264,24 +289,21 @@ class TinyTransformer(_Model):
         self.x = [new(T, d) for _ in range(n_layers + 1)]  # block inputs, x[L] = final hidden state
         self.saved = []
         for _ in range(n_layers):
-            self.saved.append(dict(ln1=new(T, d), q=new(T, d), k=new(T, d), v=new(T, d),
-                                   o=new(batch, n_heads, seq, self.Dh),
+            self.saved.append(dict(ln1=new(T, d), qkv=new(T, 3 * d), ctx=new(T, d),
                                    lse=torch.empty((batch, n_heads, seq), dtype=torch.float32, device=dev),
-                                   ctx=new(T, d), h=new(T, d), ln2=new(T, d), f1=new(T, d_ff)))
+                                   h=new(T, d), ln2=new(T, d), f1=new(T, d_ff)))
         self.Vp = _pad8(vocab)
         self.logits_buf = new(T, self.Vp)
         self.logits = self.logits_buf[:, :vocab]
         # backward scratch, reused by every block
-        self.t_a, self.t_b, self.t_c, self.t_d = new(T, d), new(T, d), new(T, d), new(T, d)
+        self.t_dx, self.t_b = new(T, d), new(T, d)
         self.t_ff = new(T, d_ff)
-        self.dO = new(batch, n_heads, seq, self.Dh)
+        self.t_dqkv = new(T, 3 * d)
 
-    # BSHD <-> BHSD copies (the reference's .transpose(1, 2) + contiguous around the attention node)
-    def _to_bshd(self, src_bhsd, dst_td):
-        dst_td.view(self.B, self.S, self.H, self.Dh).copy_(src_bhsd.permute(0, 2, 1, 3))
-
-    def _to_bhsd(self, src_td, dst_bhsd):
-        dst_bhsd.copy_(src_td.view(self.B, self.S, self.H, self.Dh).permute(0, 2, 1, 3))
+    def _heads(self, qkv):
+        """(q, k, v) views (B, S, H, Dh) of a (T, 3d) fused projection buffer."""
+        v5 = qkv.view(self.B, self.S, 3, self.H, self.Dh)
+        return v5[:, :, 0], v5[:, :, 1], v5[:, :, 2]
 
     def forward_backward(self):
         P, G, st = self.store.P, self.store.G, self.store
@@ -291,52 +313,39 @@ class TinyTransformer(_Model):
         for l in range(L):
             sv, x = self.saved[l], self.x[l]
             K.layer_norm_fwd_dispatch(x, P[f"g1_{l}"], P[f"be1_{l}"], out=sv["ln1"])
-            K.matmul_bias_strided(sv["ln1"], P[f"Wq{l}"], out=sv["q"])
-            K.matmul_bias_strided(sv["ln1"], P[f"Wk{l}"], out=sv["k"])
-            K.matmul_bias_strided(sv["ln1"], P[f"Wv{l}"], out=sv["v"])
-            q4, k4, v4 = (sv[n].view(B, S, H, Dh) for n in ("q", "k", "v"))
-            K.flash_attn_fwd_dispatch(q4, k4, v4, None, None, True, False, out=sv["o"], lse_out=sv["lse"])
-            self._to_bshd(sv["o"], sv["ctx"])
-            K.matmul_bias_strided(sv["ctx"], P[f"Wo{l}"], out=self.t_a)
-            K.add(x, self.t_a, out=sv["h"])
+            K.matmul_bias_strided(sv["ln1"], P[f"Wqkv{l}"], out=sv["qkv"])
+            q4, k4, v4 = self._heads(sv["qkv"])
+            K.flash_attn_fwd_dispatch(q4, k4, v4, None, None, True, False, out=sv["ctx"].view(B, S, H, Dh),
+                                      lse_out=sv["lse"], o_bshd=True)
+            K.matmul_bias_strided(sv["ctx"], P[f"Wo{l}"], out=sv["h"], residual=x)
             K.layer_norm_fwd_dispatch(sv["h"], P[f"g2_{l}"], P[f"be2_{l}"], out=sv["ln2"])
             K.matmul_bias_strided(sv["ln2"], P[f"W1_{l}"], P[f"b1_{l}"], act=1, out=sv["f1"])
-            K.matmul_bias_strided(sv["f1"], P[f"W2_{l}"], out=self.t_a)
-            K.add(sv["h"], self.t_a, out=self.x[l + 1])
+            K.matmul_bias_strided(sv["f1"], P[f"W2_{l}"], out=self.x[l + 1], residual=sv["h"])
         K.matmul_bias_strided(self.x[L], P["lm_head"], out=self.logits)
         loss, dl = K.softmax_xent_fwd_bwd(self.logits, self.d_targets.view(-1), inplace=True)
 
         # ---- backward
-        dx = self.t_a  # gradient w.r.t. the current block's output
+        dx = self.t_dx  # gradient w.r.t. the current block's output
         K.matmul_bias_bt_bwd(dl, self.x[L], P["lm_head"], dx_out=dx, dw_out=G["lm_head"], need_db=False)
         self._grads_ready_down_to(st.range["lm_head"][0])
         for l in range(L - 1, -1, -1):
             sv, x = self.saved[l], self.x[l]
             # FFN: out = h + W2 relu(W1 ln2 + b1)
-            K.matmul_bias_bt_bwd(dx, sv["f1"], P[f"W2_{l}"], dx_out=self.t_ff, dw_out=G[f"W2_{l}"], need_db=False)
-            K.relu_grad(sv["f1"], self.t_ff)
+            K.matmul_bias_bt_bwd(dx, sv["f1"], P[f"W2_{l}"], dx_out=self.t_ff, dw_out=G[f"W2_{l}"], need_db=False,
+                                 relu_y=sv["f1"])
             K.matmul_bias_bt_bwd(self.t_ff, sv["ln2"], P[f"W1_{l}"], dx_out=self.t_b, dw_out=G[f"W1_{l}"],
                                  db_out=G[f"b1_{l}"])
-            K.layer_norm_bwd_dispatch(self.t_b, sv["h"], P[f"g2_{l}"], dx_out=self.t_c, dgamma_out=G[f"g2_{l}"],
-                                      dbeta_out=G[f"be2_{l}"])
-            K.add(dx, self.t_c, out=dx)  # dh
+            K.layer_norm_bwd_dispatch(self.t_b, sv["h"], P[f"g2_{l}"], dx_out=dx, dgamma_out=G[f"g2_{l}"],
+                                      dbeta_out=G[f"be2_{l}"], dx_residual=dx)  # dx is now dL/dh
             # attention: h = x + Wo ctx
             K.matmul_bias_bt_bwd(dx, sv["ctx"], P[f"Wo{l}"], dx_out=self.t_b, dw_out=G[f"Wo{l}"], need_db=False)
-            self._to_bhsd(self.t_b, self.dO)
-            q4, k4, v4 = (sv[n].view(B, S, H, Dh) for n in ("q", "k", "v"))
-            dq, dk, dv = self.t_b.view(B, S, H, Dh), self.t_c.view(B, S, H, Dh), self.t_d.view(B, S, H, Dh)
-            K.flash_attn_bwd_dispatch(self.dO, sv["o"], q4, k4, v4, None, sv["lse"], None, True, False,
-                                      out=(dq, dk, dv))
-            # ln1 feeds Q, K and V
-            dln1 = sv["ctx"]  # free to overwrite now
-            K.matmul_bias_bt_bwd(self.t_b, sv["ln1"], P[f"Wq{l}"], dx_out=dln1, dw_out=G[f"Wq{l}"], need_db=False)
-            K.matmul_bias_bt_bwd(self.t_c, sv["ln1"], P[f"Wk{l}"], dx_out=self.t_b, dw_out=G[f"Wk{l}"], need_db=False)
-            K.add(dln1, self.t_b, out=dln1)
-            K.matmul_bias_bt_bwd(self.t_d, sv["ln1"], P[f"Wv{l}"], dx_out=self.t_b, dw_out=G[f"Wv{l}"], need_db=False)
-            K.add(dln1, self.t_b, out=dln1)
-            K.layer_norm_bwd_dispatch(dln1, x, P[f"g1_{l}"], dx_out=self.t_c, dgamma_out=G[f"g1_{l}"],
-                                      dbeta_out=G[f"be1_{l}"])
-            K.add(dx, self.t_c, out=dx)
-            self._grads_ready_down_to(st.range[f"Wq{l}"][0])
+            q4, k4, v4 = self._heads(sv["qkv"])
+            K.flash_attn_bwd_dispatch(self.t_b.view(B, S, H, Dh), sv["ctx"].view(B, S, H, Dh), q4, k4, v4, None,
+                                      sv["lse"], None, True, False, out=self._heads(self.t_dqkv), o_bshd=True)
+            K.matmul_bias_bt_bwd(self.t_dqkv, sv["ln1"], P[f"Wqkv{l}"], dx_out=self.t_b, dw_out=G[f"Wqkv{l}"],
+                                 need_db=False)
+            K.layer_norm_bwd_dispatch(self.t_b, x, P[f"g1_{l}"], dx_out=dx, dgamma_out=G[f"g1_{l}"],
+                                      dbeta_out=G[f"be1_{l}"], dx_residual=dx)  # dx is now dL/dx
+            self._grads_ready_down_to(st.range[f"Wqkv{l}"][0])
         K.scatter_add_rows(dx, tok, self.V, out=G["embed"])
         return loss

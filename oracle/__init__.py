@@ -157,8 +157,8 @@ def sdpa_fwd(q, k, v, scale, causal, mask=None):
     return out, lse
 
 
-def sdpa_bwd(q, k, v, dy, scale, causal, mask=None):
-    """q,k,v BSHD, dy BHSD -> (dQ, dK, dV) BSHD."""
+def sdpa_bwd(q, k, v, dy, scale, causal, mask=None, o_saved=None):
+    """q,k,v BSHD, dy BHSD -> (dQ, dK, dV) BSHD.  o_saved: stored forward output (BHSD) to take delta from."""
     q, qp = _f(q)
     k, kp = _f(k)
     v, vp = _f(v)
@@ -170,7 +170,10 @@ def sdpa_bwd(q, k, v, dy, scale, causal, mask=None):
     mp = None
     if mask is not None:
         mask, mp = _f(mask)
-    lib().orc_sdpa_bwd(qp, kp, vp, dp, mp, dq.ctypes.data_as(_f32p), dk.ctypes.data_as(_f32p),
+    op = None
+    if o_saved is not None:
+        o_saved, op = _f(o_saved)
+    lib().orc_sdpa_bwd(qp, kp, vp, dp, mp, op, dq.ctypes.data_as(_f32p), dk.ctypes.data_as(_f32p),
                        dv.ctypes.data_as(_f32p), _i64(B), _i64(S), _i64(H), _i64(D), _dbl(scale),
                        ctypes.c_int(int(causal)))
     return dq, dk, dv

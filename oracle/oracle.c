@@ -301,10 +301,15 @@ ORC_API void orc_sdpa_fwd(const float* q, const float* k, const float* v, const 
 /* ds = p*(dp - delta)*scale, dq += ds*k, dk += ds*q, dv += p*dO, with       */
 /* delta = sum_d dO*O recomputed from p and v.                               */
 /* Parallelised over (b,h); every (b,h) owns its slice of dQ/dK/dV.          */
+/* o_saved (BHSD, may be NULL): when given, delta = sum_d dO*o_saved, i.e.   */
+/* the forward output as it was STORED, which is what the reference's GPU    */
+/* kernels use (flash_attn_bwd_delta_kernel,                                 */
+/* mograd/runtime/gpu/kernels/attention/nvidia_bwd.mojo:784-836); with NULL  */
+/* delta comes from the exact recomputed output as in the harness.           */
 /* ------------------------------------------------------------------------ */
 ORC_API void orc_sdpa_bwd(const float* q, const float* k, const float* v, const float* dy, const float* mask,
-                          float* dq, float* dk, float* dv, int64_t B, int64_t S, int64_t H, int64_t D,
-                          double scale, int causal) {
+                          const float* o_saved, float* dq, float* dk, float* dv, int64_t B, int64_t S, int64_t H,
+                          int64_t D, double scale, int causal) {
 #pragma omp parallel
   {
     double* p = (double*)malloc(sizeof(double) * (size_t)S);
@@ -344,7 +349,12 @@ ORC_API void orc_sdpa_bwd(const float* q, const float* k, const float* v, const 
           for (int64_t d = 0; d < D; ++d) od[d] += p[j] * (double)vj[d];
         }
         double delta = 0.0;
-        for (int64_t d = 0; d < D; ++d) delta += (double)dyi[d] * od[d];
+        if (o_saved) {
+          const float* oi = o_saved + (bh * S + i) * D;
+          for (int64_t d = 0; d < D; ++d) delta += (double)dyi[d] * (double)oi[d];
+        } else {
+          for (int64_t d = 0; d < D; ++d) delta += (double)dyi[d] * od[d];
+        }
         for (int64_t j = 0; j < j_end; ++j) {
           const float* kj = k + ((b * S + j) * H + h) * D;
           const float* vj = v + ((b * S + j) * H + h) * D;

@@ -76,7 +76,7 @@ def transformer_step(params, tokens, targets, n_layers, n_heads, round_fn=_id):
         ln2 = r(O.layer_norm_fwd(h, params[f"g2_{l}"], params[f"be2_{l}"])[0])
         f1 = r(O.relu(O.matmul_bias_bt(ln2, params[f"W1_{l}"], params[f"b1_{l}"])))
         out = r(h + r(O.matmul_bias_bt(f1, params[f"W2_{l}"])))
-        saved.append(dict(ln1=ln1, q=q, k=k, v=v, ctx=ctx, h=h, ln2=ln2, f1=f1))
+        saved.append(dict(ln1=ln1, q=q, k=k, v=v, o=o, ctx=ctx, h=h, ln2=ln2, f1=f1))
         x.append(out)
     logits = r(O.matmul_bias_bt(x[-1], params["lm_head"]))
     loss, dl, _ = O.cross_entropy_index(logits, targets.reshape(-1))
@@ -94,7 +94,7 @@ def transformer_step(params, tokens, targets, n_layers, n_heads, round_fn=_id):
         dctx, grads[f"Wo{l}"], _ = O.matmul_bias_bt_bwd(dh, sv["ctx"], params[f"Wo{l}"], need_db=False)
         dO = np.ascontiguousarray(r(dctx).reshape(B, S, H, Dh).transpose(0, 2, 1, 3))
         dq, dk, dv = O.sdpa_bwd(sv["q"].reshape(B, S, H, Dh), sv["k"].reshape(B, S, H, Dh), sv["v"].reshape(B, S, H, Dh),
-                                dO, 1 / math.sqrt(Dh), True)
+                                dO, 1 / math.sqrt(Dh), True, o_saved=None if round_fn is _id else sv["o"])
         dq, dk, dv = (r(t).reshape(T, d) for t in (dq, dk, dv))
         d1, grads[f"Wq{l}"], _ = O.matmul_bias_bt_bwd(dq, sv["ln1"], params[f"Wq{l}"], need_db=False)
         d2, grads[f"Wk{l}"], _ = O.matmul_bias_bt_bwd(dk, sv["ln1"], params[f"Wk{l}"], need_db=False)

@@ -185,3 +185,29 @@ def test_full_size_properties(cuda, oracle):
     vs = v[bsel, :, hsel].float().cpu().numpy()[None, :, None, :]
     wo, wlse = oracle.sdpa_fwd(qs[:, :512], ks[:, :512], vs[:, :512], 1 / math.sqrt(D), True)
     assert rel_err(o[bsel, hsel, :512].float().cpu().numpy(), wo[0, 0]) <= TOL_BF16
+
+
+@pytest.mark.parametrize("B,S,H,D,dt", [(2, 256, 3, 64, "bf16"), (1, 200, 2, 128, "bf16"), (2, 40, 2, 16, "f32")])
+def test_fused_projection_layout(cuda, oracle, B, S, H, D, dt):
+    """Q, K, V as column blocks of one (tokens, 3*H*D) buffer, O / dO token-major (BSHD), dQ/dK/dV into one buffer."""
+    import torch
+    from mograd_b200 import dispatch as K
+
+    q, k, v, dy = _mk(B, S, H, D, dt, 31)
+    scale = 1 / math.sqrt(D)
+    wo, _ = oracle.sdpa_fwd(q, k, v, scale, True)
+    wdq, wdk, wdv = oracle.sdpa_bwd(q, k, v, dy, scale, True)
+    tdt = torch.float32 if dt == "f32" else torch.bfloat16
+    qkv = torch.from_numpy(np.stack([q, k, v], axis=2)).to(cuda).to(tdt)  # (B, S, 3, H, D)
+    q4, k4, v4 = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    o, lse = K.flash_attn_fwd_dispatch(q4, k4, v4, None, None, True, False, o_bshd=True)
+    assert o.shape == (B, S, H, D)
+    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    assert rel_err(o.float().cpu().numpy(), wo.transpose(0, 2, 1, 3)) <= tol
+    dqkv = torch.full_like(qkv, float("nan"))
+    do = torch.from_numpy(np.ascontiguousarray(dy.transpose(0, 2, 1, 3))).to(cuda).to(tdt)  # BSHD
+    K.flash_attn_bwd_dispatch(do, o, q4, k4, v4, None, lse, None, True, False,
+                              out=(dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]), o_bshd=True)
+    assert _status() == 0
+    got = dqkv.float().cpu().numpy()
+    assert rel_err(got[:, :, 0], wdq) <= tol and rel_err(got[:, :, 1], wdk) <= tol and rel_err(got[:, :, 2], wdv) <= tol

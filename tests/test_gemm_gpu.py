@@ -123,3 +123,47 @@ def test_large_linearity(cuda):
     assert torch.equal(y2, y1 * 2)
     ref = (a1[:256].float() @ w.float().T)
     assert rel_err(y1[:256].cpu().numpy(), ref.cpu().numpy()) <= TOL_BF16
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("M,N,K", [(256, 384, 128), (130, 72, 200), (64, 10, 32)])
+def test_extended_epilogues(cuda, oracle, M, N, K, dt):
+    """Fused residual add (forward), ReLU-backward mask and gradient accumulation (dX), db inside the dW GEMM."""
+    from mograd_b200 import dispatch as Kx
+
+    rng = np.random.default_rng(M + N)
+    x, w, b, dy = _mk(M, N, K, dt, 11)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    relu_y = np.maximum(rng.standard_normal((M, K)), 0).astype(np.float32)
+    dres = rng.standard_normal((M, K)).astype(np.float32)
+    if dt == "bf16":
+        res, relu_y, dres = bf16_round(res), bf16_round(relu_y), bf16_round(dres)
+    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    y = Kx.matmul_bias_strided(_dev(x, cuda, dt), _dev(w, cuda, dt), _dev(b, cuda, dt), act=1, residual=_dev(res, cuda, dt))
+    want = np.maximum(oracle.matmul_bias_bt(x, w, b), 0) + res
+    assert rel_err(y.float().cpu().numpy(), want) <= tol
+    wdx, wdw, wdb = oracle.matmul_bias_bt_bwd(dy, x, w)
+    wdx = oracle.relu_grad(relu_y, wdx) + dres
+    dx, dw, db = Kx.matmul_bias_bt_bwd(_dev(dy, cuda, dt), _dev(x, cuda, dt), _dev(w, cuda, dt),
+                                       relu_y=_dev(relu_y, cuda, dt), dx_residual=_dev(dres, cuda, dt))
+    assert _status() == 0
+    assert rel_err(dx.float().cpu().numpy(), wdx) <= tol
+    assert rel_err(dw.float().cpu().numpy(), wdw) <= tol
+    assert rel_err(db.float().cpu().numpy(), wdb) <= tol
+
+
+def test_db_inside_dw_gemm_tall(cuda, oracle):
+    """Bias gradient accumulated from the dY tiles of the split dW GEMM (contraction 16384)."""
+    from mograd_b200 import dispatch as Kx
+
+    x, w, _, dy = _mk(16384, 384, 256, "bf16", 21)
+    _, wdw, wdb = oracle.matmul_bias_bt_bwd(dy, x, w)
+    args = (_dev(dy, cuda, "bf16"), _dev(x, cuda, "bf16"), _dev(w, cuda, "bf16"))
+    _, dw, db = Kx.matmul_bias_bt_bwd(*args, need_dx=False)
+    _, dw2, db2 = Kx.matmul_bias_bt_bwd(*args, need_dx=False)
+    assert _status() == 0
+    assert rel_err(dw.float().cpu().numpy(), wdw) <= TOL_BF16
+    assert rel_err(db.float().cpu().numpy(), wdb) <= TOL_BF16
+    import torch
+
+    assert torch.equal(db, db2) and torch.equal(dw, dw2)

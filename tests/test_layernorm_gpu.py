@@ -105,3 +105,26 @@ def test_full_size_properties(cuda, oracle):
     assert rel_err(dx[sel].float().cpu().numpy(), wdx) <= TOL_BF16
     # dx of every row is orthogonal to the all-ones vector when gamma-weighted terms are removed: sum_c dx = 0
     assert dx.float().sum(dim=1).abs().max().item() < 0.5
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 768), (65, 4096), (9, 37)])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_bwd_with_residual_gradient(cuda, oracle, rows, cols, dt):
+    """dx = layer_norm_bwd(...) + dx_residual, in place on the residual buffer."""
+    import torch
+    from mograd_b200 import dispatch as K
+
+    rng = np.random.default_rng(rows + cols)
+    x, dy, res = (rng.standard_normal((rows, cols)).astype(np.float32) for _ in range(3))
+    g = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    tdt = torch.float32 if dt == "f32" else torch.bfloat16
+    if dt == "bf16":
+        x, dy, res, g = (bf16_round(t) for t in (x, dy, res, g))
+    wdx, wdg, wdb = oracle.layer_norm_bwd(dy, x, g)
+    dev = lambda t: torch.from_numpy(t).to(cuda).to(tdt)
+    rbuf = dev(res)
+    dx, dg, db = K.layer_norm_bwd_dispatch(dev(dy), dev(x), dev(g), dx_out=rbuf, dx_residual=rbuf)
+    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    assert dx.data_ptr() == rbuf.data_ptr()
+    assert rel_err(dx.float().cpu().numpy(), wdx + res) <= tol
+    assert rel_err(dg.float().cpu().numpy(), wdg) <= tol and rel_err(db.float().cpu().numpy(), wdb) <= tol
