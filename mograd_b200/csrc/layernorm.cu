@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
 // row is being reduced.  A lane only ever reads back the 16-byte chunks it
 // copied itself, so the ring needs no barrier.  Registers hold just gamma and
 // the fp32 dgamma / dbeta partials.
-constexpr int kLnStages = 4;
+constexpr int kLnStages = 3;
 
 __device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(gptr) : "memory");
@@ -320,6 +320,37 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Sums four values over the team's WPR warps with one block barrier per call;
+// `red` holds two parity buffers of 4 floats per warp, alternated by the caller.
+template <int WPR>
+__device__ __forceinline__ void team_sum4(float (&v)[4], float* red, int parity, int warps, int warp, int team,
+                                          int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = warp_sum(v[i]);
+  if (WPR > 1) {
+    float* buf = red + parity * warps * 4;
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) buf[warp * 4 + i] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = 0.f;
+#pragma unroll
+    for (int w = 0; w < WPR; ++w) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] += buf[(team * WPR + w) * 4 + i];
+    }
+  }
+}
+
+// Row pass count is what bounds this kernel once the loads are asynchronous:
+// per element it issues ~14 instructions (two passes) instead of the ~24 of
+// the three-pass form.  Pass A forms sum x, sum x^2, sum dy*g and sum dy*g*x
+// together; c2 = mean(dy*g*xhat) then follows as rstd*(sum dy*g*x - mu*sum dy*g)/n.
+// Pass B writes dx = dy*g*rstd - rstd*c1 - xhat*rstd*c2 with two FMAs and
+// accumulates dgamma / dbeta.  When a lane's slice is small (KEEP) the
+// unpacked x and dy stay in registers between the passes.
 template <typename T, int WPR, int CHUNKS>
 __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     ln_bwd_pipe_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid,
@@ -327,11 +358,11 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
   constexpr int V = Vec<T>::N;
   using S = Shape<WPR>;
   constexpr int SLOT = CHUNKS * 512;  // bytes of one array (x or dy) of one row slot of one warp
+  constexpr bool KEEP = CHUNKS * V <= 16;
   extern __shared__ __align__(16) unsigned char dsm[];
   float* fold = reinterpret_cast<float*>(dsm);                       // [2][cols]
   unsigned char* ring_base = dsm + ((2 * cols * sizeof(float) + 15) / 16) * 16;
-  __shared__ float redA[2 * S::WARPS];
-  __shared__ float redB[2 * S::WARPS];
+  __shared__ float red[2 * S::WARPS * 4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int team = warp / WPR;
   const int lt = (warp % WPR) * 32 + lane;
@@ -371,63 +402,64 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
 #pragma unroll
   for (int s = 0; s < kLnStages - 1; ++s) issue(r_first + s * r_step, s);
 
-  int slot = 0;
+  int slot = 0, parity = 0;
   for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * S::TEAMS; r0 < rows; r0 += r_step) {
     const int64_t row = r0 + team;
     const bool live = row < rows;
-    // keep kLnStages - 1 rows in flight: refill the slot that was consumed in the previous iteration
     issue(row + (kLnStages - 1) * r_step, (slot + kLnStages - 1) % kLnStages);
     cp_async_wait<kLnStages - 1>();
     const uint4* xs = reinterpret_cast<const uint4*>(ring + slot * 2 * SLOT);
     const uint4* ds = reinterpret_cast<const uint4*>(ring + slot * 2 * SLOT + SLOT);
-    float sx = 0.f, sx2 = 0.f;
+    float xk[KEEP ? CHUNKS : 1][V], dk[KEEP ? CHUNKS : 1][V];
+    float sums[4] = {0.f, 0.f, 0.f, 0.f};  // sum x, sum x^2, sum dy*g, sum dy*g*x
 #pragma unroll
     for (int j = 0; j < CHUNKS; ++j) {
-      if (live && colj[j] < cols) {
-        float v[V];
-        unpack<T>(xs[j * 32 + lane], v);
+      float v[V], d[V], g[V];
+      const bool in = live && colj[j] < cols;
+      unpack<T>(in ? xs[j * 32 + lane] : make_uint4(0, 0, 0, 0), v);
+      unpack<T>(in ? ds[j * 32 + lane] : make_uint4(0, 0, 0, 0), d);
+      unpack<T>(g_raw[j], g);
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          sx += v[e];
-          sx2 = fmaf(v[e], v[e], sx2);
+      for (int e = 0; e < V; ++e) {
+        const float dyg = d[e] * g[e];
+        sums[0] += v[e];
+        sums[1] = fmaf(v[e], v[e], sums[1]);
+        sums[2] += dyg;
+        sums[3] = fmaf(dyg, v[e], sums[3]);
+        if (KEEP) {
+          xk[j][e] = v[e];
+          dk[j][e] = d[e];
         }
       }
     }
-    team_sum2<WPR>(sx, sx2, redA, warp, team, lane);
-    const float mu = sx * inv_n;
-    const float rs = rsqrtf(fmaxf(sx2 * inv_n - mu * mu, 0.f) + eps);
-    float c1 = 0.f, c2 = 0.f;
-#pragma unroll
-    for (int j = 0; j < CHUNKS; ++j) {
-      if (live && colj[j] < cols) {
-        float v[V], d[V], g[V];
-        unpack<T>(xs[j * 32 + lane], v);
-        unpack<T>(ds[j * 32 + lane], d);
-        unpack<T>(g_raw[j], g);
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          const float dyg = d[e] * g[e];
-          c1 += dyg;
-          c2 = fmaf(dyg, (v[e] - mu) * rs, c2);
-        }
-      }
-    }
-    team_sum2<WPR>(c1, c2, redB, warp, team, lane);
-    c1 *= inv_n;
-    c2 *= inv_n;
+    team_sum4<WPR>(sums, red, parity, S::WARPS, warp, team, lane);
+    parity ^= 1;
+    const float mu = sums[0] * inv_n;
+    const float rs = rsqrtf(fmaxf(sums[1] * inv_n - mu * mu, 0.f) + eps);
+    const float c1 = sums[2] * inv_n;
+    const float c2 = rs * (sums[3] - mu * sums[2]) * inv_n;
+    const float nmr = -mu * rs, k1 = -rs * c1, k2 = -rs * c2;
     if (live) {
       T* dxr = dx + row * cols;
 #pragma unroll
       for (int j = 0; j < CHUNKS; ++j) {
         if (colj[j] < cols) {
           float v[V], d[V], g[V], o[V];
-          unpack<T>(xs[j * 32 + lane], v);
-          unpack<T>(ds[j * 32 + lane], d);
+          if (KEEP) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              v[e] = xk[j][e];
+              d[e] = dk[j][e];
+            }
+          } else {
+            unpack<T>(xs[j * 32 + lane], v);
+            unpack<T>(ds[j * 32 + lane], d);
+          }
           unpack<T>(g_raw[j], g);
 #pragma unroll
           for (int e = 0; e < V; ++e) {
-            const float xhat = (v[e] - mu) * rs;
-            o[e] = rs * (d[e] * g[e] - c1 - xhat * c2);
+            const float xhat = fmaf(v[e], rs, nmr);
+            o[e] = fmaf(xhat, k2, fmaf(d[e] * g[e], rs, k1));
             dg[j][e] = fmaf(d[e], xhat, dg[j][e]);
             db[j][e] += d[e];
           }

@@ -109,12 +109,11 @@ class _Model:
         self.store = ParamStore(dtype, self.device)
         self.step_count = 0
         self.comm_stream = None
-        self._bucket_lo = None
-        self.launches = 0
+        self.exchanged = []  # (lo, hi) slices all-reduced so far, in issue order (cleared by the caller)
 
     # ---- data-parallel gradient exchange -------------------------------------------------
     def _setup_buckets(self):
-        if self.world_size > 1:
+        if self.world_size > 1 and self.device.type == "cuda":
             self.comm_stream = torch.cuda.Stream(device=self.device)
         esz = self.store.g.element_size()
         per = max(1, self.bucket_bytes // esz)
@@ -135,18 +134,23 @@ class _Model:
 
         while self._next_bucket < len(self.buckets) and self.buckets[self._next_bucket][0] >= offset:
             lo, hi = self.buckets[self._next_bucket]
-            ev = torch.cuda.Event()
-            ev.record(torch.cuda.current_stream(self.device))
-            self.comm_stream.wait_event(ev)
-            with torch.cuda.stream(self.comm_stream):
+            if self.comm_stream is None:  # host tensors (gloo): no streams to order
                 dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
+            else:
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(self.device))
+                self.comm_stream.wait_event(ev)
+                with torch.cuda.stream(self.comm_stream):
+                    dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
+            self.exchanged.append((lo, hi))
             self._next_bucket += 1
 
     def _finish_exchange(self):
         if self.world_size == 1:
             return
         self._grads_ready_down_to(0)
-        torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        if self.comm_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         self._next_bucket = 0
 
     def optimizer_step(self):
