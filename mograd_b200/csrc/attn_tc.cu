@@ -13,7 +13,7 @@
 // tiles i (i >= j when causal; tiles above the diagonal are skipped):
 //     S  = Q_i K_j^T          dP = dO_i V_j^T              (tensor cores -> TMEM)
 //     P  = exp2(S*scale*log2e - lse*log2e),  dS = P*(dP - delta)*scale
-//                                                          (8 warps, TMEM -> bf16 in shared)
+//                                                          (16 warps, TMEM -> bf16 in shared)
 //     dV += P^T dO_i          dK += dS^T Q_i               (accumulate in TMEM over i)
 //     dQ_i partial = dS K_j   -> fp32 vector reductions into the dQ accumulator
 // dK / dV leave TMEM once per CTA; dQ is converted to bf16 by a last kernel.
@@ -24,6 +24,7 @@
 // P goes to shared memory as bf16, O += P V_j accumulates in TMEM and is
 // rescaled in place when a row maximum moves.
 #include <math.h>
+#include <stdlib.h>
 
 #include "attn.cuh"
 #include "common.cuh"
@@ -47,10 +48,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 // K-major slice k (16 contraction elements) of a [128][cols] swizzled tile.
 __device__ __forceinline__ uint64_t desc_k(uint32_t tile, int k) {
   return smem_desc_sw128(tile + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
@@ -78,45 +75,60 @@ struct AttnParams {
   int64_t ld_dqkv;  // elements between consecutive tokens of dK / dV
   int o_bshd;       // layout of O (forward output)
   int* status;
+  long long* trace;  // TEMP
 };
 
 // ============================================================== backward
+// Schedule of one CTA (key tile j), steady state of query tile i:
+//   tensor cores : dP_i | S_{i+1} (as soon as S_i, dP_i sit in registers) | dV_i, dK_i, dQ_i
+//   16 warps     : S_i, dP_i -> registers | exp / dS math -> P, dS in shared | dQ_i -> registers -> reductions
+//   TMA          : Q two tiles ahead (two slots), dO one tile ahead (D = 64: two slots; D = 128: one)
+// dQ_i is written over the dP columns, which are free once dP_i is in registers; the next dP waits for the
+// 16 warps to have read dQ_i out of TMEM (the reductions themselves are issued afterwards and do not block).
 template <int D>
 struct BwdCfg {
   static constexpr int HALVES = D / 64;
   static constexpr int TILE_BYTES = 128 * D * 2;
-  static constexpr int QSTAGES = (D == 64) ? 2 : 1;
+  static constexpr int QST = 2;
+  static constexpr int DOST = (D == 64) ? 2 : 1;
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = TILE_BYTES;
   static constexpr int OFF_Q = 2 * TILE_BYTES;
-  static constexpr int OFF_DO = OFF_Q + QSTAGES * TILE_BYTES;
-  static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;
+  static constexpr int OFF_DO = OFF_Q + QST * TILE_BYTES;
+  static constexpr int OFF_P = OFF_DO + DOST * TILE_BYTES;
   static constexpr int OFF_DS = OFF_P + kPsBytes;
   static constexpr int OFF_BAR = OFF_DS + kPsBytes;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
-  static constexpr int COL_DQ = (D == 64) ? 384 : 0;
+  static constexpr int COL_DQ = COL_DP;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int THREADS = 320;
+  static constexpr int THREADS = 608;  // TMA warp, MMA warp, 16 compute warps, dQ reduction warp
 };
 
 template <int D>
 __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                       const AttnParams p) {
+                       const __grid_constant__ CUtensorMap tm_dq, const AttnParams p) {
   using C = BwdCfg<D>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
   const uint32_t bar = base + C::OFF_BAR;
-  const uint32_t bar_kv = bar, bar_sdp = bar + 8, bar_pds = bar + 16, bar_dqf = bar + 24, bar_dqd = bar + 32;
-  auto bar_qf = [&](int s) { return bar + 40 + 8u * s; };
-  auto bar_qe = [&](int s) { return bar + 56 + 8u * s; };
-  const uint32_t tmem_slot = bar + 72;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 72);
+  const uint32_t bar_kv = bar, bar_sdp = bar + 8, bar_sfree = bar + 16, bar_pds = bar + 24, bar_dqf = bar + 32,
+                 bar_dqd = bar + 40;
+  auto bar_qf = [&](int s) { return bar + 48 + 8u * s; };
+  auto bar_qe = [&](int s) { return bar + 64 + 8u * s; };
+  auto bar_dof = [&](int s) { return bar + 80 + 8u * s; };
+  auto bar_doe = [&](int s) { return bar + 96 + 8u * s; };
+  const uint32_t bar_stg = bar + 112;   // dQ staging area (the P | dS tiles) has been read by the TMA unit
+  const uint32_t bar_stgf = bar + 120;  // dQ staging area holds this tile's fp32 dQ
+  const uint32_t tmem_slot = bar + 128;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0;  // TEMP
+#define TR(slot, it) do { if (tr && (it) < 16) p.trace[(it) * 16 + (slot)] = clock64(); } while (0)
   const int j = blockIdx.x;  // key tile
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
@@ -127,12 +139,17 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
     mbar_init(bar_sdp, 1);
-    mbar_init(bar_pds, 8);
+    mbar_init(bar_sfree, 16);
+    mbar_init(bar_pds, 16);
     mbar_init(bar_dqf, 1);
-    mbar_init(bar_dqd, 8);
+    mbar_init(bar_dqd, 16);
+    mbar_init(bar_stg, 1);
+    mbar_init(bar_stgf, 16);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_qf(s), 1);
       mbar_init(bar_qe(s), 1);
+      mbar_init(bar_dof(s), 1);
+      mbar_init(bar_doe(s), 1);
     }
     mbar_fence_init();
   }
@@ -152,30 +169,45 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_dq);
       mbar_expect_tx(bar_kv, 2 * C::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < C::HALVES; ++c) {
         tma_load_4d(base + C::OFF_K + c * kHalfBytes, &tm_k, bar_kv, c * 64, h, j * 128, b);
         tma_load_4d(base + C::OFF_V + c * kHalfBytes, &tm_v, bar_kv, c * 64, h, j * 128, b);
       }
-      for (int it = 0; it < iters; ++it) {
-        const int s = it % C::QSTAGES;
-        const uint32_t ph = (it / C::QSTAGES) & 1u;
-        if (!mbar_wait(bar_qe(s), ph ^ 1u)) {
-          atomicExch(p.status, kErrBwdTma);
-          break;
-        }
-        const int i = i0 + it;
-        mbar_expect_tx(bar_qf(s), 2 * C::TILE_BYTES);
+      bool ok = true;
+      auto load_q = [&](int it) {
+        const int s = it % C::QST;
+        if (!mbar_wait(bar_qe(s), ((it / C::QST) & 1u) ^ 1u)) return false;
+        mbar_expect_tx(bar_qf(s), C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::HALVES; ++c)
+          tma_load_4d(base + C::OFF_Q + s * C::TILE_BYTES + c * kHalfBytes, &tm_q, bar_qf(s), c * 64, h,
+                      (i0 + it) * 128, b);
+        return true;
+      };
+      auto load_do = [&](int it) {
+        const int s = it % C::DOST;
+        if (!mbar_wait(bar_doe(s), ((it / C::DOST) & 1u) ^ 1u)) return false;
+        TR(0, it);
+        mbar_expect_tx(bar_dof(s), C::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < C::HALVES; ++c) {
-          tma_load_4d(base + C::OFF_Q + s * C::TILE_BYTES + c * kHalfBytes, &tm_q, bar_qf(s), c * 64, h, i * 128, b);
+          const uint32_t dst = base + C::OFF_DO + s * C::TILE_BYTES + c * kHalfBytes;
           if (p.o_bshd)
-            tma_load_4d(base + C::OFF_DO + s * C::TILE_BYTES + c * kHalfBytes, &tm_do, bar_qf(s), c * 64, h, i * 128, b);
+            tma_load_4d(dst, &tm_do, bar_dof(s), c * 64, h, (i0 + it) * 128, b);
           else
-            tma_load_3d(base + C::OFF_DO + s * C::TILE_BYTES + c * kHalfBytes, &tm_do, bar_qf(s), c * 64, i * 128, bh);
+            tma_load_3d(dst, &tm_do, bar_dof(s), c * 64, (i0 + it) * 128, bh);
         }
+        return true;
+      };
+      ok = load_q(0) && load_do(0);
+      for (int it = 0; it < iters && ok; ++it) {
+        if (it + 1 < iters) ok = load_q(it + 1);
+        if (ok && it + 1 < iters) ok = load_do(it + 1);
       }
+      if (!ok) atomicExch(p.status, kErrBwdTma);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -185,59 +217,94 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       constexpr uint32_t id_mm = umma_idesc_bf16(128, D, 1, 1);
       constexpr uint32_t id_km = umma_idesc_bf16(128, D, 0, 1);
       const uint32_t sK = base + C::OFF_K, sV = base + C::OFF_V, sP = base + C::OFF_P, sDS = base + C::OFF_DS;
-      bool ok = mbar_wait(bar_kv, 0);
-      if (!ok) atomicExch(p.status, kErrBwdMma);
-      for (int it = 0; it < iters && ok; ++it) {
-        const int s = it % C::QSTAGES;
-        const uint32_t ph = (it / C::QSTAGES) & 1u;
-        const uint32_t sQ = base + C::OFF_Q + s * C::TILE_BYTES, sDO = base + C::OFF_DO + s * C::TILE_BYTES;
-        ok = mbar_wait(bar_qf(s), ph);
-        if (ok && D == 128 && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ lives in the S columns
-        if (!ok) {
-          atomicExch(p.status, kErrBwdMma);
-          break;
-        }
-        tc_fence_after();
+      auto q_tile = [&](int it) { return base + C::OFF_Q + (it % C::QST) * C::TILE_BYTES; };
+      auto do_tile = [&](int it) { return base + C::OFF_DO + (it % C::DOST) * C::TILE_BYTES; };
+      auto issue_s = [&](int it) {
+        const uint32_t sQ = q_tile(it);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S, desc_k(sQ, k), desc_k(sK, k), id_ss, k > 0);
+      };
+      bool ok = iters > 0 && mbar_wait(bar_kv, 0) && mbar_wait(bar_qf(0), 0);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int it = 0; it < iters && ok; ++it) {
+        const uint32_t sQ = q_tile(it), sDO = do_tile(it);
+        ok = mbar_wait(bar_dof(it % C::DOST), (it / C::DOST) & 1u);
+        if (ok && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ_{it-1} has left the dP columns
+        if (!ok) break;
+        tc_fence_after();
+        TR(1, it);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_DP, desc_k(sDO, k), desc_k(sV, k), id_ss, k > 0);
-        umma_commit(bar_sdp);
-        if (!mbar_wait(bar_pds, it & 1u)) {
-          atomicExch(p.status, kErrBwdMma);
+        umma_commit(bar_sdp);  // also covers S_it, issued one iteration earlier
+        TR(2, it);
+        if (!mbar_wait(bar_sfree, it & 1u)) {
           ok = false;
           break;
         }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss(tmem + C::COL_DV, desc_mn(sP, k), desc_mn(sDO, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss(tmem + C::COL_DK, desc_mn(sDS, k), desc_mn(sQ, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
-        umma_commit(bar_qe(s));
-        if (D == 64 && it > 0) {
-          if (!mbar_wait(bar_dqd, (it - 1) & 1u)) {
-            atomicExch(p.status, kErrBwdMma);
+        if (it + 1 < iters) {
+          if (!mbar_wait(bar_qf((it + 1) % C::QST), ((it + 1) / C::QST) & 1u)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          issue_s(it + 1);  // runs while the 16 warps work on tile it
         }
+        if (!mbar_wait(bar_pds, it & 1u)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        TR(3, it);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DV, desc_mn(sP, k), desc_mn(sDO, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar_doe(it % C::DOST));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DK, desc_mn(sDS, k), desc_mn(sQ, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar_qe(it % C::QST));
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_DQ, desc_k(sDS, k), desc_mn(sK, k), id_km, k > 0);
         umma_commit(bar_dqf);
+        TR(4, it);
       }
+      if (!ok && iters > 0) atomicExch(p.status, kErrBwdMma);
+    }
+    __syncwarp();
+  } else if (warp == 18) {
+    // ------------------------------------------------- dQ reduction (TMA)
+    if (lane == 0) {
+      for (int it = 0; it < iters; ++it) {
+        if (!mbar_wait(bar_stgf, it & 1u)) {
+          atomicExch(p.status, kErrBwdCompute);
+          break;
+        }
+        TR(11, it);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c)
+          tma_reduce_add_4d(&tm_dq, base + C::OFF_P + c * kHalfBytes, c * 32, h, (i0 + it) * 128, b);
+        bulk_commit();
+        bulk_wait_read0();
+        TR(12, it);
+        mbar_arrive(bar_stg);
+      }
+      bulk_wait0();  // every reduction has landed before the CTA retires
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------ compute
+    // 16 warps: TMEM lane quarter = warp % 4 (hardware rule), column group cg = 32 of the 128 S / dP columns.
+    // The softmax scale is left out of dS here and applied once to dK (epilogue) and dQ (final cast).
     const int cw = warp - 2;
     const int quarter = warp & 3;
-    const int ch = cw >> 2;  // which 64-column half of S / dP this warp handles
+    const int cg = cw >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float scale_log2 = p.scale * kLog2e;
+    constexpr int DC = D / 4;  // dQ / dK / dV columns per warp
     bool ok = true;
     for (int it = 0; it < iters && ok; ++it) {
       const int i = i0 + it;
@@ -251,15 +318,28 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         break;
       }
       tc_fence_after();
+      if (warp == 2 && lane == 0) TR(5, it);
       const bool diag = p.causal && (i == j);
-#pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        const int col0 = ch * 64 + c0;
-        uint32_t s[32], dp[32];
-        tmem_ld32(tmem + lane_base + C::COL_S + col0, s);
-        tmem_ld32(tmem + lane_base + C::COL_DP + col0, dp);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
+      const bool masked = diag || (j * 128 + 128 > p.S) || (i * 128 + 128 > p.S);  // uniform over the CTA
+      const int col0 = cg * 32;
+      uint32_t sv[32], dpv[32];
+      tmem_ld32(tmem + lane_base + C::COL_S + col0, sv);
+      tmem_ld32(tmem + lane_base + C::COL_DP + col0, dpv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sfree);  // S and dP columns may be overwritten
+      if (warp == 2 && lane == 0) TR(13, it);
+      uint32_t pk[16], dk[16];
+      if (!masked) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(sv[e]), scale_log2, -lse2));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -lse2));
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+          dk[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dpv[e]) - dlt), p1 * (__uint_as_float(dpv[e + 1]) - dlt));
+        }
+      } else {
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pv[2], dv[2];
@@ -267,78 +347,93 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
           for (int u = 0; u < 2; ++u) {
             const int kvrow = j * 128 + col0 + e + u;
             const bool keep = vq && kvrow < p.S && (!diag || kvrow <= qrow);
-            const float pe = keep ? ex2(fmaf(__uint_as_float(s[e + u]), scale_log2, -lse2)) : 0.f;
+            const float pe = keep ? ex2(fmaf(__uint_as_float(sv[e + u]), scale_log2, -lse2)) : 0.f;
             pv[u] = pe;
-            dv[u] = pe * (__uint_as_float(dp[e + u]) - dlt) * p.scale;
+            dv[u] = pe * (__uint_as_float(dpv[e + u]) - dlt);
           }
           pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
           dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
         }
+      }
+      if (warp == 2 && lane == 0) TR(9, it);
+      if (it > 0 && !mbar_wait(bar_stg, (it - 1) & 1u)) {  // the previous dQ tile has left the P | dS area
+        if (lane == 0) atomicExch(p.status, kErrBwdCompute);
+        ok = false;
+        break;
+      }
+      if (warp == 2 && lane == 0) TR(10, it);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const uint32_t off = ps_chunk_off(r, (col0 >> 3) + t);
-          *reinterpret_cast<uint4*>(gen + C::OFF_P + off) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
-          *reinterpret_cast<uint4*>(gen + C::OFF_DS + off) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
-        }
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t off = ps_chunk_off(r, (col0 >> 3) + t);
+        *reinterpret_cast<uint4*>(gen + C::OFF_P + off) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+        *reinterpret_cast<uint4*>(gen + C::OFF_DS + off) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
       }
       fence_async_smem();
-      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pds);
-      // drain this tile's dQ contribution
+      if (warp == 2 && lane == 0) TR(6, it);
+      // this tile's dQ contribution: TMEM -> registers, release the columns, then reduce into the accumulator
       if (!mbar_wait(bar_dqf, it & 1u)) {
         if (lane == 0) atomicExch(p.status, kErrBwdCompute);
         ok = false;
         break;
       }
       tc_fence_after();
-      float* dq_row = p.dq_acc + ((static_cast<int64_t>(b) * p.S + (vq ? qrow : 0)) * p.H + h) * D;
-#pragma unroll 1
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
-        const int dcol = ch * (D / 2) + c0;
-        uint32_t v[32];
-        tmem_ld32(tmem + lane_base + C::COL_DQ + dcol, v);
-        tmem_ld_wait();
-        if (vq) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            red_add_v4(dq_row + dcol + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
-                       __uint_as_float(v[e + 3]));
-        }
+      if (warp == 2 && lane == 0) TR(7, it);
+      uint32_t v[DC];
+      if constexpr (DC == 32) {
+        tmem_ld32(tmem + lane_base + C::COL_DQ + cg * DC, v);
+      } else {
+        tmem_ld16(tmem + lane_base + C::COL_DQ + cg * DC, v);
       }
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_dqd);
+      if (warp == 2 && lane == 0) TR(8, it);
+      // Stage the fp32 tile in the P | dS area (both are idle once bar_dqf fired) as [128 rows][32 floats]
+      // boxes with the 128-byte swizzle, then let the TMA unit add it into the dQ accumulator: whole 128-byte
+      // lines per request instead of one 16-byte atomic per thread, and rows past S are clipped by the map.
+      {
+        constexpr int CH = DC / 4;                  // 16-byte chunks this thread owns
+        const int box = (cg * DC) / 32;             // which [128][32] box
+        const int ch0 = ((cg * DC) % 32) / 4;       // first chunk inside the 128-byte row
+        unsigned char* stg = gen + C::OFF_P + box * kHalfBytes + r * 128;
+#pragma unroll
+        for (int t = 0; t < CH; ++t)
+          *reinterpret_cast<uint4*>(stg + (((ch0 + t) ^ (r & 7)) << 4)) = make_uint4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_stgf);
     }
     // dK / dV: every MMA was complete when the last bar_dqf fired
-    if (ok) {
+    if (ok && iters > 0) {
       const int kvrow = j * 128 + r;
-      if (iters > 0) {
-        const int64_t tok = static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0);
-        bf16* dk_row = p.dk + tok * p.ld_dqkv + static_cast<int64_t>(h) * D;
-        bf16* dv_row = p.dv + tok * p.ld_dqkv + static_cast<int64_t>(h) * D;
+      const int64_t tok = static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0);
+      bf16* dk_row = p.dk + tok * p.ld_dqkv + static_cast<int64_t>(h) * D + cg * DC;
+      bf16* dv_row = p.dv + tok * p.ld_dqkv + static_cast<int64_t>(h) * D + cg * DC;
+      const float sc = p.scale;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
-          const int dcol = ch * (D / 2) + c0;
-          uint32_t a[32], c[32];
-          tmem_ld32(tmem + lane_base + C::COL_DK + dcol, a);
-          tmem_ld32(tmem + lane_base + C::COL_DV + dcol, c);
-          tmem_ld_wait();
-          if (kvrow < p.S) {
+      for (int c0 = 0; c0 < DC; c0 += 16) {
+        uint32_t a[16], c[16];
+        tmem_ld16(tmem + lane_base + C::COL_DK + cg * DC + c0, a);
+        tmem_ld16(tmem + lane_base + C::COL_DV + cg * DC + c0, c);
+        tmem_ld_wait();
+        if (kvrow < p.S) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              uint4 o1, o2;
-              o1.x = pack_bf16x2(__uint_as_float(a[e]), __uint_as_float(a[e + 1]));
-              o1.y = pack_bf16x2(__uint_as_float(a[e + 2]), __uint_as_float(a[e + 3]));
-              o1.z = pack_bf16x2(__uint_as_float(a[e + 4]), __uint_as_float(a[e + 5]));
-              o1.w = pack_bf16x2(__uint_as_float(a[e + 6]), __uint_as_float(a[e + 7]));
-              o2.x = pack_bf16x2(__uint_as_float(c[e]), __uint_as_float(c[e + 1]));
-              o2.y = pack_bf16x2(__uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
-              o2.z = pack_bf16x2(__uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
-              o2.w = pack_bf16x2(__uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
-              *reinterpret_cast<uint4*>(dk_row + dcol + e) = o1;
-              *reinterpret_cast<uint4*>(dv_row + dcol + e) = o2;
-            }
+          for (int e = 0; e < 16; e += 8) {
+            uint4 o1, o2;
+            o1.x = pack_bf16x2(__uint_as_float(a[e]) * sc, __uint_as_float(a[e + 1]) * sc);
+            o1.y = pack_bf16x2(__uint_as_float(a[e + 2]) * sc, __uint_as_float(a[e + 3]) * sc);
+            o1.z = pack_bf16x2(__uint_as_float(a[e + 4]) * sc, __uint_as_float(a[e + 5]) * sc);
+            o1.w = pack_bf16x2(__uint_as_float(a[e + 6]) * sc, __uint_as_float(a[e + 7]) * sc);
+            o2.x = pack_bf16x2(__uint_as_float(c[e]), __uint_as_float(c[e + 1]));
+            o2.y = pack_bf16x2(__uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
+            o2.z = pack_bf16x2(__uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
+            o2.w = pack_bf16x2(__uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
+            *reinterpret_cast<uint4*>(dk_row + c0 + e) = o1;
+            *reinterpret_cast<uint4*>(dv_row + c0 + e) = o2;
           }
         }
       }
@@ -354,7 +449,7 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
 
 // acc is packed (tokens x HD) fp32; dq rows are ld elements apart.
 __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8,
-                                                      int hd8, int64_t ld) {
+                                                      int hd8, int64_t ld, float scale) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < n8; i += stride) {
     const int64_t tok = i / hd8;
@@ -362,10 +457,10 @@ __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ 
     const float4 a = reinterpret_cast<const float4*>(acc)[2 * i];
     const float4 c = reinterpret_cast<const float4*>(acc)[2 * i + 1];
     uint4 o;
-    o.x = pack_bf16x2(a.x, a.y);
-    o.y = pack_bf16x2(a.z, a.w);
-    o.z = pack_bf16x2(c.x, c.y);
-    o.w = pack_bf16x2(c.z, c.w);
+    o.x = pack_bf16x2(a.x * scale, a.y * scale);
+    o.y = pack_bf16x2(a.z * scale, a.w * scale);
+    o.z = pack_bf16x2(c.x * scale, c.y * scale);
+    o.w = pack_bf16x2(c.z * scale, c.w * scale);
     *reinterpret_cast<uint4*>(dq + tok * ld + c8 * 8) = o;
   }
 }
@@ -661,11 +756,20 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
   if (!(p.o_bshd ? map_bshd(&mdo, dy, p.B, p.S, p.H, D, static_cast<int64_t>(p.H) * D)
                  : map_bhsd(&mdo, dy, p.B, p.S, p.H, D)))
     return MGB_ECUDA;
+  CUtensorMap mdq;  // fp32 (B,S,H,D) accumulator, boxes of [128 rows][32 floats]
+  {
+    const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.H), static_cast<uint64_t>(p.S),
+                              static_cast<uint64_t>(p.B)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(D) * 4, static_cast<uint64_t>(p.H) * D * 4,
+                                 static_cast<uint64_t>(p.S) * p.H * D * 4};
+    const uint32_t box[4] = {32, 1, 128, 1};
+    if (!encode_tmap_f32(&mdq, p.dq_acc, 4, dims, strides, box)) return MGB_ECUDA;
+  }
   auto kern = attn_bwd_tc_kernel<D>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
-  kern<<<grid, C::THREADS, C::SMEM, st>>>(mq, mk, mv, mdo, p);
+  kern<<<grid, C::THREADS, C::SMEM, st>>>(mq, mk, mv, mdo, mdq, p);
   return check_launch("attn_bwd_tc_kernel");
 }
 
@@ -720,6 +824,7 @@ int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const fl
   p.ld_dqkv = lay.ld_dqkv;
   p.o_bshd = lay.o_bshd;
   p.status = device_status_ptr();
+  if (getenv("MGB_TRACE")) p.trace = reinterpret_cast<long long*>(strtoull(getenv("MGB_TRACE"), nullptr, 0));  // TEMP
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_bwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_bwd: B*H=%d exceeds 65535", B * H);
   const int64_t n = static_cast<int64_t>(B) * S * H * D;
@@ -730,7 +835,7 @@ int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const fl
   const int64_t n8 = n / 8;
   int grid = static_cast<int>((n8 + 255) / 256);
   if (grid > sm_count() * 8) grid = sm_count() * 8;
-  cast_dq_kernel<<<grid, 256, 0, st>>>(dq_acc, static_cast<bf16*>(dq), n8, H * D / 8, lay.ld_dqkv);
+  cast_dq_kernel<<<grid, 256, 0, st>>>(dq_acc, static_cast<bf16*>(dq), n8, H * D / 8, lay.ld_dqkv, scale);
   return check_launch("cast_dq_kernel");
 }
 

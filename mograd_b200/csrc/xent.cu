@@ -90,21 +90,21 @@ __global__ void __launch_bounds__(kRowThreads) xent_row_kernel(const XentParams<
   const int tid = threadIdx.x;
   const T* x = p.logits + row * p.ldx;
   const T* lbl = DENSE ? p.dense + row * p.ldl : nullptr;
-  const int64_t nvec = p.vec_in ? p.C / V : 0;
+  const int nvec = p.vec_in ? static_cast<int>(p.C / V) : 0;
 
   float m = -INFINITY, s = 0.f, slx = 0.f, sl = 0.f;
 
   // ---- pass 1: HBM -> registers (-> shared), online max / sum-exp
-  for (int64_t i0 = 0; i0 < nvec; i0 += 4 * kRowThreads) {
+  for (int i0 = 0; i0 < nvec; i0 += 4 * kRowThreads) {
     uint4 raw[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int64_t i = i0 + u * kRowThreads + tid;
+      const int i = i0 + u * kRowThreads + tid;
       if (i < nvec) raw[u] = __ldcs(reinterpret_cast<const uint4*>(x) + i);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int64_t i = i0 + u * kRowThreads + tid;
+      const int i = i0 + u * kRowThreads + tid;
       if (i < nvec) {
         if (p.staged) reinterpret_cast<uint4*>(row_s)[i] = raw[u];
         float v[V];
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(kRowThreads) xent_row_kernel(const XentParams<
       }
     }
   }
-  for (int64_t c = nvec * V + tid; c < p.C; c += kRowThreads) {  // scalar tail / unaligned rows
+  for (int c = nvec * V + tid; c < static_cast<int>(p.C); c += kRowThreads) {  // scalar tail / unaligned rows
     const T raw = x[c];
     if (p.staged) row_s[c] = raw;
     const float v = to_f32(raw);
@@ -196,212 +196,41 @@ __global__ void __launch_bounds__(kRowThreads) xent_row_kernel(const XentParams<
   // ---- pass 2: shared (or L2) -> (softmax - label) * g -> HBM
   const float up = p.upstream_dev ? to_f32(p.upstream_dev[0]) : p.upstream_host;
   const float g = up / static_cast<float>(p.N);
-  const float inv_s = 1.f / s;
+  const float k = g / s;
   const float mb = m * kLog2e;
   T* out = p.dlogits + row * p.lddx;
   const T* src = p.staged ? row_s : x;
-  const int64_t nvec2 = (p.vec_out && (p.staged || p.vec_in)) ? p.C / V : 0;
-  for (int64_t i = tid; i < nvec2; i += kRowThreads) {
+  const int C = static_cast<int>(p.C);
+  const int nvec2 = (p.vec_out && (p.staged || p.vec_in)) ? C / V : 0;
+  const int ti = (t >= 0 && t < p.C) ? static_cast<int>(t) : -1;
+  // index labels with the row in shared memory: plain softmax * g in the loop, the target element is
+  // rewritten afterwards by the thread that stored it (no per-element compare)
+  const bool fixup = !DENSE && p.staged;
+  for (int i = tid; i < nvec2; i += kRowThreads) {
     float v[V], o[V];
     load_vec(src + i * V, v);
     if (DENSE) {
       float l[V];
       load_labels<T>(lbl, i, p.vec_lbl, l);
 #pragma unroll
-      for (int j = 0; j < V; ++j) o[j] = (ex2(fmaf(v[j], kLog2e, -mb)) * inv_s - l[j]) * g;
+      for (int j = 0; j < V; ++j) o[j] = fmaf(ex2(fmaf(v[j], kLog2e, -mb)), k, -l[j] * g);
+    } else if (fixup) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = ex2(fmaf(v[j], kLog2e, -mb)) * k;
     } else {
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float onehot = (i * V + j == t) ? 1.f : 0.f;
-        o[j] = (ex2(fmaf(v[j], kLog2e, -mb)) * inv_s - onehot) * g;
-      }
+      for (int j = 0; j < V; ++j) o[j] = fmaf(ex2(fmaf(v[j], kLog2e, -mb)), k, (i * V + j == ti) ? -g : 0.f);
     }
     store_vec(out + i * V, o);
   }
-  for (int64_t c = nvec2 * V + tid; c < p.C; c += kRowThreads) {
+  for (int c = nvec2 * V + tid; c < C; c += kRowThreads) {
     const float v = to_f32(src[c]);
-    const float l = DENSE ? to_f32(lbl[c]) : (c == t ? 1.f : 0.f);
-    out[c] = from_f32<T>((ex2(fmaf(v, kLog2e, -mb)) * inv_s - l) * g);
+    const float l = DENSE ? to_f32(lbl[c]) : ((c == ti && !fixup) ? 1.f : 0.f);
+    out[c] = from_f32<T>(fmaf(ex2(fmaf(v, kLog2e, -mb)), k, -l * g));
   }
-}
-
-// Row held in shared memory, three passes, one exp per element:
-//   1. HBM -> shared copy (16-byte loads, four in flight per thread) and the row maximum
-//      (packed bf16 max, no unpacking);
-//   2. shared -> shared: e = exp2((x - m) * log2e) replaces x in place (stored in T), sum in fp32;
-//   3. shared -> HBM: (e / s - label) * g with 16-byte stores.
-// The element of the target class is rewritten afterwards by the thread that stored it.
-template <typename T>
-__device__ __forceinline__ float vec_max(const uint4& raw);
-template <>
-__device__ __forceinline__ float vec_max<float>(const uint4& raw) {
-  return fmaxf(fmaxf(__uint_as_float(raw.x), __uint_as_float(raw.y)), fmaxf(__uint_as_float(raw.z), __uint_as_float(raw.w)));
-}
-template <>
-__device__ __forceinline__ float vec_max<__nv_bfloat16>(const uint4& raw) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  const __nv_bfloat162 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
-  return fmaxf(__low2float(m), __high2float(m));
-}
-
-template <typename T, bool DENSE>
-__global__ void __launch_bounds__(kRowThreads) xent_row_staged_kernel(const XentParams<T> p) {
-  constexpr int V = Vec<T>::N;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* row_s = reinterpret_cast<T*>(smem_raw);
-  uint4* row_v = reinterpret_cast<uint4*>(smem_raw);
-  __shared__ float red[3][kRowThreads / 32];
-  __shared__ float bcast[3];
-
-  const int64_t row = blockIdx.x;
-  const int tid = threadIdx.x;
-  const int warp = tid >> 5, lane = tid & 31;
-  const int C = static_cast<int>(p.C);
-  const T* x = p.logits + row * p.ldx;
-  const T* lbl = DENSE ? p.dense + row * p.ldl : nullptr;
-  const int nvec = p.vec_in ? C / V : 0;
-  int t = -1;
-  float xt = 0.f;
-  if (!DENSE) {
-    const int64_t t64 = p.index[row];
-    t = (t64 >= 0 && t64 < C) ? static_cast<int>(t64) : -1;
-    if (tid == 0 && t >= 0) xt = to_f32(x[t]);  // read before anything is written (dlogits may alias logits)
-  }
-
-  // ---- pass 1
-  float m = -INFINITY, slx = 0.f, sl = 0.f;
-  for (int i0 = 0; i0 < nvec; i0 += 4 * kRowThreads) {
-    uint4 raw[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * kRowThreads + tid;
-      if (i < nvec) raw[u] = __ldcs(reinterpret_cast<const uint4*>(x) + i);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int i = i0 + u * kRowThreads + tid;
-      if (i < nvec) {
-        row_v[i] = raw[u];
-        m = fmaxf(m, vec_max<T>(raw[u]));
-        if (DENSE) {
-          float v[V], l[V];
-          load_vec(reinterpret_cast<const T*>(&raw[u]), v);
-          load_labels<T>(lbl, i, p.vec_lbl, l);
-#pragma unroll
-          for (int j = 0; j < V; ++j) {
-            slx = fmaf(l[j], v[j], slx);
-            sl += l[j];
-          }
-        }
-      }
-    }
-  }
-  for (int c = nvec * V + tid; c < C; c += kRowThreads) {
-    const T raw = x[c];
-    row_s[c] = raw;
-    const float v = to_f32(raw);
-    m = fmaxf(m, v);
-    if (DENSE) {
-      const float l = to_f32(lbl[c]);
-      slx = fmaf(l, v, slx);
-      sl += l;
-    }
-  }
-  m = warp_max(m);
-  if (DENSE) {
-    slx = warp_sum(slx);
-    sl = warp_sum(sl);
-  }
-  if (lane == 0) {
-    red[0][warp] = m;
-    red[1][warp] = slx;
-    red[2][warp] = sl;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    constexpr int W = kRowThreads / 32;
-    float mm = lane < W ? red[0][lane] : -INFINITY;
-    float a = lane < W ? red[1][lane] : 0.f;
-    float b = lane < W ? red[2][lane] : 0.f;
-    mm = warp_max(mm);
-    a = warp_sum(a);
-    b = warp_sum(b);
-    if (lane == 0) {
-      bcast[0] = mm;
-      bcast[1] = a;
-      bcast[2] = b;
-    }
-  }
-  __syncthreads();
-  m = bcast[0];
-  const float slx_all = bcast[1], sl_all = bcast[2];
-  const float mb = m * kLog2e;
-
-  // ---- pass 2: e = exp(x - m) in place, fp32 sum
-  const int nv_s = C / V;  // the shared copy is always 16-byte addressable
-  float s = 0.f;
-  for (int i = tid; i < nv_s; i += kRowThreads) {
-    float v[V];
-    load_vec(row_s + i * V, v);
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-      v[j] = ex2(fmaf(v[j], kLog2e, -mb));
-      s += v[j];
-    }
-    store_vec(row_s + i * V, v);
-  }
-  for (int c = nv_s * V + tid; c < C; c += kRowThreads) {
-    const float e = ex2(fmaf(to_f32(row_s[c]), kLog2e, -mb));
-    s += e;
-    row_s[c] = from_f32<T>(e);
-  }
-  s = warp_sum(s);
-  if (lane == 0) red[0][warp] = s;  // pass 1's readers of red[] / bcast[] are behind its second barrier
-  __syncthreads();
-  if (warp == 0) {
-    constexpr int W = kRowThreads / 32;
-    float ss = lane < W ? red[0][lane] : 0.f;
-    ss = warp_sum(ss);
-    if (lane == 0) bcast[0] = ss;
-  }
-  __syncthreads();
-  s = bcast[0];
-
-  if (tid == 0 && p.row_loss) {
-    const float lse = m + logf(s);
-    const float l = DENSE ? -(slx_all - lse * sl_all) : (t >= 0 ? -(xt - lse) : 0.f);
-    p.row_loss[row] = l / static_cast<float>(p.N);
-  }
-  if (!p.dlogits) return;
-
-  // ---- pass 3
-  const float up = p.upstream_dev ? to_f32(p.upstream_dev[0]) : p.upstream_host;
-  const float g = up / static_cast<float>(p.N);
-  const float k = g / s;
-  T* out = p.dlogits + row * p.lddx;
-  const int nvec3 = p.vec_out ? C / V : 0;
-  for (int i = tid; i < nvec3; i += kRowThreads) {
-    float v[V];
-    load_vec(row_s + i * V, v);
-    if (DENSE) {
-      float l[V];
-      load_labels<T>(lbl, i, p.vec_lbl, l);
-#pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = fmaf(v[j], k, -l[j] * g);
-    } else {
-#pragma unroll
-      for (int j = 0; j < V; ++j) v[j] *= k;
-    }
-    store_vec(out + i * V, v);
-  }
-  for (int c = nvec3 * V + tid; c < C; c += kRowThreads) {
-    const float l = DENSE ? to_f32(lbl[c]) : 0.f;
-    out[c] = from_f32<T>(fmaf(to_f32(row_s[c]), k, -l * g));
-  }
-  if (!DENSE && t >= 0) {
-    // the thread that stored element t rewrites it with the one-hot term
-    const int owner = (t < nvec3 * V) ? ((t / V) % kRowThreads) : ((t - nvec3 * V) % kRowThreads);
-    if (tid == owner) out[t] = from_f32<T>((to_f32(row_s[t]) / s - 1.f) * g);
+  if (fixup && ti >= 0) {
+    const int owner = (ti < nvec2 * V) ? ((ti / V) % kRowThreads) : ((ti - nvec2 * V) % kRowThreads);
+    if (tid == owner) out[ti] = from_f32<T>(fmaf(ex2(fmaf(to_f32(row_s[ti]), kLog2e, -mb)), k, -g));
   }
 }
 
@@ -493,7 +322,7 @@ int launch_xent(XentParams<T> p, cudaStream_t st) {
   const size_t smem = round_up(row_bytes, 16);
   p.staged = smem <= smem_cap;
   const size_t dyn = p.staged ? smem : 0;
-  auto kern = p.staged ? xent_row_staged_kernel<T, DENSE> : xent_row_kernel<T, DENSE>;
+  auto kern = xent_row_kernel<T, DENSE>;
   if (dyn > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dyn));
     if (e != cudaSuccess) return fail(MGB_ECUDA, "xent smem opt-in (%zu B): %s", dyn, cudaGetErrorString(e));
