@@ -49,7 +49,7 @@ WORKLOADS = {
                        tokens_per_step=16 * 1024,
                        desc="GPT-2-small-shaped decoder L12 H12 d768 ctx 1024 vocab 50304, per-GPU batch 16, bf16"),
 }
-DEFAULT_WORKLOAD = "readme_mlp"
+DEFAULT_WORKLOAD = "gpt2_small"
 
 
 def load_peaks():

@@ -24,7 +24,6 @@
 // P goes to shared memory as bf16, O += P V_j accumulates in TMEM and is
 // rescaled in place when a row maximum moves.
 #include <math.h>
-#include <stdlib.h>
 
 #include "attn.cuh"
 #include "common.cuh"
@@ -48,13 +47,17 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Descriptors are built once per tile; the slice for contraction step k is the base plus a constant in the
+// 16-byte-granular start-address field (the field cannot carry: shared addresses stay below 256 KB).
 // K-major slice k (16 contraction elements) of a [128][cols] swizzled tile.
-__device__ __forceinline__ uint64_t desc_k(uint32_t tile, int k) {
-  return smem_desc_sw128(tile + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
+__device__ __forceinline__ uint64_t base_k(uint32_t tile) { return smem_desc_sw128(tile, 16, 1024); }
+__device__ __forceinline__ uint64_t desc_k(uint64_t base, int k) {
+  return base + static_cast<uint64_t>(((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4);
 }
 // MN-major slice k (16 contraction rows) of a [128 rows][cols] swizzled tile.
-__device__ __forceinline__ uint64_t desc_mn(uint32_t tile, int k) {
-  return smem_desc_sw128(tile + k * 2048, kHalfBytes, 1024);
+__device__ __forceinline__ uint64_t base_mn(uint32_t tile) { return smem_desc_sw128(tile, kHalfBytes, 1024); }
+__device__ __forceinline__ uint64_t desc_mn(uint64_t base, int k) {
+  return base + static_cast<uint64_t>((k * 2048) >> 4);
 }
 // Byte offset of the 16-byte chunk holding columns [c8*8, c8*8+8) of row r in a [128][128] bf16 swizzled tile.
 __device__ __forceinline__ uint32_t ps_chunk_off(int r, int c8) {
@@ -75,7 +78,6 @@ struct AttnParams {
   int64_t ld_dqkv;  // elements between consecutive tokens of dK / dV
   int o_bshd;       // layout of O (forward output)
   int* status;
-  long long* trace;  // TEMP
 };
 
 // ============================================================== backward
@@ -97,10 +99,16 @@ struct BwdCfg {
   static constexpr int OFF_DO = OFF_Q + QST * TILE_BYTES;
   static constexpr int OFF_P = OFF_DO + DOST * TILE_BYTES;
   static constexpr int OFF_DS = OFF_P + kPsBytes;
-  static constexpr int OFF_BAR = OFF_DS + kPsBytes;
+  // D = 64 leaves room in TMEM and shared memory: dQ gets its own columns and its own fp32 staging tile, so the
+  // next tile's dP can start early and the dQ drain runs one tile behind the exp phase (LATE).  D = 128 fills
+  // TMEM: dQ overwrites the dP columns, is staged in the P | dS tiles and drained right away.
+  static constexpr bool LATE = (D == 64);
+  static constexpr int STG_BYTES = LATE ? 128 * D * 4 : 0;
+  static constexpr int OFF_STG = LATE ? OFF_DS + kPsBytes : OFF_P;
+  static constexpr int OFF_BAR = OFF_DS + kPsBytes + STG_BYTES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
-  static constexpr int COL_DQ = COL_DP;
+  static constexpr int COL_DQ = LATE ? 384 : COL_DP;
   static constexpr int TMEM_COLS = 512;
   static constexpr int THREADS = 608;  // TMA warp, MMA warp, 16 compute warps, dQ reduction warp
 };
@@ -127,8 +135,6 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool tr = p.trace && blockIdx.x == 0 && blockIdx.y == 0;  // TEMP
-#define TR(slot, it) do { if (tr && (it) < 16) p.trace[(it) * 16 + (slot)] = clock64(); } while (0)
   const int j = blockIdx.x;  // key tile
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
@@ -190,7 +196,6 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       auto load_do = [&](int it) {
         const int s = it % C::DOST;
         if (!mbar_wait(bar_doe(s), ((it / C::DOST) & 1u) ^ 1u)) return false;
-        TR(0, it);
         mbar_expect_tx(bar_dof(s), C::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < C::HALVES; ++c) {
@@ -219,57 +224,89 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       const uint32_t sK = base + C::OFF_K, sV = base + C::OFF_V, sP = base + C::OFF_P, sDS = base + C::OFF_DS;
       auto q_tile = [&](int it) { return base + C::OFF_Q + (it % C::QST) * C::TILE_BYTES; };
       auto do_tile = [&](int it) { return base + C::OFF_DO + (it % C::DOST) * C::TILE_BYTES; };
+      const uint64_t dK_k = base_k(sK), dK_mn = base_mn(sK), dV_k = base_k(sV);
+      const uint64_t dP_mn = base_mn(sP), dDS_mn = base_mn(sDS), dDS_k = base_k(sDS);
       auto issue_s = [&](int it) {
-        const uint32_t sQ = q_tile(it);
+        const uint64_t dQ_k = base_k(q_tile(it));
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S, desc_k(sQ, k), desc_k(sK, k), id_ss, k > 0);
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S, desc_k(dQ_k, k), desc_k(dK_k, k), id_ss, k > 0);
       };
-      bool ok = iters > 0 && mbar_wait(bar_kv, 0) && mbar_wait(bar_qf(0), 0);
+      auto issue_dp = [&](int it) {
+        const uint64_t dDO_k = base_k(do_tile(it));
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_DP, desc_k(dDO_k, k), desc_k(dV_k, k), id_ss, k > 0);
+      };
+      auto issue_grads = [&](int it) {  // dV, dK (accumulating over tiles) and this tile's dQ
+        const uint64_t dQ_mn = base_mn(q_tile(it)), dDO_mn = base_mn(do_tile(it));
+        const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DV, desc_mn(dP_mn, k), desc_mn(dDO_mn, k), id_mm, k > 0 ? 1u : acc);
+        umma_commit(bar_doe(it % C::DOST));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DK, desc_mn(dDS_mn, k), desc_mn(dQ_mn, k), id_mm, k > 0 ? 1u : acc);
+        umma_commit(bar_qe(it % C::QST));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_DQ, desc_k(dDS_k, k), desc_mn(dK_mn, k), id_km, k > 0);
+        umma_commit(bar_dqf);
+      };
+      auto wait_q = [&](int it) { return mbar_wait(bar_qf(it % C::QST), (it / C::QST) & 1u); };
+      auto wait_do = [&](int it) { return mbar_wait(bar_dof(it % C::DOST), (it / C::DOST) & 1u); };
+      bool ok = iters > 0 && mbar_wait(bar_kv, 0) && wait_q(0);
       if (ok) {
         tc_fence_after();
         issue_s(0);
       }
-      for (int it = 0; it < iters && ok; ++it) {
-        const uint32_t sQ = q_tile(it), sDO = do_tile(it);
-        ok = mbar_wait(bar_dof(it % C::DOST), (it / C::DOST) & 1u);
-        if (ok && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ_{it-1} has left the dP columns
-        if (!ok) break;
-        tc_fence_after();
-        TR(1, it);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_DP, desc_k(sDO, k), desc_k(sV, k), id_ss, k > 0);
-        umma_commit(bar_sdp);  // also covers S_it, issued one iteration earlier
-        TR(2, it);
-        if (!mbar_wait(bar_sfree, it & 1u)) {
-          ok = false;
-          break;
+      if (C::LATE) {
+        if (ok && (ok = wait_do(0))) {
+          tc_fence_after();
+          issue_dp(0);
+          umma_commit(bar_sdp);
         }
-        if (it + 1 < iters) {
-          if (!mbar_wait(bar_qf((it + 1) % C::QST), ((it + 1) / C::QST) & 1u)) {
+        for (int it = 0; it < iters && ok; ++it) {
+          ok = mbar_wait(bar_sfree, it & 1u);  // S_it, dP_it are in registers
+          if (ok && it + 1 < iters) {
+            ok = wait_q(it + 1) && wait_do(it + 1);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(it + 1);
+            issue_dp(it + 1);
+            umma_commit(bar_sdp);
+          }
+          ok = ok && mbar_wait(bar_pds, it & 1u);
+          if (ok && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ_{it-1} has left its columns
+          if (!ok) break;
+          tc_fence_after();
+          issue_grads(it);
+        }
+      } else {
+        for (int it = 0; it < iters && ok; ++it) {
+          ok = wait_do(it);
+          if (ok && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ_{it-1} has left the dP columns
+          if (!ok) break;
+          tc_fence_after();
+          issue_dp(it);
+          umma_commit(bar_sdp);  // also covers S_it, issued one iteration earlier
+          if (!mbar_wait(bar_sfree, it & 1u)) {
+            ok = false;
+            break;
+          }
+          if (it + 1 < iters) {
+            if (!wait_q(it + 1)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_s(it + 1);  // runs while the 16 warps work on tile it
+          }
+          if (!mbar_wait(bar_pds, it & 1u)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          issue_s(it + 1);  // runs while the 16 warps work on tile it
+          issue_grads(it);
         }
-        if (!mbar_wait(bar_pds, it & 1u)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        TR(3, it);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss(tmem + C::COL_DV, desc_mn(sP, k), desc_mn(sDO, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
-        umma_commit(bar_doe(it % C::DOST));
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ss(tmem + C::COL_DK, desc_mn(sDS, k), desc_mn(sQ, k), id_mm, (it > 0 || k > 0) ? 1u : 0u);
-        umma_commit(bar_qe(it % C::QST));
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_DQ, desc_k(sDS, k), desc_mn(sK, k), id_km, k > 0);
-        umma_commit(bar_dqf);
-        TR(4, it);
       }
       if (!ok && iters > 0) atomicExch(p.status, kErrBwdMma);
     }
@@ -282,13 +319,11 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
           atomicExch(p.status, kErrBwdCompute);
           break;
         }
-        TR(11, it);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c)
-          tma_reduce_add_4d(&tm_dq, base + C::OFF_P + c * kHalfBytes, c * 32, h, (i0 + it) * 128, b);
+          tma_reduce_add_4d(&tm_dq, base + C::OFF_STG + c * kHalfBytes, c * 32, h, (i0 + it) * 128, b);
         bulk_commit();
         bulk_wait_read0();
-        TR(12, it);
         mbar_arrive(bar_stg);
       }
       bulk_wait0();  // every reduction has landed before the CTA retires
@@ -306,6 +341,36 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     const float scale_log2 = p.scale * kLog2e;
     constexpr int DC = D / 4;  // dQ / dK / dV columns per warp
     bool ok = true;
+    // dQ of tile t: TMEM -> registers (frees the columns) -> fp32 staging tile in shared memory as
+    // [128 rows][32 floats] boxes with the 128-byte swizzle -> the reduction warp lets the TMA unit add it into
+    // the accumulator (whole 128-byte lines per request; rows past S are clipped by the tensor map).
+    auto drain = [&](int t, bool wait_ready) -> bool {
+      if (wait_ready && !mbar_wait(bar_dqf, t & 1u)) return false;  // never wait twice on one phase
+      tc_fence_after();
+      uint32_t v[DC];
+      if constexpr (DC == 32) {
+        tmem_ld32(tmem + lane_base + C::COL_DQ + cg * DC, v);
+      } else {
+        tmem_ld16(tmem + lane_base + C::COL_DQ + cg * DC, v);
+      }
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_dqd);
+      if (C::LATE && t > 0 && !mbar_wait(bar_stg, (t - 1) & 1u)) return false;  // staging tile read by the TMA unit
+      constexpr int CH = DC / 4;             // 16-byte chunks this thread owns
+      const int box = (cg * DC) / 32;        // which [128][32] box
+      const int ch0 = ((cg * DC) % 32) / 4;  // first chunk inside the 128-byte row
+      unsigned char* stg = gen + C::OFF_STG + box * kHalfBytes + r * 128;
+#pragma unroll
+      for (int t4 = 0; t4 < CH; ++t4)
+        *reinterpret_cast<uint4*>(stg + (((ch0 + t4) ^ (r & 7)) << 4)) =
+            make_uint4(v[4 * t4], v[4 * t4 + 1], v[4 * t4 + 2], v[4 * t4 + 3]);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_stgf);
+      return true;
+    };
     for (int it = 0; it < iters && ok; ++it) {
       const int i = i0 + it;
       const int qrow = i * 128 + r;
@@ -313,12 +378,10 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       const float lse2 = vq ? p.lse[static_cast<int64_t>(bh) * p.S + qrow] * kLog2e : 0.f;
       const float dlt = vq ? p.delta[static_cast<int64_t>(bh) * p.S + qrow] : 0.f;
       if (!mbar_wait(bar_sdp, it & 1u)) {
-        if (lane == 0) atomicExch(p.status, kErrBwdCompute);
         ok = false;
         break;
       }
       tc_fence_after();
-      if (warp == 2 && lane == 0) TR(5, it);
       const bool diag = p.causal && (i == j);
       const bool masked = diag || (j * 128 + 128 > p.S) || (i * 128 + 128 > p.S);  // uniform over the CTA
       const int col0 = cg * 32;
@@ -329,7 +392,6 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sfree);  // S and dP columns may be overwritten
-      if (warp == 2 && lane == 0) TR(13, it);
       uint32_t pk[16], dk[16];
       if (!masked) {
 #pragma unroll
@@ -355,13 +417,12 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
           dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
         }
       }
-      if (warp == 2 && lane == 0) TR(9, it);
-      if (it > 0 && !mbar_wait(bar_stg, (it - 1) & 1u)) {  // the previous dQ tile has left the P | dS area
-        if (lane == 0) atomicExch(p.status, kErrBwdCompute);
-        ok = false;
-        break;
+      // P | dS may be rewritten once the previous tile's MMAs have read them (LATE: bar_dqf of that tile;
+      // otherwise: the TMA unit has read the dQ tile that was staged there)
+      if (it > 0) {
+        ok = C::LATE ? mbar_wait(bar_dqf, (it - 1) & 1u) : mbar_wait(bar_stg, (it - 1) & 1u);
+        if (!ok) break;
       }
-      if (warp == 2 && lane == 0) TR(10, it);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const uint32_t off = ps_chunk_off(r, (col0 >> 3) + t);
@@ -371,42 +432,14 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pds);
-      if (warp == 2 && lane == 0) TR(6, it);
-      // this tile's dQ contribution: TMEM -> registers, release the columns, then reduce into the accumulator
-      if (!mbar_wait(bar_dqf, it & 1u)) {
-        if (lane == 0) atomicExch(p.status, kErrBwdCompute);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      if (warp == 2 && lane == 0) TR(7, it);
-      uint32_t v[DC];
-      if constexpr (DC == 32) {
-        tmem_ld32(tmem + lane_base + C::COL_DQ + cg * DC, v);
+      if (C::LATE) {
+        if (it > 0) ok = drain(it - 1, false);  // bar_dqf of tile it-1 was waited for above
       } else {
-        tmem_ld16(tmem + lane_base + C::COL_DQ + cg * DC, v);
+        ok = drain(it, true);
       }
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_dqd);
-      if (warp == 2 && lane == 0) TR(8, it);
-      // Stage the fp32 tile in the P | dS area (both are idle once bar_dqf fired) as [128 rows][32 floats]
-      // boxes with the 128-byte swizzle, then let the TMA unit add it into the dQ accumulator: whole 128-byte
-      // lines per request instead of one 16-byte atomic per thread, and rows past S are clipped by the map.
-      {
-        constexpr int CH = DC / 4;                  // 16-byte chunks this thread owns
-        const int box = (cg * DC) / 32;             // which [128][32] box
-        const int ch0 = ((cg * DC) % 32) / 4;       // first chunk inside the 128-byte row
-        unsigned char* stg = gen + C::OFF_P + box * kHalfBytes + r * 128;
-#pragma unroll
-        for (int t = 0; t < CH; ++t)
-          *reinterpret_cast<uint4*>(stg + (((ch0 + t) ^ (r & 7)) << 4)) = make_uint4(v[4 * t], v[4 * t + 1], v[4 * t + 2], v[4 * t + 3]);
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_stgf);
     }
+    if (C::LATE && ok && iters > 0) ok = drain(iters - 1, true);
+    if (!ok && lane == 0) atomicExch(p.status, kErrBwdCompute);
     // dK / dV: every MMA was complete when the last bar_dqf fired
     if (ok && iters > 0) {
       const int kvrow = j * 128 + r;
@@ -567,16 +600,16 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
     if (lane == 0) {
       constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
-      const uint32_t sQ = base + C::OFF_Q, sP = base + C::OFF_P;
+      const uint64_t dQ = base_k(base + C::OFF_Q), dP = base_k(base + C::OFF_P);
       auto issue_s = [&](int jt) -> bool {
         const int s = jt & 1;
         const uint32_t ph = (jt >> 1) & 1u;
         if (!mbar_wait(bar_kf(s), ph)) return false;
         if (jt >= 2 && !mbar_wait(bar_sr(s), ((jt - 2) >> 1) & 1u)) return false;
         tc_fence_after();
-        const uint32_t sK = base + C::OFF_K + s * C::TILE_BYTES;
+        const uint64_t dK = base_k(base + C::OFF_K + s * C::TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S + s * 128, desc_k(sQ, k), desc_k(sK, k), id_s, k > 0);
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S + s * 128, desc_k(dQ, k), desc_k(dK, k), id_s, k > 0);
         umma_commit(bar_ke(s));
         umma_commit(bar_sf(s));
         return true;
@@ -589,9 +622,9 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
         ok = ok && mbar_wait(bar_pr, jt & 1u) && mbar_wait(bar_vf(s), ph);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sV = base + C::OFF_V + s * C::TILE_BYTES;
+        const uint64_t dV = base_mn(base + C::OFF_V + s * C::TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_O, desc_k(sP, k), desc_mn(sV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_O, desc_k(dP, k), desc_mn(dV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
         umma_commit(bar_ve(s));
         umma_commit(bar_pv);
       }
@@ -824,7 +857,6 @@ int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const fl
   p.ld_dqkv = lay.ld_dqkv;
   p.o_bshd = lay.o_bshd;
   p.status = device_status_ptr();
-  if (getenv("MGB_TRACE")) p.trace = reinterpret_cast<long long*>(strtoull(getenv("MGB_TRACE"), nullptr, 0));  // TEMP
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_bwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_bwd: B*H=%d exceeds 65535", B * H);
   const int64_t n = static_cast<int64_t>(B) * S * H * D;

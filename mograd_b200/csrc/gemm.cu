@@ -180,12 +180,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tc_fence_after();
           const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
           const uint32_t sb = sa + T::A_BYTES;
+          // one descriptor per operand and stage; contraction step k adds a constant to the start-address field
+          const uint64_t a0 = A_MN ? smem_desc_sw128(sa, 64 * BK * 2, 1024) : smem_desc_sw128(sa, 16, 1024);
+          const uint64_t b0 = B_MN ? smem_desc_sw128(sb, 64 * BK * 2, 1024) : smem_desc_sw128(sb, 16, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adesc = A_MN ? smem_desc_sw128(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                        : smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
-            const uint64_t bdesc = B_MN ? smem_desc_sw128(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024)
-                                        : smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t adesc = a0 + static_cast<uint64_t>((k * (A_MN ? UMMA_K * 128 : UMMA_K * 2)) >> 4);
+            const uint64_t bdesc = b0 + static_cast<uint64_t>((k * (B_MN ? UMMA_K * 128 : UMMA_K * 2)) >> 4);
             umma_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
