@@ -242,9 +242,45 @@ __global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ o, con
 
 }  // namespace
 
+// Same reduction for packed 16-byte-aligned rows whose length is a power of two between 8 and 256 elements
+// (bf16) : each thread takes one 16-byte slice, D/V lanes cover a row, a warp covers 32*V/D rows per step.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o, const T* __restrict__ dy,
+                                                        float* __restrict__ delta, int64_t rows, int S, int H, int D,
+                                                        int o_bshd) {
+  constexpr int V = Vec<T>::N;
+  const int lanes_per_row = D / V;
+  const int rows_per_warp = 32 / lanes_per_row;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / lanes_per_row, part = lane % lanes_per_row;
+  const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t row = warp_global * rows_per_warp + sub;
+  float acc = 0.f;
+  if (row < rows) {
+    const int s = static_cast<int>(row % S);
+    const int bh = static_cast<int>(row / S);
+    const int64_t off = o_row_off(o_bshd, bh / H, bh % H, s, S, H, D) + part * V;
+    float a[V], b[V];
+    load_vec(o + off, a);
+    load_vec(dy + off, b);
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc = fmaf(a[e], b[e], acc);
+  }
+  for (int ofs = lanes_per_row >> 1; ofs > 0; ofs >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, ofs);
+  if (row < rows && part == 0) delta[row] = acc;
+}
+
 template <typename T>
 int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, cudaStream_t st) {
   const int64_t rows = static_cast<int64_t>(B) * H * S;
+  constexpr int V = Vec<T>::N;
+  const int lpr = D / V;
+  if (D % V == 0 && lpr >= 1 && lpr <= 32 && (lpr & (lpr - 1)) == 0 && aligned16(o) && aligned16(dy)) {
+    const int rows_per_block = 8 * (32 / lpr);
+    delta_vec_kernel<T><<<static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block), 256, 0, st>>>(
+        static_cast<const T*>(o), static_cast<const T*>(dy), delta, rows, S, H, D, o_bshd);
+    return check_launch("delta_vec_kernel");
+  }
   delta_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(o),
                                                                        static_cast<const T*>(dy), delta, rows, S, H, D,
                                                                        o_bshd);

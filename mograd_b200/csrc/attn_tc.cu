@@ -20,7 +20,7 @@
 // TMEM columns: S 128 | dP 128 | dV D | dK D | dQ D (D = 128: dQ reuses S).
 //
 // Forward, per CTA = one query tile: S_j = Q K_j^T double-buffered in TMEM so
-// the next tile's scores are computed while 4 softmax warps work on this one;
+// the next tile's scores are computed while 8 softmax warps work on this one;
 // P goes to shared memory as bf16, O += P V_j accumulates in TMEM and is
 // rescaled in place when a row maximum moves.
 #include <math.h>
@@ -507,12 +507,13 @@ struct FwdCfg {
   static constexpr int OFF_K = TILE_BYTES;       // 2 stages
   static constexpr int OFF_V = 3 * TILE_BYTES;   // 2 stages
   static constexpr int OFF_P = 5 * TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_P + kPsBytes;
+  static constexpr int OFF_X = OFF_P + kPsBytes;  // row-maximum exchange between the two warps of a quarter
+  static constexpr int OFF_BAR = OFF_X + 2 * 2 * 128 * 4;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int COL_S = 0;    // two buffers of 128 columns
   static constexpr int COL_O = 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 320;  // TMA warp, MMA warp, 8 softmax warps
 };
 
 template <int D>
@@ -551,9 +552,9 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
       mbar_init(bar_vf(s), 1);
       mbar_init(bar_ve(s), 1);
       mbar_init(bar_sf(s), 1);
-      mbar_init(bar_sr(s), 4);
+      mbar_init(bar_sr(s), 8);
     }
-    mbar_init(bar_pr, 4);
+    mbar_init(bar_pr, 8);
     mbar_init(bar_pv, 1);
     mbar_fence_init();
   }
@@ -633,11 +634,16 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
     __syncwarp();
   } else {
     // ------------------------------------------------------------ softmax
+    // 8 warps: TMEM lane quarter = warp % 4; the two warps of a quarter split the 128 key columns (and the D
+    // output columns) in halves and exchange their partial row maxima through shared memory once per tile.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const int qrow = i * 128 + r;
     const float scale_log2 = p.scale * kLog2e;
+    float* xmax = reinterpret_cast<float*>(gen + C::OFF_X);  // [2 parities][2 halves][128 rows]
+    constexpr int DH = D / 2;                                 // output columns this warp owns
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int jt = 0; jt < nkv && ok; ++jt) {
@@ -648,21 +654,31 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
       }
       tc_fence_after();
       const bool diag = p.causal && (jt == i);
-      const int kv0 = jt * 128;
-      // pass 1: row maximum of the kept entries
+      const int kv0 = jt * 128 + half * 64;
+      const bool masked = diag || (jt * 128 + 128 > p.S);  // uniform over the CTA
+      const uint32_t s_cols = tmem + lane_base + C::COL_S + s * 128 + half * 64;
+      // pass 1: maximum of this warp's 64 columns
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(tmem + lane_base + C::COL_S + s * 128 + c0, v);
+        tmem_ld32(s_cols + c0, v);
         tmem_ld_wait();
+        if (!masked) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int kvrow = kv0 + c0 + e;
-          const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
-          mx = fmaxf(mx, keep ? __uint_as_float(v[e]) : -INFINITY);
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kvrow = kv0 + c0 + e;
+            const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
+            mx = fmaxf(mx, keep ? __uint_as_float(v[e]) : -INFINITY);
+          }
         }
       }
+      xmax[(s * 2 + half) * 128 + r] = mx;
+      named_barrier(2, 256);
+      mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * 128 + r]);
       const float m_new = fmaxf(m, mx * scale_log2);
       const float corr = (m == -INFINITY) ? 0.f : ex2(m - m_new);
       // the previous P V product must be complete before P is overwritten or O rescaled
@@ -673,39 +689,49 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
       tc_fence_after();
       if (jt > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 16) {
+        for (int c0 = 0; c0 < DH; c0 += 16) {
           uint32_t o[16];
-          tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
+          tmem_ld16(tmem + lane_base + C::COL_O + half * DH + c0, o);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
-          tmem_st16(tmem + lane_base + C::COL_O + c0, o);
+          tmem_st16(tmem + lane_base + C::COL_O + half * DH + c0, o);
         }
         tmem_st_wait();
       }
       // pass 2: P = exp2(S*scale*log2e - m_new) -> bf16 in shared memory
       float rs = 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t v[32];
-        tmem_ld32(tmem + lane_base + C::COL_S + s * 128 + c0, v);
+        tmem_ld32(s_cols + c0, v);
         tmem_ld_wait();
         uint32_t pk[16];
+        if (!masked) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kvrow = kv0 + c0 + e + u;
-            const bool keep = kvrow < p.S && (!diag || kvrow <= qrow) && m_new != -INFINITY;
-            pv[u] = keep ? ex2(fmaf(__uint_as_float(v[e + u]), scale_log2, -m_new)) : 0.f;
-            rs += pv[u];
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(v[e]), scale_log2, -m_new));
+            const float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), scale_log2, -m_new));
+            rs += p0 + p1;
+            pk[e >> 1] = pack_bf16x2(p0, p1);
           }
-          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float pv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int kvrow = kv0 + c0 + e + u;
+              const bool keep = kvrow < p.S && (!diag || kvrow <= qrow) && m_new != -INFINITY;
+              pv[u] = keep ? ex2(fmaf(__uint_as_float(v[e + u]), scale_log2, -m_new)) : 0.f;
+              rs += pv[u];
+            }
+            pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+          }
         }
 #pragma unroll
         for (int t = 0; t < 4; ++t)
-          *reinterpret_cast<uint4*>(gen + C::OFF_P + ps_chunk_off(r, (c0 >> 3) + t)) =
+          *reinterpret_cast<uint4*>(gen + C::OFF_P + ps_chunk_off(r, ((half * 64 + c0) >> 3) + t)) =
               make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
       }
       l = l * corr + rs;
@@ -723,18 +749,24 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
       if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
     } else {
       tc_fence_after();
+      // the two halves hold partial row sums under the same maximum
+      float* xsum = xmax;  // all tiles are done: reuse the exchange buffer
+      named_barrier(2, 256);
+      xsum[half * 128 + r] = l;
+      named_barrier(2, 256);
+      l += xsum[(half ^ 1) * 128 + r];
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int qr = qrow < p.S ? qrow : 0;
       bf16* orow = p.out + (p.o_bshd ? ((static_cast<int64_t>(b) * p.S + qr) * p.H + h) * D
-                                     : (static_cast<int64_t>(bh) * p.S + qr) * D);
+                                     : (static_cast<int64_t>(bh) * p.S + qr) * D) + half * DH;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem + lane_base + C::COL_O + c0, v);
+      for (int c0 = 0; c0 < DH; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem + lane_base + C::COL_O + half * DH + c0, v);
         tmem_ld_wait();
         if (qrow < p.S) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 8) {
+          for (int e = 0; e < 16; e += 8) {
             uint4 o;
             o.x = pack_bf16x2(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
             o.y = pack_bf16x2(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
@@ -744,7 +776,7 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
           }
         }
       }
-      if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
+      if (half == 0 && qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
     }
   }
   tc_fence_before();

@@ -309,7 +309,11 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
 // row is being reduced.  A lane only ever reads back the 16-byte chunks it
 // copied itself, so the ring needs no barrier.  Registers hold just gamma and
 // the fp32 dgamma / dbeta partials.
-constexpr int kLnStages = 3;
+// Row slots per warp: three for narrow slices; two when a slice is 4 chunks wide, so that two CTAs still fit per SM.
+template <int CHUNKS>
+struct LnStages {
+  static constexpr int N = CHUNKS >= 4 ? 2 : 3;
+};
 
 __device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(gptr) : "memory");
@@ -358,6 +362,7 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
   constexpr int V = Vec<T>::N;
   using S = Shape<WPR>;
   constexpr int SLOT = CHUNKS * 512;  // bytes of one array (x or dy) of one row slot of one warp
+  constexpr int kLnStages = LnStages<CHUNKS>::N;
   constexpr bool KEEP = CHUNKS * V <= 16;
   extern __shared__ __align__(16) unsigned char dsm[];
   float* fold = reinterpret_cast<float*>(dsm);                       // [2][cols]
@@ -563,7 +568,7 @@ int launch_bwd(const T* dy, const T* x, const T* g, const T* resid, T* dx, float
                float eps, bool vec, int grid, cudaStream_t st) {
   constexpr int TH = Shape<WPR>::THREADS;
   const size_t fold_bytes = round_up(static_cast<size_t>(2 * cols) * sizeof(float), 16);
-  const size_t pipe_smem = fold_bytes + static_cast<size_t>(Shape<WPR>::WARPS) * kLnStages * 2 * CHUNKS * 512;
+  const size_t pipe_smem = fold_bytes + static_cast<size_t>(Shape<WPR>::WARPS) * LnStages<CHUNKS>::N * 2 * CHUNKS * 512;
   if (vec && pipe_smem + 1024 <= static_cast<size_t>(max_smem_optin())) {
     const size_t smem = pipe_smem;
     auto k = ln_bwd_pipe_kernel<T, WPR, CHUNKS>;
