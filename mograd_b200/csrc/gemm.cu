@@ -9,7 +9,7 @@
 //     dW = dY^T . X : A = dY viewed [n][m] (MN-major), B = X viewed [k][m] (MN-major)
 // so no operand is ever transposed in memory.  Per CTA: warp 0 issues TMA
 // loads of 128-byte-swizzled tiles into a shared-memory ring, warp 1 issues
-// UMMA 128xBNx16 instructions into one of two TMEM accumulators, warps 2-5
+// UMMA 128xBNx16 instructions into one of two TMEM accumulators, warps 2-9
 // drain the other accumulator (tcgen05.ld -> bias / ReLU -> bf16 -> global),
 // so the epilogue of tile t overlaps the main loop of tile t+1.  Tiles whose
 // output is small next to the contraction length (dW) are split along the
@@ -31,7 +31,7 @@ using bf16 = __nv_bfloat16;
 constexpr int BM = 128;
 constexpr int BK = 64;     // bf16 elements per stage along the contraction = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kGemmThreads = 320;  // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-9 column sums of A (db)
+constexpr int kGemmThreads = 448;  // warp 0 TMA, 1 MMA, 2-9 epilogue, 10-13 column sums of A (db)
 constexpr int kMaxSplits = 16;
 
 enum : int { kErrTmaWait = 101, kErrMmaWait = 102, kErrEpiWait = 103 };
@@ -64,6 +64,131 @@ struct GemmParams {
   int* status;
 };
 
+// Drains one half (chalf) of a 128 x BN fp32 accumulator: TMEM -> registers -> (+ bias, ReLU, ReLU-backward
+// mask, + residual) -> bf16 -> global, or fp32 partial tile when the contraction is split.  `row` is the output
+// row of this thread, t_row the TMEM address of its lane at the accumulator's first column.
+template <int BN>
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_row, int row, int n_blk, int split,
+                                                  int chalf) {
+  const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
+  const bool mask_vec = (p.ldm & 7) == 0 && (reinterpret_cast<uintptr_t>(p.relu_mask) & 15u) == 0;
+  const bool res_vec = (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0;
+#pragma unroll 1
+  for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
+    const int col0 = n_blk * BN + c0;
+    if (col0 >= p.N) break;  // warp-uniform
+    uint32_t r[32];
+    tmem_ld32(t_row + c0, r);
+    // epilogue operands of this chunk are fetched while the TMEM load is in flight: 16-byte loads, the
+    // bias slice is the same for every lane (one broadcast transaction)
+    const bool full = col0 + 32 <= p.N;
+    uint4 ep_bias[4], ep_mask[4], ep_res[4];
+    if (p.splits == 1 && full && row < p.M) {
+      if (p.bias && bias_vec) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ep_bias[q] = __ldg(reinterpret_cast<const uint4*>(p.bias + col0) + q);
+      }
+      if (p.relu_mask && mask_vec) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ep_mask[q] = __ldg(src + q);
+      }
+      if (p.residual && res_vec) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.residual + static_cast<int64_t>(row) * p.ldr + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ep_res[q] = src[q];  // may alias the output: plain load
+      }
+    }
+    tmem_ld_wait();
+    if (row < p.M) {
+      if (p.splits > 1) {
+        float* dst = p.partial + (static_cast<int64_t>(split) * p.M + row) * p.N + col0;
+        if (col0 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
+        }
+      } else {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.bias) {
+          if (full && bias_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float bv[8];
+              load_vec(reinterpret_cast<const bf16*>(&ep_bias[j >> 3]), bv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[j + e] += bv[e];
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+          }
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        }
+        if (p.relu_mask) {
+          if (full && mask_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float mv[8];
+              load_vec(reinterpret_cast<const bf16*>(&ep_mask[j >> 3]), mv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[j + e] = mv[e] > 0.f ? v[j + e] : 0.f;
+            }
+          } else {
+            const bf16* mk = p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] = __bfloat162float(mk[j]) > 0.f ? v[j] : 0.f;
+          }
+        }
+        if (p.residual) {
+          if (full && res_vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float rv[8];
+              load_vec(reinterpret_cast<const bf16*>(&ep_res[j >> 3]), rv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[j + e] += rv[e];
+            }
+          } else {
+            const bf16* rs = p.residual + static_cast<int64_t>(row) * p.ldr + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
+          }
+        }
+        bf16* dst = p.d + static_cast<int64_t>(row) * p.ldd + col0;
+        if (col0 + 32 <= p.N && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(v[j], v[j + 1]);
+            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+            *reinterpret_cast<uint4*>(dst + j) = o;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+      }
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -90,7 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 8);
     }
     mbar_fence_init();
   }
@@ -199,13 +324,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
     }
     __syncwarp();
-  } else if (warp >= 6) {
+  } else if (warp >= 10) {
     // ------------------------------------------- row sums of A (bias gradient)
     // Only used with an MN-major A (dW = dY^T X, A = dY): every stage's A tile
     // is [BK rows of the contraction][128 output rows], so the sum over the
     // contraction of output row t is a column sum of the tile in shared memory.
     if (A_MN && p.rowsum_partial) {
-      const int t = threadIdx.x - 6 * 32;  // 0..127: output row within the tile
+      const int t = threadIdx.x - 10 * 32;  // 0..127: output row within the tile
       const uint32_t col_off = (t >> 6) * (64 * BK * 2);
       const int chunk = (t & 63) >> 3, elem = t & 7;
       int stage = 0;
@@ -260,90 +385,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        const int col0 = n_blk * BN + c0;
-        if (col0 >= p.N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld32(t_row + c0, r);
-        tmem_ld_wait();
-        if (row < p.M) {
-          if (p.splits > 1) {
-            float* dst = p.partial + (static_cast<int64_t>(split) * p.M + row) * p.N + col0;
-            if (col0 + 32 <= p.N && (p.N & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
-            }
-          } else {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            if (p.bias) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
-            }
-            if (p.act == 1) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-            }
-            if (p.relu_mask) {
-              const bf16* mk = p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0;
-              if (col0 + 32 <= p.N && (p.ldm & 7) == 0 && (reinterpret_cast<uintptr_t>(p.relu_mask) & 15u) == 0) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  float mv[8];
-                  load_vec(mk + j, mv);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) v[j + e] = mv[e] > 0.f ? v[j + e] : 0.f;
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N) v[j] = __bfloat162float(mk[j]) > 0.f ? v[j] : 0.f;
-              }
-            }
-            if (p.residual) {
-              const bf16* rs = p.residual + static_cast<int64_t>(row) * p.ldr + col0;
-              if (col0 + 32 <= p.N && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  float rv[8];
-                  load_vec(rs + j, rv);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) v[j + e] += rv[e];
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
-              }
-            }
-            bf16* dst = p.d + static_cast<int64_t>(row) * p.ldd + col0;
-            if (col0 + 32 <= p.N && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(dst + j) = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
-            }
-          }
-        }
-      }
+      drain_accumulator<BN>(p, t_row, row, n_blk, split, (warp - 2) >> 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -356,6 +398,202 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair variant for large products: a cluster of two CTAs computes a 256 x 256 tile with one
+// tcgen05.mma.cta_group::2 per 16 contraction elements.  Each CTA loads only its own 128 rows of A and 128 of the
+// 256 B rows per stage (32 KB instead of 48 KB for the same flops: the L2 -> SM traffic per flop drops by a
+// third, which is what bounds the single-CTA kernel), keeps 128 accumulator rows in its own TMEM and drains
+// them with its own 8 epilogue warps.  Rank 0 issues the MMAs; barriers: full[s] lives in rank 0 and counts the
+// bytes of both CTAs' loads; empty[s] and tfull[a] exist in both CTAs and get one commit each; tempty[a] lives
+// in rank 0 and collects the 16 epilogue warps of the pair.
+struct Tile2 {
+  static constexpr int BN = 256;
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_tc2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmParams p) {
+  using T = Tile2;
+  constexpr int BN = T::BN;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + T::STAGES * T::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (T::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * T::STAGES + 4);
+  unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + T::STAGES * T::STAGE_BYTES +
+                                                                          8 * (2 * T::STAGES + 4));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // rank 0: its producer's arrive.expect_tx (bytes of both CTAs)
+      mbar_init(empty_bar(s), 1);  // one MMA commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 16);              // rank 0: 8 epilogue warps of each CTA
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, T::TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs are initialised before any remote arrival
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  const int tiles_mn = p.num_m * p.num_n;  // num_m counts 256-row blocks here
+  const int total = tiles_mn * p.splits;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total && ok; tile += num_clusters) {
+        const int split = tile / tiles_mn;
+        const int rem = tile - split * tiles_mn;
+        const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+        const int m0 = m_blk * 256 + static_cast<int>(rank) * 128;
+        const int n0 = n_blk * 256 + static_cast<int>(rank) * 128;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            atomicExch(p.status, kErrTmaWait);
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
+          const uint32_t sb = sa + T::A_BYTES;
+          const uint32_t full0 = map_to_cta(full_bar(stage), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) tma_load_2d_2cta(sa + i * (64 * BK * 2), &tma_a, full0, m0 + i * 64, kb * BK);
+          } else {
+            tma_load_2d_2cta(sa, &tma_a, full0, kb * BK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) tma_load_2d_2cta(sb + i * (64 * BK * 2), &tma_b, full0, n0 + i * 64, kb * BK);
+          } else {
+            tma_load_2d_2cta(sb, &tma_b, full0, kb * BK, n0);
+          }
+          if (++stage == T::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (rank 0 only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total && ok; tile += num_clusters, ++local) {
+        const int split = tile / tiles_mn;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u)) {
+          atomicExch(p.status, kErrMmaWait);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            atomicExch(p.status, kErrMmaWait);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
+          const uint32_t sb = sa + T::A_BYTES;
+          const uint64_t a0 = A_MN ? smem_desc_sw128(sa, 64 * BK * 2, 1024) : smem_desc_sw128(sa, 16, 1024);
+          const uint64_t b0 = B_MN ? smem_desc_sw128(sb, 64 * BK * 2, 1024) : smem_desc_sw128(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = a0 + static_cast<uint64_t>((k * (A_MN ? UMMA_K * 128 : UMMA_K * 2)) >> 4);
+            const uint64_t bdesc = b0 + static_cast<uint64_t>((k * (B_MN ? UMMA_K * 128 : UMMA_K * 2)) >> 4);
+            umma_ss_2cta(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_2cta(map_to_cta(empty_bar(stage), 0));  // both CTAs may refill this stage
+          umma_commit_2cta(map_to_cta(empty_bar(stage), 1));
+          if (++stage == T::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) {
+          umma_commit_2cta(map_to_cta(tfull_bar(acc), 0));  // accumulator complete in both CTAs
+          umma_commit_2cta(map_to_cta(tfull_bar(acc), 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 10) {
+    // the bias-gradient row sums are only fused into the single-CTA kernel: a CTA of rank 1 cannot poll the
+    // full barrier, which lives in rank 0
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    int local = 0;
+    for (int tile = cluster_id; tile < total; tile += num_clusters, ++local) {
+      const int split = tile / tiles_mn;
+      const int rem = tile - split * tiles_mn;
+      const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), acc_phase)) {
+        if (lane == 0) atomicExch(p.status, kErrEpiWait);
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      drain_accumulator<BN>(p, t_row, row, n_blk, split, (warp - 2) >> 2);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  cluster_sync_all();  // no CTA retires while its peer may still signal its barriers or read its shared memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, T::TMEM_COLS);
   }
 }
 
@@ -548,21 +786,51 @@ int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st)
   return check_launch("gemm_tc_kernel");
 }
 
+template <bool A_MN, bool B_MN>
+int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st) {
+  using T = Tile2;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, a, 64, A_MN ? BK : 128)) return MGB_ECUDA;
+  if (!make_map(&mb, b, 64, B_MN ? BK : 128)) return MGB_ECUDA;
+  auto kern = gemm_tc2_kernel<A_MN, B_MN>;
+  static bool attr_done = false;
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done || attr_dev != dev) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(MGB_ECUDA, "gemm smem opt-in (%d B): %s", T::SMEM_BYTES, cudaGetErrorString(e));
+    attr_done = true;
+    attr_dev = dev;
+  }
+  const int total = p.num_m * p.num_n * p.splits;
+  const int max_clusters = sm_count() / 2;
+  const int clusters = total < max_clusters ? total : max_clusters;
+  kern<<<2 * clusters, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
+  return check_launch("gemm_tc2_kernel");
+}
+
 // D[M,N] = A . B^T style product on tensor cores; operands described as they lie in memory.
 // rowsum_out (A_MN only): bf16[M] = sum over the contraction of A(i, :), produced inside the same kernel.
 template <bool A_MN, bool B_MN>
 int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epilogue& ep, bf16* rowsum_out, int64_t M,
             int64_t N, int64_t K, void* ws, size_t ws_bytes, bool allow_split, cudaStream_t st) {
   const int BN = choose_bn(N);
+  // CTA pairs (256 x 256 tiles) for products large enough to fill the GPU with them and with a long contraction
+  // (measured: with 12 k-blocks per tile the pair's cluster-wide accumulator hand-off costs more than the saved
+  // L2 traffic; from 32 k-blocks on the pair wins); db is fused only in the single-CTA kernel
+  const bool pair = !rowsum_out && BN == 256 && M >= 512 && K >= 32 * BK &&
+                    ((M + 255) / 256) * ((N + 255) / 256) >= sm_count() / 4;
+  const int bm = pair ? 256 : BM;
   GemmParams p{};
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
-  p.num_m = static_cast<int>((M + BM - 1) / BM);
+  p.num_m = static_cast<int>((M + bm - 1) / bm);
   p.num_n = static_cast<int>((N + BN - 1) / BN);
   p.num_kb = static_cast<int>((K + BK - 1) / BK);
   const bool plain = !ep.relu_mask && !ep.residual;
-  p.splits = (allow_split && plain) ? choose_splits(M, N, K, BN) : 1;
+  p.splits = (allow_split && plain && !pair) ? choose_splits(M, N, K, BN) : 1;
   size_t ws_used = 0;
   if (rowsum_out) {  // the row-sum partials sit at the start of the workspace
     if (!ws || ws_bytes < rowsum_bytes(M)) return fail(MGB_EWORKSPACE, "gemm: workspace too small for the bias gradient");
@@ -584,7 +852,8 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   p.ldr = ep.ldr;
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "gemm: device status word unavailable");
-  int rc = BN == 256 ? launch_tc<256, A_MN, B_MN>(a, b, p, st) : launch_tc<128, A_MN, B_MN>(a, b, p, st);
+  int rc = pair ? launch_tc2<A_MN, B_MN>(a, b, p, st)
+                : (BN == 256 ? launch_tc<256, A_MN, B_MN>(a, b, p, st) : launch_tc<128, A_MN, B_MN>(a, b, p, st));
   if (rc != MGB_OK) return rc;
   if (p.splits > 1) {
     const int64_t total = M * N;

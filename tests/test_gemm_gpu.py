@@ -167,3 +167,22 @@ def test_db_inside_dw_gemm_tall(cuda, oracle):
     import torch
 
     assert torch.equal(db, db2) and torch.equal(dw, dw2)
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 320), (4096, 512, 1024), (1024, 4096, 1024), (1100, 2300, 200)])
+def test_cta_pair_kernel(cuda, oracle, M, N, K):
+    """Shapes large enough for the two-CTA (256 x 256 tile) kernel, in all three operand-major combinations,
+    including ragged edges where the second CTA's rows fall partly or wholly outside the matrix."""
+    from mograd_b200 import dispatch as Kx
+
+    x, w, b, dy = _mk(M, N, K, "bf16", M + K)
+    res = bf16_round(np.random.default_rng(1).standard_normal((M, N)).astype(np.float32))
+    y = Kx.matmul_bias_strided(_dev(x, cuda, "bf16"), _dev(w, cuda, "bf16"), _dev(b, cuda, "bf16"), act=1,
+                               residual=_dev(res, cuda, "bf16"))
+    assert _status() == 0
+    assert rel_err(y.float().cpu().numpy(), np.maximum(oracle.matmul_bias_bt(x, w, b), 0) + res) <= TOL_BF16
+    wdx, wdw, _ = oracle.matmul_bias_bt_bwd(dy, x, w, need_db=False)
+    dx, dw, _ = Kx.matmul_bias_bt_bwd(_dev(dy, cuda, "bf16"), _dev(x, cuda, "bf16"), _dev(w, cuda, "bf16"), need_db=False)
+    assert _status() == 0
+    assert rel_err(dx.float().cpu().numpy(), wdx) <= TOL_BF16
+    assert rel_err(dw.float().cpu().numpy(), wdw) <= TOL_BF16
