@@ -42,8 +42,9 @@ struct Tile {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STG_BYTES = 2 * 128 * 128;  // two [128][64] bf16 output boxes, one per column half
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + BAR_BYTES + 1024;  // + alignment slack
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -61,22 +62,43 @@ struct GemmParams {
   const bf16* residual;        // optional M x N added last (may alias d), splits == 1 only
   int64_t ldr;
   float* rowsum_partial;       // optional [splits][M]: sum over the contraction of A(i, :) (db inside the dW GEMM)
+  int d_tma;                   // output leaves through the TMA unit (tensor map valid)
   int* status;
 };
 
+// Where the epilogue of one CTA puts its output tile.
+struct EpilogueOut {
+  const CUtensorMap* tm_d;  // map over the bf16 output (box 64 x 128), or nullptr: direct stores
+  unsigned char* stg;       // this column-half's 16 KB staging box in shared memory (generic address)
+  uint32_t stg_s;           // same, shared address
+  int m0;                   // first output row of this CTA's 128-row tile
+  int bar_id;               // named barrier of the four warps that share the box
+  bool leader;              // the thread that issues the TMA stores of this half
+};
+
 // Drains one half (chalf) of a 128 x BN fp32 accumulator: TMEM -> registers -> (+ bias, ReLU, ReLU-backward
-// mask, + residual) -> bf16 -> global, or fp32 partial tile when the contraction is split.  `row` is the output
-// row of this thread, t_row the TMEM address of its lane at the accumulator's first column.
+// mask, + residual) -> bf16.  With a tensor map the bf16 tile is staged in shared memory as a 128-byte-swizzled
+// [128 rows][64 columns] box (each thread writes its own row, conflict-free) and leaves through the TMA unit
+// in whole 128-byte lines; otherwise (unaligned output, or fp32 partial tiles of a split contraction) each
+// thread stores its own row.  `row` is the output row of this thread, t_row the TMEM address of its lane at
+// the accumulator's first column.
 template <int BN>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_row, int row, int n_blk, int split,
-                                                  int chalf) {
+                                                  int chalf, const EpilogueOut& eo, int lane_row) {
   const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
   const bool mask_vec = (p.ldm & 7) == 0 && (reinterpret_cast<uintptr_t>(p.relu_mask) & 15u) == 0;
   const bool res_vec = (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0;
+  const bool staged = eo.tm_d != nullptr && p.splits == 1;  // bf16 output boxes; fp32 partial boxes are handled apart
 #pragma unroll 1
   for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
     const int col0 = n_blk * BN + c0;
-    if (col0 >= p.N) break;  // warp-uniform
+    if (col0 >= p.N) break;  // uniform over the four warps of this half
+    const int sub = (c0 >> 5) & 1;  // which 32-column half of the 64-column box
+    if (staged && sub == 0) {
+      // the box may be refilled once the TMA unit has read the previous store out of it
+      if (eo.leader) bulk_wait_read0();
+      named_barrier(eo.bar_id, 128);
+    }
     uint32_t r[32];
     tmem_ld32(t_row + c0, r);
     // epilogue operands of this chunk are fetched while the TMEM load is in flight: 16-byte loads, the
@@ -100,8 +122,24 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
       }
     }
     tmem_ld_wait();
-    if (row < p.M) {
-      if (p.splits > 1) {
+    if (p.splits > 1 && eo.tm_d != nullptr) {
+      // fp32 partial tile of a split contraction: one [128 rows][32 floats] box per chunk through the TMA unit
+      if (eo.leader) bulk_wait_read0();
+      named_barrier(eo.bar_id, 128);
+      unsigned char* brow = eo.stg + lane_row * 128;
+#pragma unroll
+      for (int t = 0; t < 8; ++t)
+        *reinterpret_cast<uint4*>(brow + ((t ^ (lane_row & 7)) << 4)) = make_uint4(r[4 * t], r[4 * t + 1], r[4 * t + 2], r[4 * t + 3]);
+      fence_async_smem();
+      named_barrier(eo.bar_id, 128);
+      if (eo.leader) {
+        tma_store_3d(eo.tm_d, eo.stg_s, col0, eo.m0, split);
+        bulk_commit();
+      }
+      continue;
+    }
+    if (p.splits > 1) {
+      if (row < p.M) {
         float* dst = p.partial + (static_cast<int64_t>(split) * p.M + row) * p.N + col0;
         if (col0 + 32 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
@@ -113,77 +151,102 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
           for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
         }
-      } else {
-        float v[32];
+      }
+      continue;
+    }
+    float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.bias) {
-          if (full && bias_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float bv[8];
-              load_vec(reinterpret_cast<const bf16*>(&ep_bias[j >> 3]), bv);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[j + e] += bv[e];
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
-          }
-        }
-        if (p.act == 1) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-        }
-        if (p.relu_mask) {
-          if (full && mask_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float mv[8];
-              load_vec(reinterpret_cast<const bf16*>(&ep_mask[j >> 3]), mv);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[j + e] = mv[e] > 0.f ? v[j + e] : 0.f;
-            }
-          } else {
-            const bf16* mk = p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] = __bfloat162float(mk[j]) > 0.f ? v[j] : 0.f;
-          }
-        }
-        if (p.residual) {
-          if (full && res_vec) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float rv[8];
-              load_vec(reinterpret_cast<const bf16*>(&ep_res[j >> 3]), rv);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[j + e] += rv[e];
-            }
-          } else {
-            const bf16* rs = p.residual + static_cast<int64_t>(row) * p.ldr + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
-          }
-        }
-        bf16* dst = p.d + static_cast<int64_t>(row) * p.ldd + col0;
-        if (col0 + 32 <= p.N && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) {
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (row < p.M) {
+      if (p.bias) {
+        if (full && bias_vec) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
-            uint4 o;
-            o.x = pack_bf16x2(v[j], v[j + 1]);
-            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-            *reinterpret_cast<uint4*>(dst + j) = o;
+            float bv[8];
+            load_vec(reinterpret_cast<const bf16*>(&ep_bias[j >> 3]), bv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j + e] += bv[e];
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+            if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
         }
+      }
+      if (p.act == 1) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+      }
+      if (p.relu_mask) {
+        if (full && mask_vec) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            float mv[8];
+            load_vec(reinterpret_cast<const bf16*>(&ep_mask[j >> 3]), mv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j + e] = mv[e] > 0.f ? v[j + e] : 0.f;
+          }
+        } else {
+          const bf16* mk = p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] = __bfloat162float(mk[j]) > 0.f ? v[j] : 0.f;
+        }
+      }
+      if (p.residual) {
+        if (full && res_vec) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            float rv[8];
+            load_vec(reinterpret_cast<const bf16*>(&ep_res[j >> 3]), rv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j + e] += rv[e];
+          }
+        } else {
+          const bf16* rs = p.residual + static_cast<int64_t>(row) * p.ldr + col0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
+        }
+      }
+    }
+    if (staged) {
+      // row lane_row of the box, 16-byte chunks (sub * 4 + t) ^ (row & 7)
+      unsigned char* brow = eo.stg + lane_row * 128;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        uint4 o;
+        o.x = pack_bf16x2(v[8 * t], v[8 * t + 1]);
+        o.y = pack_bf16x2(v[8 * t + 2], v[8 * t + 3]);
+        o.z = pack_bf16x2(v[8 * t + 4], v[8 * t + 5]);
+        o.w = pack_bf16x2(v[8 * t + 6], v[8 * t + 7]);
+        *reinterpret_cast<uint4*>(brow + (((sub * 4 + t) ^ (lane_row & 7)) << 4)) = o;
+      }
+      const bool last_of_box = sub == 1 || col0 + 32 >= p.N;
+      if (last_of_box) {
+        fence_async_smem();
+        named_barrier(eo.bar_id, 128);
+        if (eo.leader) {
+          tma_store_2d(eo.tm_d, eo.stg_s, col0 - sub * 32, eo.m0);  // rows / columns past the matrix are clipped
+          bulk_commit();
+        }
+      }
+    } else if (row < p.M) {
+      bf16* dst = p.d + static_cast<int64_t>(row) * p.ldd + col0;
+      if (col0 + 32 <= p.N && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 o;
+          o.x = pack_bf16x2(v[j], v[j + 1]);
+          o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+          o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+          o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+          *reinterpret_cast<uint4*>(dst + j) = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
       }
     }
   }
@@ -192,11 +255,12 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                   const GemmParams p) {
+                   const __grid_constant__ CUtensorMap tma_d, const GemmParams p) {
   using T = Tile<BN>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + T::STAGES * T::STAGE_BYTES;
+  const uint32_t stg_base = smem_base + T::STAGES * T::STAGE_BYTES;
+  const uint32_t bar_base = stg_base + T::STG_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (T::STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + a); };
@@ -204,7 +268,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t tmem_slot = bar_base + 8u * (2 * T::STAGES + 4);
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + T::STAGES * T::STAGE_BYTES +
-                                                                          8 * (2 * T::STAGES + 4));
+                                                                          T::STG_BYTES + 8 * (2 * T::STAGES + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -371,6 +435,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
+    const int chalf = (warp - 2) >> 2;  // the two warps of a lane quarter split the tile's columns
+    EpilogueOut eo;
+    eo.tm_d = p.d_tma ? &tma_d : nullptr;
+    eo.stg = smem_gen + T::STAGES * T::STAGE_BYTES + chalf * (128 * 128);
+    eo.stg_s = stg_base + chalf * (128 * 128);
+    eo.m0 = 0;
+    eo.bar_id = 1 + chalf;
+    eo.leader = (warp == 2 + 4 * chalf) && lane == 0;
     int local = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
       const int split = tile / tiles_mn;
@@ -385,11 +457,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      drain_accumulator<BN>(p, t_row, row, n_blk, split, (warp - 2) >> 2);
+      eo.m0 = m_blk * BM;
+      drain_accumulator<BN>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
+    if (eo.leader) bulk_wait0();  // every output box has been written before the CTA retires
   }
 
   // ------------------------------------------------------------------ teardown
@@ -415,20 +489,22 @@ struct Tile2 {
   static constexpr int B_BYTES = 128 * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = 6;
+  static constexpr int STG_BYTES = 2 * 128 * 128;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + BAR_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tma_d, const GemmParams p) {
   using T = Tile2;
   constexpr int BN = T::BN;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + T::STAGES * T::STAGE_BYTES;
+  const uint32_t stg_base = smem_base + T::STAGES * T::STAGE_BYTES;
+  const uint32_t bar_base = stg_base + T::STG_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (T::STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + a); };
@@ -436,7 +512,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   const uint32_t tmem_slot = bar_base + 8u * (2 * T::STAGES + 4);
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + T::STAGES * T::STAGE_BYTES +
-                                                                          8 * (2 * T::STAGES + 4));
+                                                                          T::STG_BYTES + 8 * (2 * T::STAGES + 4));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
 
@@ -567,6 +643,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs)
     const int quarter = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    EpilogueOut eo;
+    eo.tm_d = p.d_tma ? &tma_d : nullptr;
+    eo.stg = smem_gen + T::STAGES * T::STAGE_BYTES + chalf * (128 * 128);
+    eo.stg_s = stg_base + chalf * (128 * 128);
+    eo.m0 = 0;
+    eo.bar_id = 1 + chalf;
+    eo.leader = (warp == 2 + 4 * chalf) && lane == 0;
     int local = 0;
     for (int tile = cluster_id; tile < total; tile += num_clusters, ++local) {
       const int split = tile / tiles_mn;
@@ -581,11 +665,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       tc_fence_after();
       const int row = m_blk * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      drain_accumulator<BN>(p, t_row, row, n_blk, split, (warp - 2) >> 2);
+      eo.m0 = m_blk * 256 + static_cast<int>(rank) * 128;
+      drain_accumulator<BN>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
     }
+    if (eo.leader) bulk_wait0();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -780,9 +866,17 @@ int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st)
     attr_done = true;
     attr_dev = dev;
   }
+  CUtensorMap md = ma;  // placeholder when the output cannot take TMA stores
+  if (p.d_tma && p.splits == 1 && !make_map(&md, Operand{p.d, p.M, p.N, p.ldd}, 64, 128)) return MGB_ECUDA;
+  if (p.d_tma && p.splits > 1) {  // fp32 partial tiles [splits][M][N]
+    const uint64_t dims[3] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.splits)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(p.N) * 4, static_cast<uint64_t>(p.M) * p.N * 4};
+    const uint32_t box[3] = {32, 128, 1};
+    if (!encode_tmap_f32(&md, p.partial, 3, dims, strides, box)) return MGB_ECUDA;
+  }
   const int total = p.num_m * p.num_n * p.splits;
   const int grid = total < sm_count() ? total : sm_count();
-  kern<<<grid, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
+  kern<<<grid, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, md, p);
   return check_launch("gemm_tc_kernel");
 }
 
@@ -803,10 +897,12 @@ int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st
     attr_done = true;
     attr_dev = dev;
   }
+  CUtensorMap md = ma;
+  if (p.d_tma && !make_map(&md, Operand{p.d, p.M, p.N, p.ldd}, 64, 128)) return MGB_ECUDA;
   const int total = p.num_m * p.num_n * p.splits;
   const int max_clusters = sm_count() / 2;
   const int clusters = total < max_clusters ? total : max_clusters;
-  kern<<<2 * clusters, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
+  kern<<<2 * clusters, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, md, p);
   return check_launch("gemm_tc2_kernel");
 }
 
@@ -850,6 +946,7 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   p.ldm = ep.ldm;
   p.residual = static_cast<const bf16*>(ep.residual);
   p.ldr = ep.ldr;
+  p.d_tma = p.splits == 1 ? (aligned16(d) && (ldd % 8 == 0)) : (aligned16(p.partial) && (N % 4 == 0));
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "gemm: device status word unavailable");
   int rc = pair ? launch_tc2<A_MN, B_MN>(a, b, p, st)
