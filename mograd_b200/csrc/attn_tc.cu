@@ -12,12 +12,17 @@
 // Backward, per CTA = one key tile j of one (batch, head), looping over query
 // tiles i (i >= j when causal; tiles above the diagonal are skipped):
 //     S  = Q_i K_j^T          dP = dO_i V_j^T              (tensor cores -> TMEM)
-//     P  = exp2(S*scale*log2e - lse*log2e),  dS = P*(dP - delta)*scale
+//     P  = exp2(S*scale*log2e - lse*log2e),  dS' = P*(dP - delta)
 //                                                          (16 warps, TMEM -> bf16 in shared)
-//     dV += P^T dO_i          dK += dS^T Q_i               (accumulate in TMEM over i)
-//     dQ_i partial = dS K_j   -> fp32 vector reductions into the dQ accumulator
-// dK / dV leave TMEM once per CTA; dQ is converted to bf16 by a last kernel.
-// TMEM columns: S 128 | dP 128 | dV D | dK D | dQ D (D = 128: dQ reuses S).
+//     dV += P^T dO_i          dK' += dS'^T Q_i             (accumulate in TMEM over i)
+//     dQ'_i partial = dS' K_j -> staged in shared memory, added into the fp32 dQ
+//                                accumulator by one TMA tensor reduce per tile
+// The softmax scale is left out of dS' and applied once: to dK when it leaves
+// TMEM, to dQ when the last kernel converts the accumulator to bf16.
+// dK / dV leave TMEM once per CTA.
+// TMEM columns: S 128 | dP 128 | dV D | dK D, then dQ: its own D columns for
+// D = 64 (drained one tile late, behind the next tile's MMAs); for D = 128 the
+// 512 columns are full, so dQ is accumulated over the dP columns once dP is read.
 //
 // Forward, per CTA = one query tile: S_j = Q K_j^T double-buffered in TMEM so
 // the next tile's scores are computed while 8 softmax warps work on this one;
