@@ -306,7 +306,7 @@ def cpu_baseline(cfg, budget_s=20.0):
     from oracle import ref_model
 
     oracle.build()
-    cores = os.cpu_count() or 1
+    cores = int(os.environ.get("OMP_NUM_THREADS", "0")) or (os.cpu_count() or 1)
     rng = np.random.default_rng(0)
     if cfg["kind"] == "mlp":
         dims = cfg["dims"]
@@ -375,6 +375,18 @@ def main():
     ap.add_argument("--case", default=None, help="run one small kernel case --reps times and exit (for profiling)")
     ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
+    # Libraries (NCCL's version banner, for one) write to stdout; the contract is one JSON line there.  Everything
+    # but that line goes to stderr: fd 1 is pointed at fd 2 until emit() restores it.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
+
     if args.case:
         import torch
         import mograd_b200
@@ -394,6 +406,9 @@ def main():
                             parallelism=f"dp{args.gpus}", l2="working set (weights, grads, AdamW state, activations) "
                                                              "exceeds the 126 MB L2 every step"))
 
+    # the CPU legs use every host core (torchrun presets OMP_NUM_THREADS=1; the OpenMP runtime reads it when the
+    # oracle library is first loaded, which happens after this line)
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     if args.impl == "reference":
         if rank != 0:
             return 0
@@ -412,7 +427,7 @@ def main():
                     e2e=dict(value=v, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                     note="reference = CPU restatement of mograd's math (oracle/); mograd itself is Mojo/MAX and has no "
                          "CPU runtime; ms_per_step extrapolates the sample to the full batch")
-        print(json.dumps(line), flush=True)
+        emit(line)
         return 0
 
     import torch
@@ -486,7 +501,7 @@ def main():
             if not args.no_kernels:
                 line["kernels"] = standalone_kernels(peaks, device)
             line["cpu_baseline"] = cpu_baseline(cfg)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

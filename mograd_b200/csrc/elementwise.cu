@@ -102,17 +102,59 @@ template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
     adamw_kernel(T* __restrict__ w, const T* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                  float* __restrict__ master, int64_t n, float lr, float b1, float b2, float eps, float wd, float inv_bc1,
-                 float inv_bc2, float grad_scale) {
+                 float inv_bc2, float grad_scale, int vec) {
+  constexpr int V = Vec<T>::N;  // elements per 16-byte access of the parameter type
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kEwThreads;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x; i < n; i += stride) {
-    const float gi = to_f32(g[i]) * grad_scale;
-    const float mi = b1 * m[i] + (1.f - b1) * gi;
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const float decay = wd > 0.f ? 1.f - lr * wd : 1.f;
+  auto update = [&](float gi, float& mi, float& vi, float& wi) {
+    gi *= grad_scale;
+    mi = b1 * mi + (1.f - b1) * gi;
+    vi = b2 * vi + (1.f - b2) * gi * gi;
+    wi = wi * decay - lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+  };
+  const int64_t nv = vec ? n / V : 0;
+  for (int64_t i = tid; i < nv; i += stride) {
+    // every stream is read with 16-byte loads issued before any arithmetic
+    float gf[V], wf[V];
+    float4 mq[V / 4], vq[V / 4], wq[V / 4];
+    load_vec(g + i * V, gf);
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      mq[q] = reinterpret_cast<const float4*>(m)[i * (V / 4) + q];
+      vq[q] = reinterpret_cast<const float4*>(v)[i * (V / 4) + q];
+      if (master) wq[q] = reinterpret_cast<const float4*>(master)[i * (V / 4) + q];
+    }
+    if (master) {
+#pragma unroll
+      for (int q = 0; q < V / 4; ++q) {
+        wf[4 * q] = wq[q].x;
+        wf[4 * q + 1] = wq[q].y;
+        wf[4 * q + 2] = wq[q].z;
+        wf[4 * q + 3] = wq[q].w;
+      }
+    } else {
+      load_vec(w + i * V, wf);
+    }
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      update(gf[4 * q], mq[q].x, vq[q].x, wf[4 * q]);
+      update(gf[4 * q + 1], mq[q].y, vq[q].y, wf[4 * q + 1]);
+      update(gf[4 * q + 2], mq[q].z, vq[q].z, wf[4 * q + 2]);
+      update(gf[4 * q + 3], mq[q].w, vq[q].w, wf[4 * q + 3]);
+      reinterpret_cast<float4*>(m)[i * (V / 4) + q] = mq[q];
+      reinterpret_cast<float4*>(v)[i * (V / 4) + q] = vq[q];
+      if (master)
+        reinterpret_cast<float4*>(master)[i * (V / 4) + q] = make_float4(wf[4 * q], wf[4 * q + 1], wf[4 * q + 2], wf[4 * q + 3]);
+    }
+    store_vec(w + i * V, wf);
+  }
+  for (int64_t i = nv * V + tid; i < n; i += stride) {
+    float mi = m[i], vi = v[i];
+    float wi = master ? master[i] : to_f32(w[i]);
+    update(to_f32(g[i]), mi, vi, wi);
     m[i] = mi;
     v[i] = vi;
-    float wi = master ? master[i] : to_f32(w[i]);
-    if (wd > 0.f) wi *= (1.f - lr * wd);
-    wi -= lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
     if (master) master[i] = wi;
     w[i] = from_f32<T>(wi);
   }
@@ -221,9 +263,10 @@ MGB_EXPORT int mograd_b200_adamw_step(void* w, const void* g, float* m, float* v
   const float inv_bc1 = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
   const float inv_bc2 = 1.f / (1.f - powf(beta2, static_cast<float>(step)));
   MGB_DTYPE_SWITCH(dtype, "adamw_step", {
-    adamw_kernel<T><<<ew_grid(numel), kEwThreads, 0, st>>>(static_cast<T*>(w), static_cast<const T*>(g), m, v, master,
-                                                          numel, lr, beta1, beta2, eps, weight_decay, inv_bc1, inv_bc2,
-                                                          grad_scale);
+    const int vec = aligned16(w) && aligned16(g) && aligned16(m) && aligned16(v) && (!master || aligned16(master));
+    adamw_kernel<T><<<ew_grid(numel / Vec<T>::N + 1), kEwThreads, 0, st>>>(
+        static_cast<T*>(w), static_cast<const T*>(g), m, v, master, numel, lr, beta1, beta2, eps, weight_decay, inv_bc1,
+        inv_bc2, grad_scale, vec);
   })
   return check_launch("adamw_kernel");
 }

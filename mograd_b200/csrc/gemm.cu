@@ -62,43 +62,53 @@ struct GemmParams {
   const bf16* residual;        // optional M x N added last (may alias d), splits == 1 only
   int64_t ldr;
   float* rowsum_partial;       // optional [splits][M]: sum over the contraction of A(i, :) (db inside the dW GEMM)
-  int d_tma;                   // output leaves through the TMA unit (tensor map valid)
+  int d_vec;                   // output (or fp32 partial) rows take aligned 16-byte stores: staged epilogue
+  int n_fastest;               // tile order: consecutive tiles walk the N blocks of one M block (else the M blocks of one N block)
   int* status;
 };
 
-// Where the epilogue of one CTA puts its output tile.
+// Tile index -> block coordinates.  CTAs that run at the same time hold consecutive tile indices, so the order
+// decides which operand panels they share through L2: walking M first shares one B panel among all CTAs and
+// streams A; walking N first shares each A panel among the CTAs of its row of tiles and keeps all of B hot.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int rem, int& m_blk, int& n_blk) {
+  if (p.n_fastest) {
+    m_blk = rem / p.num_n;
+    n_blk = rem - m_blk * p.num_n;
+  } else {
+    n_blk = rem / p.num_m;
+    m_blk = rem - n_blk * p.num_m;
+  }
+}
+
+// Where one epilogue warp puts its part of the output tile.
 struct EpilogueOut {
-  const CUtensorMap* tm_d;  // map over the bf16 output (box 64 x 128), or nullptr: direct stores
-  unsigned char* stg;       // this column-half's 16 KB staging box in shared memory (generic address)
-  uint32_t stg_s;           // same, shared address
-  int m0;                   // first output row of this CTA's 128-row tile
-  int bar_id;               // named barrier of the four warps that share the box
-  bool leader;              // the thread that issues the TMA stores of this half
+  bool vec;            // staged path: rows leave as whole 128-byte lines
+  unsigned char* stg;  // this column-half's [128 rows][128 bytes] staging box; a warp only touches its own 32 rows
+  int m0;              // first output row of this CTA's 128-row tile
+  int lane;
+  uint64_t policy;
 };
 
 // Drains one half (chalf) of a 128 x BN fp32 accumulator: TMEM -> registers -> (+ bias, ReLU, ReLU-backward
-// mask, + residual) -> bf16.  With a tensor map the bf16 tile is staged in shared memory as a 128-byte-swizzled
-// [128 rows][64 columns] box (each thread writes its own row, conflict-free) and leaves through the TMA unit
-// in whole 128-byte lines; otherwise (unaligned output, or fp32 partial tiles of a split contraction) each
-// thread stores its own row.  `row` is the output row of this thread, t_row the TMEM address of its lane at
-// the accumulator's first column.
+// mask, + residual) -> bf16.  TMEM gives each thread one row, which is the worst shape for global stores, so on
+// the staged path every warp writes its 32 rows of a 64-column box into its own 4 KB slice of shared memory
+// (128-byte swizzle, conflict-free) and reads it back four rows per instruction: each global store instruction
+// then covers four whole 128-byte lines.  Only the warp itself touches its slice, so __syncwarp is the only
+// synchronisation and nothing waits on an asynchronous copy.  fp32 partial tiles of a split contraction take the
+// same route.  Otherwise (unaligned output) each thread stores its own row.  `row` is the output row of this
+// thread, t_row the TMEM address of its lane at the accumulator's first column.
 template <int BN>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_row, int row, int n_blk, int split,
                                                   int chalf, const EpilogueOut& eo, int lane_row) {
   const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
   const bool mask_vec = (p.ldm & 7) == 0 && (reinterpret_cast<uintptr_t>(p.relu_mask) & 15u) == 0;
   const bool res_vec = (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0;
-  const bool staged = eo.tm_d != nullptr && p.splits == 1;  // bf16 output boxes; fp32 partial boxes are handled apart
+  const bool staged = eo.vec && p.splits == 1;  // bf16 output boxes; fp32 partial boxes are handled apart
 #pragma unroll 1
   for (int c0 = chalf * (BN / 2); c0 < (chalf + 1) * (BN / 2); c0 += 32) {
     const int col0 = n_blk * BN + c0;
     if (col0 >= p.N) break;  // uniform over the four warps of this half
     const int sub = (c0 >> 5) & 1;  // which 32-column half of the 64-column box
-    if (staged && sub == 0) {
-      // the box may be refilled once the TMA unit has read the previous store out of it
-      if (eo.leader) bulk_wait_read0();
-      named_barrier(eo.bar_id, 128);
-    }
     uint32_t r[32];
     tmem_ld32(t_row + c0, r);
     // epilogue operands of this chunk are fetched while the TMEM load is in flight: 16-byte loads, the
@@ -122,20 +132,24 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
       }
     }
     tmem_ld_wait();
-    if (p.splits > 1 && eo.tm_d != nullptr) {
-      // fp32 partial tile of a split contraction: one [128 rows][32 floats] box per chunk through the TMA unit
-      if (eo.leader) bulk_wait_read0();
-      named_barrier(eo.bar_id, 128);
+    if (p.splits > 1 && eo.vec) {
+      // fp32 partial tile of a split contraction: this warp's [32 rows][32 floats] box goes through its own
+      // shared-memory slice so that the global stores are whole 128-byte lines
       unsigned char* brow = eo.stg + lane_row * 128;
 #pragma unroll
       for (int t = 0; t < 8; ++t)
         *reinterpret_cast<uint4*>(brow + ((t ^ (lane_row & 7)) << 4)) = make_uint4(r[4 * t], r[4 * t + 1], r[4 * t + 2], r[4 * t + 3]);
-      fence_async_smem();
-      named_barrier(eo.bar_id, 128);
-      if (eo.leader) {
-        tma_store_3d(eo.tm_d, eo.stg_s, col0, eo.m0, split);
-        bulk_commit();
+      __syncwarp();
+      const int c = eo.lane & 7;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int rr = (lane_row & ~31) + it * 4 + (eo.lane >> 3);
+        const uint4 val = *reinterpret_cast<const uint4*>(eo.stg + rr * 128 + ((c ^ (rr & 7)) << 4));
+        const int grow = eo.m0 + rr;
+        if (grow < p.M && col0 + c * 4 < p.N)
+          *reinterpret_cast<uint4*>(p.partial + (static_cast<int64_t>(split) * p.M + grow) * p.N + col0 + c * 4) = val;
       }
+      __syncwarp();
       continue;
     }
     if (p.splits > 1) {
@@ -224,12 +238,22 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
       }
       const bool last_of_box = sub == 1 || col0 + 32 >= p.N;
       if (last_of_box) {
-        fence_async_smem();
-        named_barrier(eo.bar_id, 128);
-        if (eo.leader) {
-          tma_store_2d(eo.tm_d, eo.stg_s, col0 - sub * 32, eo.m0);  // rows / columns past the matrix are clipped
-          bulk_commit();
+        // read the warp's 32 x 64 box back four rows per instruction: every global store is a whole 128-byte line
+        __syncwarp();
+        const int box_col0 = col0 - sub * 32;
+        const int c = eo.lane & 7;
+        const bool col_ok = box_col0 + c * 8 < p.N;  // N is a multiple of 8 on this path
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = (lane_row & ~31) + it * 4 + (eo.lane >> 3);
+          const uint4 val = *reinterpret_cast<const uint4*>(eo.stg + rr * 128 + ((c ^ (rr & 7)) << 4));
+          const int grow = eo.m0 + rr;
+          if (grow < p.M && col_ok) {
+            bf16* dst = p.d + static_cast<int64_t>(grow) * p.ldd + box_col0 + c * 8;
+            st_global_v4_hint(dst, val, eo.policy);  // written once, never re-read here: first out of L2
+          }
         }
+        __syncwarp();  // the slice may be rewritten
       }
     } else if (row < p.M) {
       bf16* dst = p.d + static_cast<int64_t>(row) * p.ldd + col0;
@@ -255,7 +279,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                   const __grid_constant__ CUtensorMap tma_d, const GemmParams p) {
+                   const GemmParams p) {
   using T = Tile<BN>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -306,7 +330,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const int split = tile / tiles_mn;
         const int rem = tile - split * tiles_mn;
-        const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+        int m_blk, n_blk;
+        tile_coords(p, rem, m_blk, n_blk);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -403,7 +428,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const int split = tile / tiles_mn;
         const int rem = tile - split * tiles_mn;
-        const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+        int m_blk, n_blk;
+        tile_coords(p, rem, m_blk, n_blk);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
         float acc = 0.f;
@@ -437,17 +463,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
     const int chalf = (warp - 2) >> 2;  // the two warps of a lane quarter split the tile's columns
     EpilogueOut eo;
-    eo.tm_d = p.d_tma ? &tma_d : nullptr;
+    eo.vec = p.d_vec != 0;
     eo.stg = smem_gen + T::STAGES * T::STAGE_BYTES + chalf * (128 * 128);
-    eo.stg_s = stg_base + chalf * (128 * 128);
     eo.m0 = 0;
-    eo.bar_id = 1 + chalf;
-    eo.leader = (warp == 2 + 4 * chalf) && lane == 0;
+    eo.lane = lane;
+    eo.policy = l2_policy_evict_first();
     int local = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++local) {
       const int split = tile / tiles_mn;
       const int rem = tile - split * tiles_mn;
-      const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+      int m_blk, n_blk;
+        tile_coords(p, rem, m_blk, n_blk);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase)) {
@@ -463,7 +489,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
-    if (eo.leader) bulk_wait0();  // every output box has been written before the CTA retires
   }
 
   // ------------------------------------------------------------------ teardown
@@ -498,7 +523,7 @@ struct Tile2 {
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                    const __grid_constant__ CUtensorMap tma_d, const GemmParams p) {
+                    const GemmParams p) {
   using T = Tile2;
   constexpr int BN = T::BN;
   extern __shared__ unsigned char smem_dyn[];
@@ -551,7 +576,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       for (int tile = cluster_id; tile < total && ok; tile += num_clusters) {
         const int split = tile / tiles_mn;
         const int rem = tile - split * tiles_mn;
-        const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+        int m_blk, n_blk;
+        tile_coords(p, rem, m_blk, n_blk);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
         const int m0 = m_blk * 256 + static_cast<int>(rank) * 128;
@@ -645,17 +671,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int quarter = warp & 3;
     const int chalf = (warp - 2) >> 2;
     EpilogueOut eo;
-    eo.tm_d = p.d_tma ? &tma_d : nullptr;
+    eo.vec = p.d_vec != 0;
     eo.stg = smem_gen + T::STAGES * T::STAGE_BYTES + chalf * (128 * 128);
-    eo.stg_s = stg_base + chalf * (128 * 128);
     eo.m0 = 0;
-    eo.bar_id = 1 + chalf;
-    eo.leader = (warp == 2 + 4 * chalf) && lane == 0;
+    eo.lane = lane;
+    eo.policy = l2_policy_evict_first();
     int local = 0;
     for (int tile = cluster_id; tile < total; tile += num_clusters, ++local) {
       const int split = tile / tiles_mn;
       const int rem = tile - split * tiles_mn;
-      const int n_blk = rem / p.num_m, m_blk = rem - n_blk * p.num_m;
+      int m_blk, n_blk;
+        tile_coords(p, rem, m_blk, n_blk);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase)) {
@@ -671,7 +697,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
     }
-    if (eo.leader) bulk_wait0();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -684,10 +709,45 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 }
 
 // out[r][c] = T(sum_s partial[s][r][c]) (+ bias[c], ReLU); fixed summation order.
+// VEC: four columns per thread (N, ldd multiples of 4, 8-byte aligned output), 32-bit indices.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
     splitk_finalize_kernel(const float* __restrict__ partial, int splits, int M, int N, bf16* __restrict__ out,
                            int64_t ldd, const bf16* __restrict__ bias, int act) {
   const int64_t total = static_cast<int64_t>(M) * N;
+  if (VEC) {
+    const int n4 = N >> 2;
+    const int total4 = static_cast<int>(total >> 2);
+    const float4* src = reinterpret_cast<const float4*>(partial);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += gridDim.x * blockDim.x) {
+      float4 acc = src[i];
+      for (int s = 1; s < splits; ++s) {
+        const float4 t = src[static_cast<int64_t>(s) * total4 + i];
+        acc.x += t.x;
+        acc.y += t.y;
+        acc.z += t.z;
+        acc.w += t.w;
+      }
+      const int r = i / n4, c = (i - r * n4) << 2;
+      if (bias) {
+        acc.x += __bfloat162float(bias[c]);
+        acc.y += __bfloat162float(bias[c + 1]);
+        acc.z += __bfloat162float(bias[c + 2]);
+        acc.w += __bfloat162float(bias[c + 3]);
+      }
+      if (act == 1) {
+        acc.x = fmaxf(acc.x, 0.f);
+        acc.y = fmaxf(acc.y, 0.f);
+        acc.z = fmaxf(acc.z, 0.f);
+        acc.w = fmaxf(acc.w, 0.f);
+      }
+      uint2 o;
+      o.x = pack_bf16x2(acc.x, acc.y);
+      o.y = pack_bf16x2(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(out + static_cast<int64_t>(r) * ldd + c) = o;
+    }
+    return;
+  }
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     float acc = 0.f;
@@ -866,17 +926,9 @@ int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st)
     attr_done = true;
     attr_dev = dev;
   }
-  CUtensorMap md = ma;  // placeholder when the output cannot take TMA stores
-  if (p.d_tma && p.splits == 1 && !make_map(&md, Operand{p.d, p.M, p.N, p.ldd}, 64, 128)) return MGB_ECUDA;
-  if (p.d_tma && p.splits > 1) {  // fp32 partial tiles [splits][M][N]
-    const uint64_t dims[3] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M), static_cast<uint64_t>(p.splits)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(p.N) * 4, static_cast<uint64_t>(p.M) * p.N * 4};
-    const uint32_t box[3] = {32, 128, 1};
-    if (!encode_tmap_f32(&md, p.partial, 3, dims, strides, box)) return MGB_ECUDA;
-  }
   const int total = p.num_m * p.num_n * p.splits;
   const int grid = total < sm_count() ? total : sm_count();
-  kern<<<grid, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, md, p);
+  kern<<<grid, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
   return check_launch("gemm_tc_kernel");
 }
 
@@ -897,12 +949,10 @@ int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st
     attr_done = true;
     attr_dev = dev;
   }
-  CUtensorMap md = ma;
-  if (p.d_tma && !make_map(&md, Operand{p.d, p.M, p.N, p.ldd}, 64, 128)) return MGB_ECUDA;
   const int total = p.num_m * p.num_n * p.splits;
   const int max_clusters = sm_count() / 2;
   const int clusters = total < max_clusters ? total : max_clusters;
-  kern<<<2 * clusters, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, md, p);
+  kern<<<2 * clusters, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
   return check_launch("gemm_tc2_kernel");
 }
 
@@ -936,6 +986,14 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   if (p.splits > 1 && (!ws || ws_bytes < ws_used + splitk_bytes(M, N, p.splits))) p.splits = 1;
   p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
   p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  {
+    // DRAM bytes of the two tile orders: an operand that does not stay in L2 is re-read once per pass over it
+    const double l2 = 64e6, bytes_a = 2.0 * M * K, bytes_b = 2.0 * N * K;
+    const double passes_b = static_cast<double>(p.num_m) * p.num_n / (pair ? sm_count() / 2 : sm_count());
+    const double m_first = bytes_b + (bytes_a <= l2 ? bytes_a : bytes_a * p.num_n);
+    const double n_first = bytes_a + (bytes_b <= l2 ? bytes_b : bytes_b * (passes_b < 1 ? 1 : passes_b));
+    p.n_fastest = n_first < m_first ? 1 : 0;
+  }
   p.d = d;
   p.ldd = ldd;
   p.partial = reinterpret_cast<float*>(static_cast<char*>(ws) + ws_used);
@@ -946,7 +1004,7 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   p.ldm = ep.ldm;
   p.residual = static_cast<const bf16*>(ep.residual);
   p.ldr = ep.ldr;
-  p.d_tma = p.splits == 1 ? (aligned16(d) && (ldd % 8 == 0)) : (aligned16(p.partial) && (N % 4 == 0));
+  p.d_vec = p.splits == 1 ? (aligned16(d) && (ldd % 8 == 0) && (N % 8 == 0)) : (aligned16(p.partial) && (N % 4 == 0));
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "gemm: device status word unavailable");
   int rc = pair ? launch_tc2<A_MN, B_MN>(a, b, p, st)
@@ -954,9 +1012,14 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   if (rc != MGB_OK) return rc;
   if (p.splits > 1) {
     const int64_t total = M * N;
-    int grid = static_cast<int>((total + 255) / 256);
+    const bool vec = (N % 4 == 0) && (ldd % 4 == 0) && (reinterpret_cast<uintptr_t>(d) % 8 == 0) && aligned16(p.partial) &&
+                     total < (int64_t{1} << 31);
+    int grid = static_cast<int>(((vec ? total / 4 : total) + 255) / 256);
     if (grid > sm_count() * 8) grid = sm_count() * 8;
-    splitk_finalize_kernel<<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
+    if (vec)
+      splitk_finalize_kernel<true><<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
+    else
+      splitk_finalize_kernel<false><<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
     rc = check_launch("splitk_finalize_kernel");
     if (rc != MGB_OK) return rc;
   }

@@ -13,6 +13,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace mgb {
 namespace {
@@ -288,6 +289,159 @@ __global__ void __launch_bounds__(kSmallThreads) xent_small_kernel(const XentPar
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Index-label fused forward+backward for long rows, fed by the bulk-copy engine.
+// A persistent CTA (one per SM) owns every gridDim.x-th row.  A producer thread streams whole rows from HBM
+// into one of two shared-memory row buffers with bulk copies; 16 compute warps turn the buffer into
+// (softmax - onehot) * g in place; the producer sends the buffer back to HBM with bulk stores and refills
+// it with the row after next once the stores have read it.  No logit passes through a register on its way in
+// or out, so the compute warps only ever wait on shared memory, and the loads, exponentials and stores of
+// neighbouring rows overlap.
+constexpr int kBulkComputeThreads = 512;
+constexpr int kBulkThreads = kBulkComputeThreads + 32;
+constexpr uint32_t kBulkChunk = 32768;  // bytes per bulk copy
+enum : int { kErrXentProducer = 301, kErrXentCompute = 302 };
+
+template <typename T>
+__global__ void __launch_bounds__(kBulkThreads, 1) xent_bulk_kernel(XentParams<T> p, int* status) {
+  using namespace sm100;
+  constexpr int V = Vec<T>::N;
+  constexpr int W = kBulkComputeThreads / 32;
+  extern __shared__ __align__(128) unsigned char xent_bulk_smem[];
+  const uint32_t row_bytes = static_cast<uint32_t>(p.C) * sizeof(T);
+  const uint32_t buf_stride = (row_bytes + 127u) & ~127u;
+  unsigned char* base = xent_bulk_smem;
+  const uint32_t base_s = smem_u32(base);
+  const uint32_t bar_s = base_s + 2 * buf_stride;  // full[0], full[1], done[0], done[1]
+  float* red = reinterpret_cast<float*>(base + 2 * buf_stride + 64);  // [2][W], then the two broadcast slots
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(bar_s + 0, 1);
+    mbar_init(bar_s + 8, 1);
+    mbar_init(bar_s + 16, W);
+    mbar_init(bar_s + 24, W);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const int64_t first = blockIdx.x, step = gridDim.x;
+
+  if (warp == W) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      auto load_row = [&](int64_t row, int b) {
+        mbar_expect_tx(bar_s + 8 * b, row_bytes);
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.logits + row * p.ldx);
+        for (uint32_t off = 0; off < row_bytes; off += kBulkChunk) {
+          const uint32_t n = row_bytes - off < kBulkChunk ? row_bytes - off : kBulkChunk;
+          bulk_load_1d(base_s + b * buf_stride + off, src + off, n, bar_s + 8 * b);
+        }
+      };
+      for (int i = 0; i < 2; ++i)
+        if (first + i * step < p.N) load_row(first + i * step, i);
+      int i = 0;
+      for (int64_t row = first; row < p.N; row += step, ++i) {
+        const int b = i & 1;
+        if (!mbar_wait(bar_s + 16 + 8 * b, (i >> 1) & 1u)) {
+          atomicExch(status, kErrXentProducer);
+          break;
+        }
+        if (p.dlogits) {
+          unsigned char* dst = reinterpret_cast<unsigned char*>(p.dlogits + row * p.lddx);
+          for (uint32_t off = 0; off < row_bytes; off += kBulkChunk) {
+            const uint32_t n = row_bytes - off < kBulkChunk ? row_bytes - off : kBulkChunk;
+            bulk_store_1d(dst + off, base_s + b * buf_stride + off, n);
+          }
+          bulk_commit();
+        }
+        if (row + 2 * step < p.N) {
+          if (p.dlogits) bulk_wait_read0();  // the stores have left the buffer
+          load_row(row + 2 * step, b);
+        }
+      }
+      bulk_wait0();  // every row is in memory before the CTA retires
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ compute warps
+  const float up = p.upstream_dev ? to_f32(p.upstream_dev[0]) : p.upstream_host;
+  const float g = up / static_cast<float>(p.N);
+  const int C = static_cast<int>(p.C);
+  const int nvec = C / V;  // the launcher guarantees C % V == 0
+  int i = 0;
+  for (int64_t row = first; row < p.N; row += step, ++i) {
+    const int b = i & 1;
+    T* row_s = reinterpret_cast<T*>(base + b * buf_stride);
+    const int64_t t = p.index[row];
+    const int ti = (t >= 0 && t < p.C) ? static_cast<int>(t) : -1;
+    if (!mbar_wait(bar_s + 8 * b, (i >> 1) & 1u)) {
+      if (lane == 0) atomicExch(status, kErrXentCompute);
+      break;
+    }
+    const float xt = ti >= 0 ? to_f32(row_s[ti]) : 0.f;  // read before anyone overwrites the row
+    // ---- pass 1: online (max, sum exp)
+    float m = -INFINITY, s = 0.f;
+#pragma unroll 2
+    for (int v0 = tid; v0 < nvec; v0 += kBulkComputeThreads) {
+      float v[V];
+      load_vec(row_s + v0 * V, v);
+      fold_vec<V>(v, m, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+      const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      ms_merge(m, s, m2, s2);
+    }
+    if (lane == 0) {
+      red[warp] = m;
+      red[W + warp] = s;
+    }
+    named_barrier(1, kBulkComputeThreads);
+    if (warp == 0) {
+      float mm = lane < W ? red[lane] : -INFINITY;
+      float ss = lane < W ? red[W + lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, mm, o);
+        const float s2 = __shfl_xor_sync(0xffffffffu, ss, o);
+        ms_merge(mm, ss, m2, s2);
+      }
+      if (lane == 0) {
+        red[2 * W] = mm;
+        red[2 * W + 1] = ss;
+      }
+    }
+    named_barrier(1, kBulkComputeThreads);
+    m = red[2 * W];
+    s = red[2 * W + 1];
+    if (tid == 0 && p.row_loss) {
+      const float lse = m + logf(s);
+      p.row_loss[row] = (ti >= 0 ? lse - xt : 0.f) / static_cast<float>(p.N);
+    }
+    if (p.dlogits) {
+      // ---- pass 2: (softmax - onehot) * g, in place
+      const float k = g / s;
+      const float mb = m * kLog2e;
+#pragma unroll 2
+      for (int v0 = tid; v0 < nvec; v0 += kBulkComputeThreads) {
+        float v[V], o[V];
+        load_vec(row_s + v0 * V, v);
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = ex2(fmaf(v[j], kLog2e, -mb)) * k;
+        store_vec(row_s + v0 * V, o);
+      }
+      // the thread that wrote the target's vector rewrites that one element
+      if (ti >= 0 && (ti / V) % kBulkComputeThreads == tid)
+        row_s[ti] = from_f32<T>(ex2(fmaf(xt, kLog2e, -mb)) * k - g);
+      fence_async_smem();  // the bulk stores read these writes through the async proxy
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_s + 16 + 8 * b);
+    // red[] is rewritten only after the next row's first barrier, which every thread reaches after reading m, s
+  }
+}
+
 // Fixed-order sum of the per-row losses (already divided by N).
 template <typename TOut>
 __global__ void __launch_bounds__(kSumThreads) xent_sum_rows_kernel(const float* row_loss, int64_t N, TOut* loss) {
@@ -319,6 +473,21 @@ int launch_xent(XentParams<T> p, cudaStream_t st) {
     return check_launch("xent_small_kernel");
   }
   const size_t smem_cap = static_cast<size_t>(max_smem_optin()) - 1024;  // static reductions live there too
+  if (!DENSE) {
+    // long rows of index-label problems go through the bulk-copy kernel when two row buffers fit
+    const size_t need = 2 * round_up(row_bytes, 128) + 64 + (2 * (kBulkComputeThreads / 32) + 2) * sizeof(float);
+    const bool aligned = row_bytes % 16 == 0 && p.vec_in && (!p.dlogits || p.vec_out) && (p.C % V == 0);
+    if (row_bytes >= 32 * 1024 && aligned && need <= smem_cap) {
+      int* status = device_status_ptr();
+      if (!status) return fail(MGB_ECUDA, "xent: device status word unavailable");
+      auto kern = xent_bulk_kernel<T>;
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(need));
+      if (e != cudaSuccess) return fail(MGB_ECUDA, "xent smem opt-in (%zu B): %s", need, cudaGetErrorString(e));
+      const int64_t grid = p.N < sm_count() ? p.N : sm_count();
+      kern<<<static_cast<unsigned>(grid), kBulkThreads, need, st>>>(p, status);
+      return check_launch("xent_bulk_kernel");
+    }
+  }
   const size_t smem = round_up(row_bytes, 16);
   p.staged = smem <= smem_cap;
   const size_t dyn = p.staged ? smem : 0;
