@@ -63,6 +63,7 @@ struct GemmParams {
   int64_t ldr;
   float* rowsum_partial;       // optional [splits][M]: sum over the contraction of A(i, :) (db inside the dW GEMM)
   int d_vec;                   // output (or fp32 partial) rows take aligned 16-byte stores: staged epilogue
+  int stream_out;              // the output is larger than L2 can keep for its consumer
   int n_fastest;               // tile order: consecutive tiles walk the N blocks of one M block (else the M blocks of one N block)
   int* status;
 };
@@ -250,7 +251,10 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
           const int grow = eo.m0 + rr;
           if (grow < p.M && col_ok) {
             bf16* dst = p.d + static_cast<int64_t>(grow) * p.ldd + box_col0 + c * 8;
-            st_global_v4_hint(dst, val, eo.policy);  // written once, never re-read here: first out of L2
+            if (p.stream_out)
+              st_global_v4_hint(dst, val, eo.policy);  // larger than L2: leave first, keep the operands resident
+            else
+              *reinterpret_cast<uint4*>(dst) = val;
           }
         }
         __syncwarp();  // the slice may be rewritten
@@ -994,6 +998,7 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
     const double n_first = bytes_a + (bytes_b <= l2 ? bytes_b : bytes_b * (passes_b < 1 ? 1 : passes_b));
     p.n_fastest = n_first < m_first ? 1 : 0;
   }
+  p.stream_out = 2.0 * M * N > 96e6 ? 1 : 0;
   p.d = d;
   p.ldd = ldd;
   p.partial = reinterpret_cast<float*>(static_cast<char*>(ws) + ws_used);
