@@ -662,37 +662,43 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
       const int kv0 = jt * 128 + half * 64;
       const bool masked = diag || (jt * 128 + 128 > p.S);  // uniform over the CTA
       const uint32_t s_cols = tmem + lane_base + C::COL_S + s * 128 + half * 64;
-      // pass 1: maximum of this warp's 64 columns
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(s_cols + c0, v);
-        tmem_ld_wait();
-        if (!masked) {
+      // this warp's 64 scores of the row are read from TMEM once and kept in registers for both passes; the
+      // score buffer goes back to the MMA warp as soon as the load has landed
+      uint32_t v[64];
+      tmem_ld32(s_cols, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+      tmem_ld32(s_cols + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sr(s));
+      if (masked) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int kvrow = kv0 + c0 + e;
-            const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
-            mx = fmaxf(mx, keep ? __uint_as_float(v[e]) : -INFINITY);
-          }
+        for (int e = 0; e < 64; ++e) {
+          const int kvrow = kv0 + e;
+          const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
+          if (!keep) v[e] = __float_as_uint(-INFINITY);
         }
       }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
       xmax[(s * 2 + half) * 128 + r] = mx;
       named_barrier(2, 256);
       mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * 128 + r]);
-      const float m_new = fmaxf(m, mx * scale_log2);
-      const float corr = (m == -INFINITY) ? 0.f : ex2(m - m_new);
+      // The reference maximum only follows the true one when it has grown by more than 2^8: until then the
+      // probabilities are at most 256 instead of 1, which bf16 and the fp32 accumulators hold equally well,
+      // and the accumulated output needs no rescaling pass through TMEM.  Tile 0 always sets it (every query
+      // row sees key 0), so it is finite from then on.
+      const float m_cand = fmaxf(m, mx * scale_log2);
+      const float m_new = (jt == 0 || m_cand - m > 8.f) ? m_cand : m;
+      const float corr = (jt == 0) ? 0.f : ex2(m - m_new);
       // the previous P V product must be complete before P is overwritten or O rescaled
       if (jt > 0 && !mbar_wait(bar_pv, (jt - 1) & 1u)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (jt > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+      if (jt > 0 && __any_sync(0xffffffffu, m_new != m)) {
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 16) {
           uint32_t o[16];
@@ -704,35 +710,18 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
         }
         tmem_st_wait();
       }
-      // pass 2: P = exp2(S*scale*log2e - m_new) -> bf16 in shared memory
+      // P = exp2(S*scale*log2e - m_new) -> bf16 in shared memory (masked scores are -inf -> 0)
       float rs = 0.f;
-#pragma unroll 1
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;  // a row with nothing to see yet stays all zero
+#pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(s_cols + c0, v);
-        tmem_ld_wait();
         uint32_t pk[16];
-        if (!masked) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = ex2(fmaf(__uint_as_float(v[e]), scale_log2, -m_new));
-            const float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), scale_log2, -m_new));
-            rs += p0 + p1;
-            pk[e >> 1] = pack_bf16x2(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float pv[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int kvrow = kv0 + c0 + e + u;
-              const bool keep = kvrow < p.S && (!diag || kvrow <= qrow) && m_new != -INFINITY;
-              pv[u] = keep ? ex2(fmaf(__uint_as_float(v[e + u]), scale_log2, -m_new)) : 0.f;
-              rs += pv[u];
-            }
-            pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          }
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(v[c0 + e]), scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(v[c0 + e + 1]), scale_log2, neg_m));
+          rs += p0 + p1;
+          pk[e >> 1] = pack_bf16x2(p0, p1);
         }
 #pragma unroll
         for (int t = 0; t < 4; ++t)
@@ -744,10 +733,7 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar_sr(s));
-        mbar_arrive(bar_pr);
-      }
+      if (lane == 0) mbar_arrive(bar_pr);
     }
     if (ok && !mbar_wait(bar_pv, (nkv - 1) & 1u)) ok = false;
     if (!ok) {
