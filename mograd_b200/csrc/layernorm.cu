@@ -365,8 +365,7 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
   constexpr int kLnStages = LnStages<CHUNKS>::N;
   constexpr bool KEEP = CHUNKS * V <= 16;
   extern __shared__ __align__(16) unsigned char dsm[];
-  float* fold = reinterpret_cast<float*>(dsm);                       // [2][cols]
-  unsigned char* ring_base = dsm + ((2 * cols * sizeof(float) + 15) / 16) * 16;
+  unsigned char* ring_base = dsm;
   __shared__ float red[2 * S::WARPS * 4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int team = warp / WPR;
@@ -481,31 +480,41 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     slot = (slot + 1) % kLnStages;
   }
   cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its ring: the rings become [TEAMS][2][cols] floats
 
-  for (int t = 0; t < S::TEAMS; ++t) {
-    if (team == t) {
+  // Column partials of the CTA: every warp parks its own columns in its team's row with 16-byte stores, then
+  // each thread adds up a few columns over the teams in a fixed order and writes them out.  (The ring always
+  // has room: it holds at least two rows of x and dy per warp, four bytes of partials replace two or four
+  // bytes of input per column.)
+  float* stage = reinterpret_cast<float*>(ring_base);
+  float* mine = stage + static_cast<size_t>(team) * 2 * cols;
 #pragma unroll
-      for (int j = 0; j < CHUNKS; ++j) {
+  for (int j = 0; j < CHUNKS; ++j) {
+    if (colj[j] + V <= cols) {
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          if (colj[j] + e < cols) {
-            if (t == 0) {
-              fold[colj[j] + e] = dg[j][e];
-              fold[cols + colj[j] + e] = db[j][e];
-            } else {
-              fold[colj[j] + e] += dg[j][e];
-              fold[cols + colj[j] + e] += db[j][e];
-            }
-          }
+      for (int e = 0; e < V; e += 4) {
+        *reinterpret_cast<float4*>(mine + colj[j] + e) = make_float4(dg[j][e], dg[j][e + 1], dg[j][e + 2], dg[j][e + 3]);
+        *reinterpret_cast<float4*>(mine + cols + colj[j] + e) = make_float4(db[j][e], db[j][e + 1], db[j][e + 2], db[j][e + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        if (colj[j] + e < cols) {
+          mine[colj[j] + e] = dg[j][e];
+          mine[cols + colj[j] + e] = db[j][e];
         }
       }
     }
-    __syncthreads();
   }
+  __syncthreads();
   float* prow = part + static_cast<int64_t>(blockIdx.x) * 2 * cols;
-  for (int64_t c = threadIdx.x; c < 2 * cols; c += S::THREADS) prow[c] = fold[c];
+  for (int64_t c = threadIdx.x; c < 2 * cols; c += S::THREADS) {
+    float acc = stage[c];
+#pragma unroll
+    for (int t = 1; t < S::TEAMS; ++t) acc += stage[static_cast<size_t>(t) * 2 * cols + c];
+    prow[c] = acc;
+  }
 }
-
 // dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c], fixed order.
 template <typename T>
 __global__ void __launch_bounds__(kFinCols* kFinLanes)
@@ -568,7 +577,7 @@ int launch_bwd(const T* dy, const T* x, const T* g, const T* resid, T* dx, float
                float eps, bool vec, int grid, cudaStream_t st) {
   constexpr int TH = Shape<WPR>::THREADS;
   const size_t fold_bytes = round_up(static_cast<size_t>(2 * cols) * sizeof(float), 16);
-  const size_t pipe_smem = fold_bytes + static_cast<size_t>(Shape<WPR>::WARPS) * LnStages<CHUNKS>::N * 2 * CHUNKS * 512;
+  const size_t pipe_smem = static_cast<size_t>(Shape<WPR>::WARPS) * LnStages<CHUNKS>::N * 2 * CHUNKS * 512;
   if (vec && pipe_smem + 1024 <= static_cast<size_t>(max_smem_optin())) {
     const size_t smem = pipe_smem;
     auto k = ln_bwd_pipe_kernel<T, WPR, CHUNKS>;
