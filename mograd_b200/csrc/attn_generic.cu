@@ -248,6 +248,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o, const T* __restrict__ dy,
                                                         float* __restrict__ delta, int64_t rows, int S, int H, int D,
                                                         int o_bshd) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = Vec<T>::N;
   const int lanes_per_row = D / V;
   const int rows_per_warp = 32 / lanes_per_row;
@@ -277,8 +279,8 @@ int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int 
   const int lpr = D / V;
   if (D % V == 0 && lpr >= 1 && lpr <= 32 && (lpr & (lpr - 1)) == 0 && aligned16(o) && aligned16(dy)) {
     const int rows_per_block = 8 * (32 / lpr);
-    delta_vec_kernel<T><<<static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block), 256, 0, st>>>(
-        static_cast<const T*>(o), static_cast<const T*>(dy), delta, rows, S, H, D, o_bshd);
+    launch_pdl(delta_vec_kernel<T>, dim3(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block)), dim3(256), 0, st,
+               static_cast<const T*>(o), static_cast<const T*>(dy), delta, static_cast<int64_t>(rows), S, H, D, o_bshd);
     return check_launch("delta_vec_kernel");
   }
   delta_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(o),

@@ -172,6 +172,8 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_gen;
+  pdl_launch_dependents();  // after the TMEM allocation: a successor takes the columns over only once they are freed
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA
@@ -488,6 +490,8 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
 // acc is packed (tokens x HD) fp32; dq rows are ld elements apart.
 __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8,
                                                       int hd8, int64_t ld, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < n8; i += stride) {
     const int64_t tok = i / hd8;
@@ -571,6 +575,8 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_gen;
+  pdl_launch_dependents();  // after the TMEM allocation: a successor takes the columns over only once they are freed
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -825,7 +831,7 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
-  kern<<<grid, C::THREADS, C::SMEM, st>>>(mq, mk, mv, mdo, mdq, p);
+  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mdo, mdq, p);
   return check_launch("attn_bwd_tc_kernel");
 }
 
@@ -840,7 +846,7 @@ int run_fwd(const void* q, const void* k, const void* v, AttnParams p, int64_t l
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
-  kern<<<grid, C::THREADS, C::SMEM, st>>>(mq, mk, mv, p);
+  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, p);
   return check_launch("attn_fwd_tc_kernel");
 }
 
@@ -890,7 +896,7 @@ int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const fl
   const int64_t n8 = n / 8;
   int grid = static_cast<int>((n8 + 255) / 256);
   if (grid > sm_count() * 8) grid = sm_count() * 8;
-  cast_dq_kernel<<<grid, 256, 0, st>>>(dq_acc, static_cast<bf16*>(dq), n8, H * D / 8, lay.ld_dqkv, scale);
+  launch_pdl(cast_dq_kernel, dim3(grid), dim3(256), 0, st, dq_acc, static_cast<bf16*>(dq), n8, H * D / 8, lay.ld_dqkv, scale);
   return check_launch("cast_dq_kernel");
 }
 

@@ -32,7 +32,31 @@ inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
     if (!(cond)) return ::mgb::fail((code), __VA_ARGS__); \
   } while (0)
 
+// Launch with programmatic stream serialization: the grid may be scheduled while the kernel before it on the
+// stream is still draining, so its set-up (barriers, TMEM, descriptor prefetch) and the launch latency overlap the
+// predecessor's tail.  Only for kernels that call pdl_wait() before their first access to global memory.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);  // errors surface in check_launch()
+}
+
 // -------------------------------------------------------------- device side
+// Programmatic dependent launch: pdl_wait() returns once every kernel before this one on the stream has
+// completed and its writes are visible; nothing before it may touch global memory.  pdl_launch_dependents() lets
+// the next kernel's blocks be scheduled as soon as every block of this grid has executed it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 template <typename T>
 struct Vec;  // elements per 16-byte vector
 template <>

@@ -319,6 +319,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_gen;
+  pdl_launch_dependents();  // TMEM is held: a successor can only take it over when this CTA has freed it
+  pdl_wait();               // operands and outputs of earlier kernels are settled from here on
 
   const int tiles_mn = p.num_m * p.num_n;
   const int total = tiles_mn * p.splits;
@@ -564,6 +566,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   cluster_sync_all();  // barriers of both CTAs are initialised before any remote arrival
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_gen;
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int tiles_mn = p.num_m * p.num_n;  // num_m counts 256-row blocks here
   const int total = tiles_mn * p.splits;
@@ -718,6 +722,8 @@ template <bool VEC>
 __global__ void __launch_bounds__(256)
     splitk_finalize_kernel(const float* __restrict__ partial, int splits, int M, int N, bf16* __restrict__ out,
                            int64_t ldd, const bf16* __restrict__ bias, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = static_cast<int64_t>(M) * N;
   if (VEC) {
     const int n4 = N >> 2;
@@ -766,6 +772,8 @@ __global__ void __launch_bounds__(256)
 // db[i] = sum_s rowsum_partial[s][i], fixed order.
 __global__ void __launch_bounds__(256)
     rowsum_finalize_kernel(const float* __restrict__ partial, int splits, int M, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * 256 + threadIdx.x;
   if (i >= M) return;
   float acc = 0.f;
@@ -932,7 +940,7 @@ int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st)
   }
   const int total = p.num_m * p.num_n * p.splits;
   const int grid = total < sm_count() ? total : sm_count();
-  kern<<<grid, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
+  launch_pdl(kern, dim3(grid), dim3(kGemmThreads), T::SMEM_BYTES, st, ma, mb, p);
   return check_launch("gemm_tc_kernel");
 }
 
@@ -956,7 +964,7 @@ int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st
   const int total = p.num_m * p.num_n * p.splits;
   const int max_clusters = sm_count() / 2;
   const int clusters = total < max_clusters ? total : max_clusters;
-  kern<<<2 * clusters, kGemmThreads, T::SMEM_BYTES, st>>>(ma, mb, p);
+  launch_pdl(kern, dim3(2 * clusters), dim3(kGemmThreads), T::SMEM_BYTES, st, ma, mb, p);
   return check_launch("gemm_tc2_kernel");
 }
 
@@ -1022,14 +1030,14 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
     int grid = static_cast<int>(((vec ? total / 4 : total) + 255) / 256);
     if (grid > sm_count() * 8) grid = sm_count() * 8;
     if (vec)
-      splitk_finalize_kernel<true><<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
+      launch_pdl(splitk_finalize_kernel<true>, dim3(grid), dim3(256), 0, st, p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
     else
-      splitk_finalize_kernel<false><<<grid, 256, 0, st>>>(p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
+      launch_pdl(splitk_finalize_kernel<false>, dim3(grid), dim3(256), 0, st, p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
     rc = check_launch("splitk_finalize_kernel");
     if (rc != MGB_OK) return rc;
   }
   if (rowsum_out) {
-    rowsum_finalize_kernel<<<(p.M + 255) / 256, 256, 0, st>>>(p.rowsum_partial, p.splits, p.M, rowsum_out);
+    launch_pdl(rowsum_finalize_kernel, dim3((p.M + 255) / 256), dim3(256), 0, st, p.rowsum_partial, p.splits, p.M, rowsum_out);
     rc = check_launch("rowsum_finalize_kernel");
   }
   return rc;

@@ -100,6 +100,8 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                   T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t rows,
                   int64_t cols, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = Vec<T>::N;
   using S = Shape<WPR>;
   __shared__ float redA[2 * S::WARPS];
@@ -367,6 +369,8 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
   extern __shared__ __align__(16) unsigned char dsm[];
   unsigned char* ring_base = dsm;
   __shared__ float red[2 * S::WARPS * 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int team = warp / WPR;
   const int lt = (warp % WPR) * 32 + lane;
@@ -520,6 +524,8 @@ template <typename T>
 __global__ void __launch_bounds__(kFinCols* kFinLanes)
     ln_bwd_finalize_kernel(const float* __restrict__ part, int nparts, int64_t cols, T* __restrict__ dgamma,
                            T* __restrict__ dbeta) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[kFinLanes][kFinCols + 1];
   const int cx = threadIdx.x % kFinCols, ry = threadIdx.x / kFinCols;
   const int64_t c2 = static_cast<int64_t>(blockIdx.x) * kFinCols + cx;  // index into [2*cols]
@@ -566,9 +572,9 @@ int launch_fwd(const T* x, const T* g, const T* b, T* y, float* mean, float* rst
                float eps, bool vec, int grid, cudaStream_t st) {
   constexpr int TH = Shape<WPR>::THREADS;
   if (vec)
-    ln_fwd_kernel<T, WPR, CHUNKS, true><<<grid, TH, 0, st>>>(x, g, b, y, mean, rstd, rows, cols, eps);
+    launch_pdl(ln_fwd_kernel<T, WPR, CHUNKS, true>, dim3(grid), dim3(TH), 0, st, x, g, b, y, mean, rstd, rows, cols, eps);
   else
-    ln_fwd_kernel<T, WPR, CHUNKS, false><<<grid, TH, 0, st>>>(x, g, b, y, mean, rstd, rows, cols, eps);
+    launch_pdl(ln_fwd_kernel<T, WPR, CHUNKS, false>, dim3(grid), dim3(TH), 0, st, x, g, b, y, mean, rstd, rows, cols, eps);
   return check_launch("ln_fwd_kernel");
 }
 
@@ -582,7 +588,7 @@ int launch_bwd(const T* dy, const T* x, const T* g, const T* resid, T* dx, float
     const size_t smem = pipe_smem;
     auto k = ln_bwd_pipe_kernel<T, WPR, CHUNKS>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    k<<<grid, TH, smem, st>>>(dy, x, g, resid, dx, part, rows, cols, eps);
+    launch_pdl(k, dim3(grid), dim3(TH), smem, st, dy, x, g, resid, dx, part, rows, cols, eps);
     return check_launch("ln_bwd_pipe_kernel");
   }
   if (vec) {  // very wide rows: the ring does not fit next to the fold buffer, keep the row in registers instead
@@ -651,8 +657,8 @@ int ln_bwd(const void* dy, const void* x, const void* gamma, const void* resid, 
   int rc = ln_bwd_main<T>(dy, x, gamma, resid, dx, part, rows, cols, eps, pl, st);
   if (rc != MGB_OK) return rc;
   const unsigned fgrid = static_cast<unsigned>((2 * cols + kFinCols - 1) / kFinCols);
-  ln_bwd_finalize_kernel<T><<<fgrid, kFinCols * kFinLanes, 0, st>>>(part, pl.grid, cols, static_cast<T*>(dgamma),
-                                                                    static_cast<T*>(dbeta));
+  launch_pdl(ln_bwd_finalize_kernel<T>, dim3(fgrid), dim3(kFinCols * kFinLanes), 0, st, static_cast<const float*>(part),
+             pl.grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
   return check_launch("ln_bwd_finalize_kernel");
 }
 
