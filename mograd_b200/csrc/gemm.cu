@@ -908,12 +908,11 @@ size_t splitk_bytes(int64_t M, int64_t N, int splits) {
 size_t rowsum_bytes(int64_t M) { return round_up(static_cast<size_t>(kMaxSplits) * M * sizeof(float), 256); }
 
 // Split the contraction when the output has too few tiles to fill the GPU.
-int choose_splits(int64_t M, int64_t N, int64_t K, int BN) {
-  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+// Splits of the contraction for an output of `tiles` tiles on `slots` concurrent CTAs (or CTA pairs).
+int choose_splits(int64_t tiles, int64_t K, int slots) {
   const int64_t num_kb = (K + BK - 1) / BK;
-  const int sms = sm_count();
-  if (tiles * 2 > sms || num_kb < 16) return 1;
-  int64_t s = sms / tiles;
+  if (tiles * 2 > slots || num_kb < 16) return 1;
+  int64_t s = slots / tiles;
   if (s > num_kb / 8) s = num_kb / 8;
   if (s > kMaxSplits) s = kMaxSplits;
   return s < 1 ? 1 : static_cast<int>(s);
@@ -977,8 +976,12 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   // CTA pairs (256 x 256 tiles) for products large enough to fill the GPU with them and with a long contraction
   // (measured: with 12 k-blocks per tile the pair's cluster-wide accumulator hand-off costs more than the saved
   // L2 traffic; from 32 k-blocks on the pair wins); db is fused only in the single-CTA kernel
-  const bool pair = !rowsum_out && BN == 256 && M >= 512 && K >= 32 * BK &&
-                    ((M + 255) / 256) * ((N + 255) / 256) >= sm_count() / 4;
+  const bool plain = !ep.relu_mask && !ep.residual;
+  const bool may_split = allow_split && plain;
+  const int64_t tiles1 = ((M + BM - 1) / BM) * ((N + BN - 1) / BN), tiles2 = ((M + 255) / 256) * ((N + 255) / 256);
+  const int splits1 = may_split ? choose_splits(tiles1, K, sm_count()) : 1;
+  const int splits2 = may_split ? choose_splits(tiles2, K, sm_count() / 2) : 1;
+  const bool pair = !rowsum_out && BN == 256 && M >= 512 && K >= 32 * BK && tiles2 * splits2 >= sm_count() / 4;
   const int bm = pair ? 256 : BM;
   GemmParams p{};
   p.M = static_cast<int>(M);
@@ -987,8 +990,7 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   p.num_m = static_cast<int>((M + bm - 1) / bm);
   p.num_n = static_cast<int>((N + BN - 1) / BN);
   p.num_kb = static_cast<int>((K + BK - 1) / BK);
-  const bool plain = !ep.relu_mask && !ep.residual;
-  p.splits = (allow_split && plain && !pair) ? choose_splits(M, N, K, BN) : 1;
+  p.splits = pair ? splits2 : splits1;
   size_t ws_used = 0;
   if (rowsum_out) {  // the row-sum partials sit at the start of the workspace
     if (!ws || ws_bytes < rowsum_bytes(M)) return fail(MGB_EWORKSPACE, "gemm: workspace too small for the bias gradient");
