@@ -961,7 +961,31 @@ int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st
     attr_dev = dev;
   }
   const int total = p.num_m * p.num_n * p.splits;
-  const int max_clusters = sm_count() / 2;
+  // CTA pairs that can be resident at once: pairs need two SMs of one GPC, so this can be fewer than half the SMs,
+  // and a pair that starts late would hold its round-robin share of the tiles back
+  static int resident_by_dev[64] = {};
+  int& resident = resident_by_dev[dev & 63];
+  if (resident == 0) {
+    cudaLaunchConfig_t occ = {};
+    occ.gridDim = dim3(sm_count() / 2 * 2);
+    occ.blockDim = dim3(kGemmThreads);
+    occ.dynamicSmemBytes = T::SMEM_BYTES;
+    cudaLaunchAttribute ca[1];
+    ca[0].id = cudaLaunchAttributeClusterDimension;
+    ca[0].val.clusterDim.x = 2;
+    ca[0].val.clusterDim.y = 1;
+    ca[0].val.clusterDim.z = 1;
+    occ.attrs = ca;
+    occ.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &occ) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    resident = n < sm_count() / 2 ? n : sm_count() / 2;
+    if (getenv("MGB_DEBUG")) fprintf(stderr, "gemm_tc2: %d resident CTA pairs\n", resident);
+  }
+  const int max_clusters = resident;
   const int clusters = total < max_clusters ? total : max_clusters;
   launch_pdl(kern, dim3(2 * clusters), dim3(kGemmThreads), T::SMEM_BYTES, st, ma, mb, p);
   return check_launch("gemm_tc2_kernel");

@@ -13,7 +13,8 @@ def _mk(rng, N, C, sigma=2.0):
     return x, idx
 
 
-@pytest.mark.parametrize("N,C", [(4, 10), (8, 5), (128, 10), (2048, 10), (1000, 65), (37, 2048), (16, 50304), (5, 4099)])
+@pytest.mark.parametrize("N,C", [(4, 10), (8, 5), (128, 10), (2048, 10), (1000, 65), (37, 2048), (16, 50304), (5, 4099),
+                                 (449, 16384), (301, 50304), (1, 32768)])  # the last three: several rows per persistent CTA
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 def test_fused_index_matches_oracle(cuda, oracle, N, C, dt):
     import torch
