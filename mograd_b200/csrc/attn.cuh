@@ -16,7 +16,9 @@ struct Layouts {
 
 // delta[(b,h,s)] = sum_d O[.,d] * dO[.,d].
 template <typename T>
-int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, cudaStream_t st);
+// zero (optional): fp32 array of B*S*H*D elements cleared by the same kernel when it can; *zeroed says whether it was
+int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, float* zero,
+                 bool* zeroed, cudaStream_t st);
 
 // CUDA-core kernels (any D <= 512, optional additive bias).
 template <typename T>
@@ -31,10 +33,11 @@ int generic_bwd(const void* dy, const void* q, const void* k, const void* v, con
 bool tc_supported(int D, int has_bias, const Layouts& lay, const void* const* ptrs, int nptrs);
 int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, int B, int S, int H, int D, float scale,
            int causal, const Layouts& lay, cudaStream_t st);
-// dq_acc: fp32 (B,S,H,D) accumulator, zero-filled by the callee.
+// dq_acc: fp32 (B,S,H,D) accumulator; zero-filled by the callee unless acc_zeroed says an earlier kernel on the
+// stream has done it.
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
-           float* dq_acc, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale, int causal,
-           const Layouts& lay, cudaStream_t st);
+           float* dq_acc, bool acc_zeroed, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale,
+           int causal, const Layouts& lay, cudaStream_t st);
 
 }  // namespace attn
 }  // namespace mgb

@@ -84,18 +84,18 @@ MGB_EXPORT int mograd_b200_flash_attn_bwd_ex(const void* dy, const void* o, cons
   const attn::Layouts lay{ld_qkv, ld_dqkv, o_layout};
   float* delta = static_cast<float*>(workspace);
   if (dtype == MGB_F32) {
-    rc = attn::launch_delta<float>(o, dy, delta, b, s, h, d, o_layout, st);
+    rc = attn::launch_delta<float>(o, dy, delta, b, s, h, d, o_layout, nullptr, nullptr, st);
     if (rc != MGB_OK) return rc;
     return attn::generic_bwd<float>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal, has_bias, lay,
                                     st);
   }
-  rc = attn::launch_delta<__nv_bfloat16>(o, dy, delta, b, s, h, d, o_layout, st);
-  if (rc != MGB_OK) return rc;
   const void* ptrs[] = {dy, q, k, v, dq, dk, dv};
-  if (attn::tc_supported(d, has_bias, lay, ptrs, 7)) {
-    float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes(B, S, H));
-    return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, dq, dk, dv, b, s, h, d, scale, causal, lay, st);
-  }
+  const bool tc = attn::tc_supported(d, has_bias, lay, ptrs, 7);
+  float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes(B, S, H));
+  bool acc_zeroed = false;
+  rc = attn::launch_delta<__nv_bfloat16>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st);
+  if (rc != MGB_OK) return rc;
+  if (tc) return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, acc_zeroed, dq, dk, dv, b, s, h, d, scale, causal, lay, st);
   return attn::generic_bwd<__nv_bfloat16>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal,
                                           has_bias, lay, st);
 }

@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ o, con
 template <typename T>
 __global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o, const T* __restrict__ dy,
                                                         float* __restrict__ delta, int64_t rows, int S, int H, int D,
-                                                        int o_bshd) {
+                                                        int o_bshd, float* __restrict__ zero) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int V = Vec<T>::N;
@@ -270,17 +270,28 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o,
   }
   for (int ofs = lanes_per_row >> 1; ofs > 0; ofs >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, ofs);
   if (row < rows && part == 0) delta[row] = acc;
+  // optional: clear an fp32 array with one element per element of O (the dQ accumulator of the tensor-core
+  // backward), V floats per thread, instead of a separate fill pass
+  if (zero != nullptr && row < rows) {
+    float4* z = reinterpret_cast<float4*>(zero + (warp_global * 32 + lane) * V);
+#pragma unroll
+    for (int e = 0; e < V / 4; ++e) z[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 }
 
 template <typename T>
-int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, cudaStream_t st) {
+int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, float* zero,
+                 bool* zeroed, cudaStream_t st) {
+  if (zeroed) *zeroed = false;
   const int64_t rows = static_cast<int64_t>(B) * H * S;
   constexpr int V = Vec<T>::N;
   const int lpr = D / V;
   if (D % V == 0 && lpr >= 1 && lpr <= 32 && (lpr & (lpr - 1)) == 0 && aligned16(o) && aligned16(dy)) {
     const int rows_per_block = 8 * (32 / lpr);
     launch_pdl(delta_vec_kernel<T>, dim3(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block)), dim3(256), 0, st,
-               static_cast<const T*>(o), static_cast<const T*>(dy), delta, static_cast<int64_t>(rows), S, H, D, o_bshd);
+               static_cast<const T*>(o), static_cast<const T*>(dy), delta, static_cast<int64_t>(rows), S, H, D, o_bshd,
+               aligned16(zero) ? zero : static_cast<float*>(nullptr));
+    if (zeroed) *zeroed = zero != nullptr && aligned16(zero);
     return check_launch("delta_vec_kernel");
   }
   delta_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(o),
@@ -288,8 +299,8 @@ int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int 
                                                                        o_bshd);
   return check_launch("delta_kernel");
 }
-template int launch_delta<float>(const void*, const void*, float*, int, int, int, int, int, cudaStream_t);
-template int launch_delta<__nv_bfloat16>(const void*, const void*, float*, int, int, int, int, int, cudaStream_t);
+template int launch_delta<float>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
+template int launch_delta<__nv_bfloat16>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
 
 template <typename T>
 int generic_fwd(const void* q, const void* k, const void* v, const void* mask, void* dst, float* lse, int B, int S,

@@ -333,7 +333,8 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         bulk_wait_read0();
         mbar_arrive(bar_stg);
       }
-      bulk_wait0();  // every reduction has landed before the CTA retires
+      // every reduction has been read out of shared memory (wait_group.read above); the adds themselves complete
+      // before the grid does, which is what the kernel after this one waits for
     }
     __syncwarp();
   } else {
@@ -874,8 +875,8 @@ int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, i
 }
 
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
-           float* dq_acc, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale, int causal,
-           const Layouts& lay, cudaStream_t st) {
+           float* dq_acc, bool acc_zeroed, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale,
+           int causal, const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
   p.lse = lse;
   p.delta = delta;
@@ -889,8 +890,10 @@ int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const fl
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_bwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_bwd: B*H=%d exceeds 65535", B * H);
   const int64_t n = static_cast<int64_t>(B) * S * H * D;
-  const cudaError_t e = cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n) * sizeof(float), st);
-  if (e != cudaSuccess) return fail(MGB_ECUDA, "flash_attn_bwd: memset of the dQ accumulator: %s", cudaGetErrorString(e));
+  if (!acc_zeroed) {
+    const cudaError_t e = cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n) * sizeof(float), st);
+    if (e != cudaSuccess) return fail(MGB_ECUDA, "flash_attn_bwd: memset of the dQ accumulator: %s", cudaGetErrorString(e));
+  }
   int rc = D == 64 ? run_bwd<64>(dy, q, k, v, p, lay.ld_qkv, st) : run_bwd<128>(dy, q, k, v, p, lay.ld_qkv, st);
   if (rc != MGB_OK) return rc;
   const int64_t n8 = n / 8;
