@@ -237,6 +237,21 @@ int mograd_b200_matmul_bias_bt_bwd_ex(const void* dy, const void* x, const void*
                                       int64_t ld_dx_residual, int64_t lddx, int64_t lddw, int dtype, void* workspace,
                                       size_t workspace_bytes, void* stream);
 
+/* The ReLU pair of a feed-forward block with the mask kept as one bit per element instead of re-reading the
+ * activation (16x fewer bytes for the backward GEMM to fetch).  Forward: Y = relu(A W^T + bias) and
+ * relu_bits[i][c / 32] bit (c % 32) = (Y[i][c] > 0); relu_bits is M rows of ld_bits uint32 words, ld_bits >=
+ * ceil(N / 32).  Backward: as matmul_bias_bt_bwd_ex with the mask taken from relu_bits (M rows, one bit per column of
+ * X, ld_bits >= ceil(K / 32)) instead of relu_y.  bf16 with 16-byte-aligned rows only (MGB_EUNSUPPORTED otherwise:
+ * use relu_y).  Absorb mograd_relu / mograd_relu_grad (mograd/grad.mojo:130-131) like the _ex forms. */
+int mograd_b200_matmul_bias_bt_relu_bits(const void* a, const void* w, const void* bias, void* y, void* relu_bits,
+                                         int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldy,
+                                         int64_t ld_bits, int dtype, void* stream);
+int mograd_b200_matmul_bias_bt_bwd_relu_bits(const void* dy, const void* x, const void* w, const void* relu_bits,
+                                             const void* dx_residual, void* dx, void* dw, void* db, int64_t M,
+                                             int64_t N, int64_t K, int64_t lddy, int64_t ldx, int64_t ldw,
+                                             int64_t ld_bits, int64_t ld_dx_residual, int64_t lddx, int64_t lddw,
+                                             int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* dx = layer_norm_bwd(...) + dx_residual (rows x cols, may be NULL, may alias
  * dx): absorbs the mograd_add of the residual branch's gradient. */
 int mograd_b200_layer_norm_bwd_ex(const void* dy, const void* x, const void* gamma, const void* dx_residual, void* dx,

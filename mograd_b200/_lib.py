@@ -57,6 +57,10 @@ SIGNATURES = {
                                              _p]),
     "mograd_b200_matmul_bias_bt_bwd_ex": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64,
                                                  _i64, _i64, _i64, _i64, _int, _p, _sz, _p]),
+    "mograd_b200_matmul_bias_bt_relu_bits": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int,
+                                                    _p]),
+    "mograd_b200_matmul_bias_bt_bwd_relu_bits": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64,
+                                                        _i64, _i64, _i64, _i64, _i64, _int, _p, _sz, _p]),
     "mograd_b200_layer_norm_bwd_ex": (_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f32, _int, _p, _sz, _p]),
     "mograd_b200_flash_attn_fwd_ex": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f32, _int, _int, _i64,
                                              _int, _int, _p]),

@@ -61,6 +61,9 @@ struct GemmParams {
   int64_t ldm;
   const bf16* residual;        // optional M x N added last (may alias d), splits == 1 only
   int64_t ldr;
+  uint32_t* bits_out;          // optional [M][ldbits]: bit c%32 of word c/32 = (value after bias and ReLU) > 0
+  const uint32_t* bits_in;     // optional, same layout: the output is zeroed where the bit is clear (ReLU backward)
+  int64_t ldbits;
   float* rowsum_partial;       // optional [splits][M]: sum over the contraction of A(i, :) (db inside the dW GEMM)
   int d_vec;                   // output (or fp32 partial) rows take aligned 16-byte stores: staged epilogue
   int stream_out;              // the output is larger than L2 can keep for its consumer
@@ -98,9 +101,17 @@ struct EpilogueOut {
 // synchronisation and nothing waits on an asynchronous copy.  fp32 partial tiles of a split contraction take the
 // same route.  Otherwise (unaligned output) each thread stores its own row.  `row` is the output row of this
 // thread, t_row the TMEM address of its lane at the accumulator's first column.
-template <int BN>
+// FUSED = false compiles the elementwise epilogue (bias, ReLU, mask, residual) out: plain products keep the
+// shortest possible drain loop.
+template <int BN, bool FUSED>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_row, int row, int n_blk, int split,
                                                   int chalf, const EpilogueOut& eo, int lane_row) {
+  const bf16* const e_bias = FUSED ? p.bias : nullptr;
+  const int e_act = FUSED ? p.act : 0;
+  const bf16* const e_mask = FUSED ? p.relu_mask : nullptr;
+  const bf16* const e_res = FUSED ? p.residual : nullptr;
+  uint32_t* const e_bits_out = FUSED ? p.bits_out : nullptr;
+  const uint32_t* const e_bits_in = FUSED ? p.bits_in : nullptr;
   const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0;
   const bool mask_vec = (p.ldm & 7) == 0 && (reinterpret_cast<uintptr_t>(p.relu_mask) & 15u) == 0;
   const bool res_vec = (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0;
@@ -117,21 +128,23 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
     const bool full = col0 + 32 <= p.N;
     uint4 ep_bias[4], ep_mask[4], ep_res[4];
     if (p.splits == 1 && full && row < p.M) {
-      if (p.bias && bias_vec) {
+      if (e_bias && bias_vec) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) ep_bias[q] = __ldg(reinterpret_cast<const uint4*>(p.bias + col0) + q);
+        for (int q = 0; q < 4; ++q) ep_bias[q] = __ldg(reinterpret_cast<const uint4*>(e_bias + col0) + q);
       }
-      if (p.relu_mask && mask_vec) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0);
+      if (e_mask && mask_vec) {
+        const uint4* src = reinterpret_cast<const uint4*>(e_mask + static_cast<int64_t>(row) * p.ldm + col0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) ep_mask[q] = __ldg(src + q);
       }
-      if (p.residual && res_vec) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.residual + static_cast<int64_t>(row) * p.ldr + col0);
+      if (e_res && res_vec) {
+        const uint4* src = reinterpret_cast<const uint4*>(e_res + static_cast<int64_t>(row) * p.ldr + col0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) ep_res[q] = src[q];  // may alias the output: plain load
       }
     }
+    uint32_t keep_bits = 0xffffffffu;
+    if (e_bits_in && p.splits == 1 && row < p.M) keep_bits = __ldg(e_bits_in + static_cast<int64_t>(row) * p.ldbits + (col0 >> 5));
     tmem_ld_wait();
     if (p.splits > 1 && eo.vec) {
       // fp32 partial tile of a split contraction: this warp's [32 rows][32 floats] box goes through its own
@@ -173,7 +186,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
     if (row < p.M) {
-      if (p.bias) {
+      if (e_bias) {
         if (full && bias_vec) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -185,14 +198,24 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+            if (col0 + j < p.N) v[j] += __bfloat162float(e_bias[col0 + j]);
         }
       }
-      if (p.act == 1) {
+      if (e_act == 1) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
       }
-      if (p.relu_mask) {
+      if (e_bits_out) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) word |= (v[j] > 0.f && col0 + j < p.N) ? (1u << j) : 0u;
+        e_bits_out[static_cast<int64_t>(row) * p.ldbits + (col0 >> 5)] = word;
+      }
+      if (e_bits_in) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = ((keep_bits >> j) & 1u) ? v[j] : 0.f;
+      }
+      if (e_mask) {
         if (full && mask_vec) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -202,13 +225,13 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
             for (int e = 0; e < 8; ++e) v[j + e] = mv[e] > 0.f ? v[j + e] : 0.f;
           }
         } else {
-          const bf16* mk = p.relu_mask + static_cast<int64_t>(row) * p.ldm + col0;
+          const bf16* mk = e_mask + static_cast<int64_t>(row) * p.ldm + col0;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) v[j] = __bfloat162float(mk[j]) > 0.f ? v[j] : 0.f;
         }
       }
-      if (p.residual) {
+      if (e_res) {
         if (full && res_vec) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -218,7 +241,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
             for (int e = 0; e < 8; ++e) v[j + e] += rv[e];
           }
         } else {
-          const bf16* rs = p.residual + static_cast<int64_t>(row) * p.ldr + col0;
+          const bf16* rs = e_res + static_cast<int64_t>(row) * p.ldr + col0;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
@@ -280,7 +303,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool FUSED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                    const GemmParams p) {
@@ -490,7 +513,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       eo.m0 = m_blk * BM;
-      drain_accumulator<BN>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
+      drain_accumulator<BN, FUSED>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -526,7 +549,7 @@ struct Tile2 {
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const GemmParams p) {
@@ -700,7 +723,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const int row = m_blk * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       eo.m0 = m_blk * 256 + static_cast<int>(rank) * 128;
-      drain_accumulator<BN>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
+      drain_accumulator<BN, FUSED>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -890,6 +913,9 @@ struct Epilogue {
   int64_t ldm = 0;
   const void* residual = nullptr;
   int64_t ldr = 0;
+  uint32_t* bits_out = nullptr;
+  const uint32_t* bits_in = nullptr;
+  int64_t ldbits = 0;
 };
 
 bool tma_ok(const Operand& o) { return aligned16(o.ptr) && (o.ld % 8 == 0) && o.ld >= o.cols; }
@@ -920,13 +946,13 @@ int choose_splits(int64_t tiles, int64_t K, int slots) {
 
 int choose_bn(int64_t N) { return N > 128 ? 256 : 128; }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool FUSED>
 int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st) {
   using T = Tile<BN>;
   CUtensorMap ma, mb;
   if (!make_map(&ma, a, 64, A_MN ? BK : BM)) return MGB_ECUDA;
   if (!make_map(&mb, b, 64, B_MN ? BK : BN)) return MGB_ECUDA;
-  auto kern = gemm_tc_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, FUSED>;
   static bool attr_done = false;  // per instantiation; the attribute is per function and device
   static int attr_dev = -1;
   int dev = 0;
@@ -943,13 +969,13 @@ int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st)
   return check_launch("gemm_tc_kernel");
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool FUSED>
 int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st) {
   using T = Tile2;
   CUtensorMap ma, mb;
   if (!make_map(&ma, a, 64, A_MN ? BK : 128)) return MGB_ECUDA;
   if (!make_map(&mb, b, 64, B_MN ? BK : 128)) return MGB_ECUDA;
-  auto kern = gemm_tc2_kernel<A_MN, B_MN>;
+  auto kern = gemm_tc2_kernel<A_MN, B_MN, FUSED>;
   static bool attr_done = false;
   static int attr_dev = -1;
   int dev = 0;
@@ -1000,7 +1026,7 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   // CTA pairs (256 x 256 tiles) for products large enough to fill the GPU with them and with a long contraction
   // (measured: with 12 k-blocks per tile the pair's cluster-wide accumulator hand-off costs more than the saved
   // L2 traffic; from 32 k-blocks on the pair wins); db is fused only in the single-CTA kernel
-  const bool plain = !ep.relu_mask && !ep.residual;
+  const bool plain = !ep.relu_mask && !ep.residual && !ep.bits_out && !ep.bits_in;
   const bool may_split = allow_split && plain;
   const int64_t tiles1 = ((M + BM - 1) / BM) * ((N + BN - 1) / BN), tiles2 = ((M + 255) / 256) * ((N + 255) / 256);
   const int splits1 = may_split ? choose_splits(tiles1, K, sm_count()) : 1;
@@ -1042,12 +1068,21 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   p.relu_mask = static_cast<const bf16*>(ep.relu_mask);
   p.ldm = ep.ldm;
   p.residual = static_cast<const bf16*>(ep.residual);
+  p.bits_out = ep.bits_out;
+  p.bits_in = ep.bits_in;
+  p.ldbits = ep.ldbits;
   p.ldr = ep.ldr;
   p.d_vec = p.splits == 1 ? (aligned16(d) && (ldd % 8 == 0) && (N % 8 == 0)) : (aligned16(p.partial) && (N % 4 == 0));
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "gemm: device status word unavailable");
-  int rc = pair ? launch_tc2<A_MN, B_MN>(a, b, p, st)
-                : (BN == 256 ? launch_tc<256, A_MN, B_MN>(a, b, p, st) : launch_tc<128, A_MN, B_MN>(a, b, p, st));
+  const bool fused = p.bias || p.act || p.relu_mask || p.residual || p.bits_out || p.bits_in;
+  int rc;
+  if (fused)
+    rc = pair ? launch_tc2<A_MN, B_MN, true>(a, b, p, st)
+              : (BN == 256 ? launch_tc<256, A_MN, B_MN, true>(a, b, p, st) : launch_tc<128, A_MN, B_MN, true>(a, b, p, st));
+  else
+    rc = pair ? launch_tc2<A_MN, B_MN, false>(a, b, p, st)
+              : (BN == 256 ? launch_tc<256, A_MN, B_MN, false>(a, b, p, st) : launch_tc<128, A_MN, B_MN, false>(a, b, p, st));
   if (rc != MGB_OK) return rc;
   if (p.splits > 1) {
     const int64_t total = M * N;
@@ -1101,9 +1136,10 @@ int colsum(const void* dy, void* db, int64_t M, int64_t N, int64_t ld, cudaStrea
 
 using namespace mgb;
 
-MGB_EXPORT int mograd_b200_matmul_bias_bt_ex(const void* a, const void* w, const void* bias, const void* residual,
-                                             void* y, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw,
-                                             int64_t ldr, int64_t ldy, int act, int dtype, void* stream) {
+namespace {
+int matmul_fwd_impl(const void* a, const void* w, const void* bias, const void* residual, void* y, void* relu_bits,
+                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldr, int64_t ldy, int64_t ld_bits,
+                    int act, int dtype, void* stream) {
   MGB_REQUIRE(a && w && y, MGB_EINVAL, "matmul_bias_bt: NULL argument");
   int rc = check_dims("matmul_bias_bt", M, N, K);
   if (rc != MGB_OK) return rc;
@@ -1116,15 +1152,34 @@ MGB_EXPORT int mograd_b200_matmul_bias_bt_ex(const void* a, const void* w, const
   ep.act = act;
   ep.residual = residual;
   ep.ldr = ldr;
+  ep.bits_out = static_cast<uint32_t*>(relu_bits);
+  ep.ldbits = ld_bits;
+  const Operand oa{a, M, K, lda}, ow{w, N, K, ldw};
+  const bool tc = dtype == MGB_BF16 && tma_ok(oa) && tma_ok(ow);
+  MGB_REQUIRE(!relu_bits || tc, MGB_EUNSUPPORTED,
+              "matmul_bias_bt_relu_bits: needs bf16 operands with 16-byte-aligned rows (the tensor-core path)");
   if (dtype == MGB_F32)
     return gemm_simt<float>(static_cast<const float*>(a), static_cast<const float*>(w), static_cast<float*>(y), M, N, K,
                             lda, 1, ldw, 1, ldy, ep, st);
   MGB_REQUIRE(dtype == MGB_BF16, MGB_EDTYPE, "matmul_bias_bt: unsupported dtype code %d", dtype);
-  const Operand oa{a, M, K, lda}, ow{w, N, K, ldw};
-  if (tma_ok(oa) && tma_ok(ow))
-    return gemm_tc<false, false>(oa, ow, static_cast<bf16*>(y), ldy, ep, nullptr, M, N, K, nullptr, 0, false, st);
+  if (tc) return gemm_tc<false, false>(oa, ow, static_cast<bf16*>(y), ldy, ep, nullptr, M, N, K, nullptr, 0, false, st);
   return gemm_simt<bf16>(static_cast<const bf16*>(a), static_cast<const bf16*>(w), static_cast<bf16*>(y), M, N, K, lda,
                          1, ldw, 1, ldy, ep, st);
+}
+}  // namespace
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt_ex(const void* a, const void* w, const void* bias, const void* residual,
+                                             void* y, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw,
+                                             int64_t ldr, int64_t ldy, int act, int dtype, void* stream) {
+  return matmul_fwd_impl(a, w, bias, residual, y, nullptr, M, N, K, lda, ldw, ldr, ldy, 0, act, dtype, stream);
+}
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt_relu_bits(const void* a, const void* w, const void* bias, void* y,
+                                                    void* relu_bits, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                                    int64_t ldw, int64_t ldy, int64_t ld_bits, int dtype, void* stream) {
+  MGB_REQUIRE(relu_bits, MGB_EINVAL, "matmul_bias_bt_relu_bits: relu_bits is NULL");
+  MGB_REQUIRE(ld_bits >= (N + 31) / 32, MGB_EINVAL, "matmul_bias_bt_relu_bits: ld_bits=%lld < ceil(N/32)", (long long)ld_bits);
+  return matmul_fwd_impl(a, w, bias, nullptr, y, relu_bits, M, N, K, lda, ldw, 0, ldy, ld_bits, 1, dtype, stream);
 }
 
 MGB_EXPORT int mograd_b200_matmul_bias_bt(const void* a, const void* w, const void* bias, void* y, int64_t M,
@@ -1139,12 +1194,11 @@ MGB_EXPORT size_t mograd_b200_matmul_bias_bt_bwd_workspace_bytes(int64_t M, int6
   return rowsum_bytes(N) + splitk_bytes(N, K, kMaxSplits);
 }
 
-MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd_ex(const void* dy, const void* x, const void* w, const void* relu_y,
-                                                 const void* dx_residual, void* dx, void* dw, void* db, int64_t M,
-                                                 int64_t N, int64_t K, int64_t lddy, int64_t ldx, int64_t ldw,
-                                                 int64_t ld_relu_y, int64_t ld_dx_residual, int64_t lddx,
-                                                 int64_t lddw, int dtype, void* workspace, size_t workspace_bytes,
-                                                 void* stream) {
+namespace {
+int matmul_bwd_impl(const void* dy, const void* x, const void* w, const void* relu_y, const void* relu_bits,
+                    const void* dx_residual, void* dx, void* dw, void* db, int64_t M, int64_t N, int64_t K, int64_t lddy,
+                    int64_t ldx, int64_t ldw, int64_t ld_relu_y, int64_t ld_bits, int64_t ld_dx_residual, int64_t lddx,
+                    int64_t lddw, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
   MGB_REQUIRE(dy, MGB_EINVAL, "matmul_bias_bt_bwd: dy is NULL");
   MGB_REQUIRE(dx || dw || db, MGB_EINVAL, "matmul_bias_bt_bwd: no output requested");
   MGB_REQUIRE(!dx || w, MGB_EINVAL, "matmul_bias_bt_bwd: dX needs W");
@@ -1161,6 +1215,13 @@ MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd_ex(const void* dy, const void* x, 
   epx.ldm = ld_relu_y;
   epx.residual = dx_residual;
   epx.ldr = ld_dx_residual;
+  epx.bits_in = static_cast<const uint32_t*>(relu_bits);
+  epx.ldbits = ld_bits;
+  if (relu_bits && dx) {
+    const Operand ody0{dy, M, N, lddy}, ow0{w, N, K, ldw};
+    MGB_REQUIRE(dtype == MGB_BF16 && tma_ok(ody0) && tma_ok(ow0), MGB_EUNSUPPORTED,
+                "matmul_bias_bt_bwd_relu_bits: needs bf16 operands with 16-byte-aligned rows (the tensor-core path)");
+  }
   const Epilogue none;
   if (dtype == MGB_F32) {
     const float* dyf = static_cast<const float*>(dy);
@@ -1207,6 +1268,29 @@ MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd_ex(const void* dy, const void* x, 
   }
   if (db && !db_done) rc = colsum<bf16>(dy, db, M, N, lddy, st);
   return rc;
+}
+}  // namespace
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd_ex(const void* dy, const void* x, const void* w, const void* relu_y,
+                                                 const void* dx_residual, void* dx, void* dw, void* db, int64_t M,
+                                                 int64_t N, int64_t K, int64_t lddy, int64_t ldx, int64_t ldw,
+                                                 int64_t ld_relu_y, int64_t ld_dx_residual, int64_t lddx,
+                                                 int64_t lddw, int dtype, void* workspace, size_t workspace_bytes,
+                                                 void* stream) {
+  return matmul_bwd_impl(dy, x, w, relu_y, nullptr, dx_residual, dx, dw, db, M, N, K, lddy, ldx, ldw, ld_relu_y, 0,
+                         ld_dx_residual, lddx, lddw, dtype, workspace, workspace_bytes, stream);
+}
+
+MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd_relu_bits(const void* dy, const void* x, const void* w,
+                                                        const void* relu_bits, const void* dx_residual, void* dx,
+                                                        void* dw, void* db, int64_t M, int64_t N, int64_t K,
+                                                        int64_t lddy, int64_t ldx, int64_t ldw, int64_t ld_bits,
+                                                        int64_t ld_dx_residual, int64_t lddx, int64_t lddw, int dtype,
+                                                        void* workspace, size_t workspace_bytes, void* stream) {
+  MGB_REQUIRE(relu_bits, MGB_EINVAL, "matmul_bias_bt_bwd_relu_bits: relu_bits is NULL");
+  MGB_REQUIRE(ld_bits >= (K + 31) / 32, MGB_EINVAL, "matmul_bias_bt_bwd_relu_bits: ld_bits=%lld < ceil(K/32)", (long long)ld_bits);
+  return matmul_bwd_impl(dy, x, w, nullptr, relu_bits, dx_residual, dx, dw, db, M, N, K, lddy, ldx, ldw, 0, ld_bits,
+                         ld_dx_residual, lddx, lddw, dtype, workspace, workspace_bytes, stream);
 }
 
 MGB_EXPORT int mograd_b200_matmul_bias_bt_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw,

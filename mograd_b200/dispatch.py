@@ -74,9 +74,10 @@ def _rows2d(t: torch.Tensor) -> tuple[int, int, int]:
 # ----------------------------------------------------------------------------
 # matmul_bias_bt (dispatch.mojo:247-278)
 # ----------------------------------------------------------------------------
-def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None, residual=None):
-    """Y = A @ W.T (+ bias) (, ReLU) (+ residual): exec rule `matmul_bias_bt` / `matmul_bt`."""
-    _require_cuda(a, w, bias, residual)
+def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None, residual=None, relu_bits=None):
+    """Y = A @ W.T (+ bias) (, ReLU) (+ residual): exec rule `matmul_bias_bt` / `matmul_bt`.
+    relu_bits (int32 (M, ceil(N/32)), with act=1 and no residual): receives one bit per output, set where Y > 0."""
+    _require_cuda(a, w, bias, residual, relu_bits)
     M, K, lda = _rows2d(a)
     N, K2, ldw = _rows2d(w)
     if K2 != K:
@@ -84,6 +85,12 @@ def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None, residual=None):
     if out is None:
         out = torch.empty(a.shape[:-1] + (N,), dtype=a.dtype, device=a.device)
     _, _, ldy = _rows2d(out)
+    if relu_bits is not None:
+        if act != 1 or residual is not None:
+            raise KernelError("matmul_bias_bt", _lib.EINVAL, "relu_bits goes with act=1 and no residual")
+        call("mograd_b200_matmul_bias_bt_relu_bits", _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(relu_bits), M, N, K,
+             lda, ldw, ldy, relu_bits.stride(0), dtype_code(a), _stream())
+        return out
     ldr = _rows2d(residual)[2] if residual is not None else 0
     call("mograd_b200_matmul_bias_bt_ex", _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, lda, ldw,
          ldr, ldy, int(act), dtype_code(a), _stream())
@@ -91,10 +98,11 @@ def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None, residual=None):
 
 
 def matmul_bias_bt_bwd(dy, x, w, need_dx=True, need_dw=True, need_db=True, dx_out=None, dw_out=None, db_out=None,
-                       relu_y=None, dx_residual=None):
+                       relu_y=None, dx_residual=None, relu_bits=None):
     """(dX, dW, db) of Y = X @ W.T + b in one call; outputs not needed are None.
-    relu_y: ReLU output that produced X (dX is masked by relu_y > 0); dx_residual: added to dX."""
-    _require_cuda(dy, x, w, relu_y, dx_residual)
+    relu_y: ReLU output that produced X (dX is masked by relu_y > 0), or relu_bits: the same mask as one bit per
+    element (from matmul_bias_strided(..., relu_bits=)); dx_residual: added to dX."""
+    _require_cuda(dy, x, w, relu_y, dx_residual, relu_bits)
     M, N, lddy = _rows2d(dy)
     M2, K, ldx = _rows2d(x)
     N2, K2, ldw = _rows2d(w)
@@ -110,6 +118,11 @@ def matmul_bias_bt_bwd(dy, x, w, need_dx=True, need_dw=True, need_db=True, dx_ou
     lddw = dw.stride(0) if dw is not None else K
     ldm = _rows2d(relu_y)[2] if relu_y is not None else 0
     ldr = _rows2d(dx_residual)[2] if dx_residual is not None else 0
+    if relu_bits is not None:
+        call("mograd_b200_matmul_bias_bt_bwd_relu_bits", _ptr(dy), _ptr(x), _ptr(w), _ptr(relu_bits), _ptr(dx_residual),
+             _ptr(dx), _ptr(dw), _ptr(db), M, N, K, lddy, ldx, ldw, relu_bits.stride(0), ldr, lddx, lddw, code, _ptr(ws),
+             ws.numel(), _stream())
+        return dx, dw, db
     call("mograd_b200_matmul_bias_bt_bwd_ex", _ptr(dy), _ptr(x), _ptr(w), _ptr(relu_y), _ptr(dx_residual), _ptr(dx),
          _ptr(dw), _ptr(db), M, N, K, lddy, ldx, ldw, ldm, ldr, lddx, lddw, code, _ptr(ws), ws.numel(), _stream())
     return dx, dw, db

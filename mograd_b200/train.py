@@ -296,6 +296,12 @@ class TinyTransformer(_Model):
             self.saved.append(dict(ln1=new(T, d), qkv=new(T, 3 * d), ctx=new(T, d),
                                    lse=torch.empty((batch, n_heads, seq), dtype=torch.float32, device=dev),
                                    h=new(T, d), ln2=new(T, d), f1=new(T, d_ff)))
+        # ReLU mask of the feed-forward activation as one bit per element (bf16 tensor-core path only): the backward
+        # GEMM fetches T*d_ff/8 bytes instead of re-reading the activation
+        self.relu_bits = dtype == torch.bfloat16 and dev.type == "cuda" and d % 8 == 0 and d_ff % 8 == 0
+        if self.relu_bits:
+            for sv in self.saved:
+                sv["f1_bits"] = torch.empty((T, (d_ff + 31) // 32), dtype=torch.int32, device=dev)
         self.Vp = _pad8(vocab)
         self.logits_buf = new(T, self.Vp)
         self.logits = self.logits_buf[:, :vocab]
@@ -323,7 +329,8 @@ class TinyTransformer(_Model):
                                       lse_out=sv["lse"], o_bshd=True)
             K.matmul_bias_strided(sv["ctx"], P[f"Wo{l}"], out=sv["h"], residual=x)
             K.layer_norm_fwd_dispatch(sv["h"], P[f"g2_{l}"], P[f"be2_{l}"], out=sv["ln2"])
-            K.matmul_bias_strided(sv["ln2"], P[f"W1_{l}"], P[f"b1_{l}"], act=1, out=sv["f1"])
+            K.matmul_bias_strided(sv["ln2"], P[f"W1_{l}"], P[f"b1_{l}"], act=1, out=sv["f1"],
+                                  relu_bits=sv.get("f1_bits"))
             K.matmul_bias_strided(sv["f1"], P[f"W2_{l}"], out=self.x[l + 1], residual=sv["h"])
         K.matmul_bias_strided(self.x[L], P["lm_head"], out=self.logits)
         loss, dl = K.softmax_xent_fwd_bwd(self.logits, self.d_targets.view(-1), inplace=True)
@@ -336,7 +343,7 @@ class TinyTransformer(_Model):
             sv, x = self.saved[l], self.x[l]
             # FFN: out = h + W2 relu(W1 ln2 + b1)
             K.matmul_bias_bt_bwd(dx, sv["f1"], P[f"W2_{l}"], dx_out=self.t_ff, dw_out=G[f"W2_{l}"], need_db=False,
-                                 relu_y=sv["f1"])
+                                 relu_y=None if self.relu_bits else sv["f1"], relu_bits=sv.get("f1_bits"))
             K.matmul_bias_bt_bwd(self.t_ff, sv["ln2"], P[f"W1_{l}"], dx_out=self.t_b, dw_out=G[f"W1_{l}"],
                                  db_out=G[f"b1_{l}"])
             K.layer_norm_bwd_dispatch(self.t_b, sv["h"], P[f"g2_{l}"], dx_out=dx, dgamma_out=G[f"g2_{l}"],

@@ -186,3 +186,51 @@ def test_cta_pair_kernel(cuda, oracle, M, N, K):
     assert _status() == 0
     assert rel_err(dx.float().cpu().numpy(), wdx) <= TOL_BF16
     assert rel_err(dw.float().cpu().numpy(), wdw) <= TOL_BF16
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(256, 384, 128), (300, 1000, 72), (128, 64, 64), (1000, 3072, 256)])
+def test_relu_bit_mask_pair(cuda, oracle, M, N, K):
+    """Forward emits one bit per output (Y > 0); backward masked by the bits equals backward masked by Y itself."""
+    import torch
+    from mograd_b200 import dispatch as Kd
+
+    rng = np.random.default_rng(M + N + K)
+    a = bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    w = bf16_round((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32))
+    b = bf16_round(rng.standard_normal(N).astype(np.float32) * 0.1)
+    dev = lambda t: torch.from_numpy(t).to(cuda).bfloat16()
+    bits = torch.full((M, (N + 31) // 32), -1, dtype=torch.int32, device=cuda)
+    y = Kd.matmul_bias_strided(dev(a), dev(w), dev(b), act=1, relu_bits=bits)
+    y_ref = Kd.matmul_bias_strided(dev(a), dev(w), dev(b), act=1)
+    assert torch.equal(y, y_ref)
+    # the bits are exactly (y > 0), padding bits of the last word are clear
+    yy = (y.float().cpu().numpy() > 0)
+    pad = np.zeros((M, bits.shape[1] * 32), dtype=bool)
+    pad[:, :N] = yy
+    want_words = np.packbits(pad.reshape(M, -1, 32), axis=-1, bitorder="little").view(np.uint32).reshape(M, -1)
+    assert np.array_equal(bits.cpu().numpy().view(np.uint32), want_words)
+    # backward of the next layer (contraction over its outputs), masked either way
+    N2 = 96
+    w2 = bf16_round((rng.standard_normal((N2, N)) / np.sqrt(N)).astype(np.float32))
+    dy = bf16_round(rng.standard_normal((M, N2)).astype(np.float32))
+    res = bf16_round(rng.standard_normal((M, N)).astype(np.float32))
+    dx1, _, _ = Kd.matmul_bias_bt_bwd(dev(dy), y, dev(w2), need_dw=False, need_db=False, relu_y=y, dx_residual=dev(res))
+    dx2, _, _ = Kd.matmul_bias_bt_bwd(dev(dy), y, dev(w2), need_dw=False, need_db=False, relu_bits=bits,
+                                      dx_residual=dev(res))
+    assert torch.equal(dx1, dx2)
+    want = (dy.astype(np.float64) @ w2.astype(np.float64)) * yy + res
+    assert rel_err(dx2.float().cpu().numpy(), want) <= TOL_BF16
+
+
+@pytest.mark.gpu
+def test_relu_bit_mask_rejected_off_the_tensor_core_path(cuda):
+    import torch
+    from mograd_b200 import dispatch as Kd
+    from mograd_b200._lib import KernelError
+
+    a = torch.zeros((8, 16), device=cuda)
+    w = torch.zeros((40, 16), device=cuda)
+    bits = torch.zeros((8, 2), dtype=torch.int32, device=cuda)
+    with pytest.raises(KernelError):
+        Kd.matmul_bias_strided(a, w, None, act=1, relu_bits=bits)  # fp32 has no bit-mask path
