@@ -206,9 +206,13 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
         for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
       }
       if (e_bits_out) {
+        // v >= 0 here (the entry point fixes act = ReLU), so v > 0 <=> its bit pattern is a positive integer:
+        // adding 0x7fffffff carries into bit 31 exactly then, and a funnel shift appends that bit to the word
         uint32_t word = 0;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) word |= (v[j] > 0.f && col0 + j < p.N) ? (1u << j) : 0u;
+        for (int j = 0; j < 32; ++j) word = __funnelshift_l(__float_as_uint(v[j]) + 0x7fffffffu, word, 1);
+        word = __brev(word);  // element j -> bit j
+        if (col0 + 32 > p.N) word &= (1u << (p.N - col0)) - 1u;
         e_bits_out[static_cast<int64_t>(row) * p.ldbits + (col0 >> 5)] = word;
       }
       if (e_bits_in) {
