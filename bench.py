@@ -37,14 +37,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE config 2: README MLP
+    # the reference README's MLP
     "readme_mlp": dict(kind="mlp", dims=[4096, 4096, 4096, 10], batch=2048, tokens_per_step=2048,
                        desc="README MLP 4096-4096(ReLU)-LN-4096(ReLU)-10, batch 2048, bf16 (1 sample = 1 token)"),
-    # BASELINE config 3: char-level transformer
+    # the reference's char-level transformer example
     "char_transformer": dict(kind="tf", vocab=65, d_model=384, d_ff=1536, n_layers=6, n_heads=6, batch=64, seq=256,
                              tokens_per_step=64 * 256,
                              desc="char transformer vocab 65 ctx 256 L6 H6 d384, batch 64, bf16"),
-    # BASELINE config 5: GPT-2-small-shaped decoder
+    # GPT-2-small-shaped decoder (the configuration the tokens/s metric is quoted on)
     "gpt2_small": dict(kind="tf", vocab=50304, d_model=768, d_ff=3072, n_layers=12, n_heads=12, batch=16, seq=1024,
                        tokens_per_step=16 * 1024,
                        desc="GPT-2-small-shaped decoder L12 H12 d768 ctx 1024 vocab 50304, per-GPU batch 16, bf16"),
@@ -190,7 +190,7 @@ def dominant_gemm_roofline(cfg, peaks, device):
 
 
 def standalone_kernels(peaks, device):
-    """The kernels BASELINE's metric names, at its standalone shapes (config 4)."""
+    """The standalone kernels the metric names, at their standalone shapes."""
     import torch
     from mograd_b200 import dispatch as K
 

@@ -785,6 +785,259 @@ __global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
   }
 }
 
+// ------------------------------------------------- forward, D = 64: two CTAs per SM
+// With 64-wide heads a query tile needs half the shared memory and TMEM of the D = 128 kernel, so two CTAs fit on
+// an SM and run out of phase: the fill and drain of one (Q/K/V loads, first scores, output epilogue) hide behind
+// the steady state of the other, and their softmax phases interleave on the MUFU pipe.  To make them fit, a CTA is
+// 6 warps (TMA, MMA, 4 softmax warps), a softmax thread owns a whole row (all 128 scores in registers, so no
+// exchange of row maxima and a single TMEM read), S has one 128-column buffer that goes back to the MMA warp as
+// soon as it is in registers, V has one stage, and 256 TMEM columns are allocated.
+struct Fwd64Cfg {
+  static constexpr int D = 64;
+  static constexpr int TILE_BYTES = 128 * D * 2;  // 16 KB
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = TILE_BYTES;        // 2 stages
+  static constexpr int OFF_V = 3 * TILE_BYTES;    // 1 stage
+  static constexpr int OFF_P = 4 * TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_P + kPsBytes;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int COL_S = 0, COL_O = 128;
+  static constexpr int TMEM_COLS = 256;
+  static constexpr int THREADS = 192;
+};
+
+__global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
+    attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                         const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  using C = Fwd64Cfg;
+  constexpr int D = C::D;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
+  const uint32_t bar = base + C::OFF_BAR;
+  const uint32_t bar_q = bar;
+  auto bar_kf = [&](int s) { return bar + 8 + 8u * s; };
+  auto bar_ke = [&](int s) { return bar + 24 + 8u * s; };
+  const uint32_t bar_vf = bar + 40, bar_ve = bar + 48;
+  const uint32_t bar_sf = bar + 56;  // scores complete in TMEM
+  const uint32_t bar_sr = bar + 64;  // scores are in registers: the buffer is free
+  const uint32_t bar_pr = bar + 72;  // P written (and O rescaled)
+  const uint32_t bar_pv = bar + 80;  // O += P V complete
+  const uint32_t tmem_slot = bar + 88;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 88);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.S + 127) / 128;
+  const int i = nq - 1 - static_cast<int>(blockIdx.x);  // heavy (late) query tiles first
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int nkv = p.causal ? i + 1 : nq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_kf(s), 1);
+      mbar_init(bar_ke(s), 1);
+    }
+    mbar_init(bar_vf, 1);
+    mbar_init(bar_ve, 1);
+    mbar_init(bar_sf, 1);
+    mbar_init(bar_sr, 4);
+    mbar_init(bar_pr, 4);
+    mbar_init(bar_pv, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_gen;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(bar_q, C::TILE_BYTES);
+      tma_load_4d(base + C::OFF_Q, &tm_q, bar_q, 0, h, i * 128, b);
+      bool ok = true;
+      auto load_k = [&](int jt) {
+        const int s = jt & 1;
+        if (!mbar_wait(bar_ke(s), ((jt >> 1) & 1u) ^ 1u)) return false;
+        mbar_expect_tx(bar_kf(s), C::TILE_BYTES);
+        tma_load_4d(base + C::OFF_K + s * C::TILE_BYTES, &tm_k, bar_kf(s), 0, h, jt * 128, b);
+        return true;
+      };
+      ok = load_k(0);
+      for (int jt = 0; jt < nkv && ok; ++jt) {
+        if (jt + 1 < nkv) ok = load_k(jt + 1);  // K runs a tile ahead of V: the next scores start early
+        if (!ok || !mbar_wait(bar_ve, (jt & 1u) ^ 1u)) {
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(bar_vf, C::TILE_BYTES);
+        tma_load_4d(base + C::OFF_V, &tm_v, bar_vf, 0, h, jt * 128, b);
+      }
+      if (!ok) atomicExch(p.status, kErrFwdTma);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
+      const uint64_t dQ = base_k(base + C::OFF_Q), dP = base_k(base + C::OFF_P);
+      const uint64_t dV = base_mn(base + C::OFF_V);
+      auto issue_s = [&](int jt) -> bool {
+        const int s = jt & 1;
+        if (!mbar_wait(bar_kf(s), (jt >> 1) & 1u)) return false;
+        if (jt >= 1 && !mbar_wait(bar_sr, (jt - 1) & 1u)) return false;  // previous scores are in registers
+        tc_fence_after();
+        const uint64_t dK = base_k(base + C::OFF_K + s * C::TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S, desc_k(dQ, k), desc_k(dK, k), id_s, k > 0);
+        umma_commit(bar_ke(s));
+        umma_commit(bar_sf);
+        return true;
+      };
+      bool ok = mbar_wait(bar_q, 0) && issue_s(0);
+      for (int jt = 0; jt < nkv && ok; ++jt) {
+        if (jt + 1 < nkv) ok = issue_s(jt + 1);
+        ok = ok && mbar_wait(bar_pr, jt & 1u) && mbar_wait(bar_vf, jt & 1u);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_O, desc_k(dP, k), desc_mn(dV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar_ve);
+        umma_commit(bar_pv);
+      }
+      if (!ok) atomicExch(p.status, kErrFwdMma);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax: one thread per query row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const int qrow = i * 128 + r;
+    const float scale_log2 = p.scale * kLog2e;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int jt = 0; jt < nkv && ok; ++jt) {
+      if (!mbar_wait(bar_sf, jt & 1u)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t v[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + C::COL_S + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sr);
+      const bool diag = p.causal && (jt == i);
+      if (diag || (jt * 128 + 128 > p.S)) {
+#pragma unroll
+        for (int e = 0; e < 128; ++e) {
+          const int kvrow = jt * 128 + e;
+          const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
+          if (!keep) v[e] = __float_as_uint(-INFINITY);
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 128; e += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(v[e]));
+        mx1 = fmaxf(mx1, __uint_as_float(v[e + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(v[e + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(v[e + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // lazy reference maximum, as in the D = 128 kernel
+      const float m_cand = fmaxf(m, mx * scale_log2);
+      const float m_new = (jt == 0 || m_cand - m > 8.f) ? m_cand : m;
+      const float corr = (jt == 0) ? 0.f : ex2(m - m_new);
+      if (jt > 0 && !mbar_wait(bar_pv, (jt - 1) & 1u)) {  // P may be overwritten, O is stable
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (jt > 0 && __any_sync(0xffffffffu, m_new != m)) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+          tmem_st16(tmem + lane_base + C::COL_O + c0, o);
+        }
+        tmem_st_wait();
+      }
+      float rs0 = 0.f, rs1 = 0.f;
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+#pragma unroll
+      for (int c8 = 0; c8 < 16; ++c8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2(fmaf(__uint_as_float(v[c8 * 8 + 2 * e]), scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2, neg_m));
+          rs0 += p0;
+          rs1 += p1;
+          pk[e] = pack_bf16x2(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(gen + C::OFF_P + ps_chunk_off(r, c8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l = l * corr + (rs0 + rs1);
+      m = m_new;
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pr);
+    }
+    if (ok && !mbar_wait(bar_pv, (nkv - 1) & 1u)) ok = false;
+    if (!ok) {
+      if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
+    } else {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int qr = qrow < p.S ? qrow : 0;
+      bf16* orow = p.out + (p.o_bshd ? ((static_cast<int64_t>(b) * p.S + qr) * p.H + h) * D
+                                     : (static_cast<int64_t>(bh) * p.S + qr) * D);
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 16) {
+        uint32_t o[16];
+        tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
+        tmem_ld_wait();
+        if (qrow < p.S) {
+#pragma unroll
+          for (int e = 0; e < 16; e += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + e) = w;
+          }
+        }
+      }
+      if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------ host
 bool map_bshd(CUtensorMap* m, const void* ptr, int B, int S, int H, int D, int64_t ld) {
   const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
@@ -836,6 +1089,20 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
   return check_launch("attn_bwd_tc_kernel");
 }
 
+int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
+  using C = Fwd64Cfg;
+  CUtensorMap mq, mk, mv;
+  if (!map_bshd(&mq, q, p.B, p.S, p.H, 64, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 64, ld_qkv) ||
+      !map_bshd(&mv, v, p.B, p.S, p.H, 64, ld_qkv))
+    return MGB_ECUDA;
+  auto kern = attn_fwd_tc64_kernel;
+  int rc = set_smem(kern, C::SMEM);
+  if (rc != MGB_OK) return rc;
+  dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
+  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, p);
+  return check_launch("attn_fwd_tc64_kernel");
+}
+
 template <int D>
 int run_fwd(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
   using C = FwdCfg<D>;
@@ -871,7 +1138,7 @@ int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, i
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_fwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_fwd: B*H=%d exceeds 65535", B * H);
-  return D == 64 ? run_fwd<64>(q, k, v, p, lay.ld_qkv, st) : run_fwd<128>(q, k, v, p, lay.ld_qkv, st);
+  return D == 64 ? run_fwd64(q, k, v, p, lay.ld_qkv, st) : run_fwd<128>(q, k, v, p, lay.ld_qkv, st);
 }
 
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,

@@ -25,7 +25,7 @@ def rel_err(got, want):
     return float(np.max(np.abs(got - want))) / denom
 
 
-# Tolerances (BASELINE north_star): fp32 paths rel <= 1e-4; bf16 paths
+# Tolerances: fp32 paths rel <= 1e-4; bf16 paths
 # max-abs-err / max-abs-ref <= 2e-2 against the fp32/f64 CPU result.
 TOL_F32 = 1e-4
 TOL_BF16 = 2e-2

@@ -14,7 +14,7 @@ def _params_np(model):
 
 
 def test_mlp_c1_fp32_step_matches_oracle(cuda, oracle):
-    """BASELINE config 1: 784 -> 256 (ReLU) -> LayerNorm(256) -> 10, batch 128, fp32, seed 0."""
+    """The reference's MNIST MLP: 784 -> 256 (ReLU) -> LayerNorm(256) -> 10, batch 128, fp32, seed 0."""
     import torch
     from mograd_b200.train import MLP, AdamWConfig
     from oracle import ref_model
