@@ -452,9 +452,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // is [BK rows of the contraction][128 output rows], so the sum over the
     // contraction of output row t is a column sum of the tile in shared memory.
     if (A_MN && p.rowsum_partial) {
-      const int t = threadIdx.x - 10 * 32;  // 0..127: output row within the tile
-      const uint32_t col_off = (t >> 6) * (64 * BK * 2);
-      const int chunk = (t & 63) >> 3, elem = t & 7;
+      // A stage's A tile is two [BK rows][64 columns] boxes (128-byte rows, swizzled).  Lane (c << 3 | g) of warp w
+      // takes the 16-byte chunk 4w + c of the eight rows g, g+8, ... (the swizzle spreads the eight rows of a
+      // quarter-warp over all banks), keeps eight column sums in registers for the whole tile and folds the eight
+      // row groups with three shuffles at the end: eight 16-byte loads per thread and stage, no dependent chain.
+      const int wq = warp - 10;
+      const int g = lane & 7;
+      const int chunk16 = 4 * wq + (lane >> 3);  // 0..15 across the two boxes
+      const uint32_t lane_off = (chunk16 >> 3) * (64 * BK * 2) + g * 128 + (((chunk16 & 7) ^ g) << 4);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -465,7 +470,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tile_coords(p, rem, m_blk, n_blk);
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
-        float acc = 0.f;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase)) {
             atomicExch(p.status, kErrEpiWait);
@@ -473,11 +480,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           if (n_blk == 0) {
-            const unsigned char* tile_a = smem_gen + stage * T::STAGE_BYTES + col_off;
-#pragma unroll 8
-            for (int rr = 0; rr < BK; ++rr) {
-              const bf16 v = *reinterpret_cast<const bf16*>(tile_a + rr * 128 + ((chunk ^ (rr & 7)) << 4) + elem * 2);
-              acc += __bfloat162float(v);
+            const unsigned char* src = smem_gen + stage * T::STAGE_BYTES + lane_off;
+#pragma unroll
+            for (int rr = 0; rr < BK / 8; ++rr) {
+              float v[8];
+              load_vec(reinterpret_cast<const bf16*>(src + rr * 8 * 128), v);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[e] += v[e];
             }
           }
           __syncwarp();
@@ -487,8 +496,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             phase ^= 1u;
           }
         }
-        const int row = m_blk * BM + t;
-        if (ok && n_blk == 0 && row < p.M) p.rowsum_partial[static_cast<int64_t>(split) * p.M + row] = acc;
+        if (ok && n_blk == 0) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+            acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+            acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 4);
+          }
+          const int row0 = m_blk * BM + chunk16 * 8;  // chunk16 * 8 = box * 64 + chunk * 8
+          if (g == 0) {
+            float* dst = p.rowsum_partial + static_cast<int64_t>(split) * p.M + row0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              if (row0 + e < p.M) dst[e] = acc[e];
+          }
+        }
       }
     }
   } else {
