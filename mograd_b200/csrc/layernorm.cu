@@ -418,6 +418,14 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     cp_async_wait<kLnStages - 1>();
     const uint4* xs = reinterpret_cast<const uint4*>(ring + slot * 2 * SLOT);
     const uint4* ds = reinterpret_cast<const uint4*>(ring + slot * 2 * SLOT + SLOT);
+    // the residual gradient of this row is requested now and consumed in the second pass: its latency hides behind
+    // the first pass and the row reduction
+    uint4 r_raw[CHUNKS];
+    if (resid != nullptr && live) {
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j)
+        if (colj[j] < cols) r_raw[j] = *reinterpret_cast<const uint4*>(resid + row * cols + colj[j]);
+    }
     float xk[KEEP ? CHUNKS : 1][V], dk[KEEP ? CHUNKS : 1][V];
     float sums[4] = {0.f, 0.f, 0.f, 0.f};  // sum x, sum x^2, sum dy*g, sum dy*g*x
 #pragma unroll
@@ -473,7 +481,7 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
           }
           if (resid) {
             float rv[V];
-            unpack<T>(*reinterpret_cast<const uint4*>(resid + row * cols + colj[j]), rv);
+            unpack<T>(r_raw[j], rv);
 #pragma unroll
             for (int e = 0; e < V; ++e) o[e] += rv[e];
           }
