@@ -357,7 +357,9 @@ __device__ __forceinline__ void team_sum4(float (&v)[4], float* red, int parity,
 // Pass B writes dx = dy*g*rstd - rstd*c1 - xhat*rstd*c2 with two FMAs and
 // accumulates dgamma / dbeta.  When a lane's slice is small (KEEP) the
 // unpacked x and dy stay in registers between the passes.
-template <typename T, int WPR, int CHUNKS>
+// RESID: a residual gradient is added to dx (compiled out otherwise: the wide-row instantiations have no
+// registers to spare).
+template <typename T, int WPR, int CHUNKS, bool RESID>
 __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     ln_bwd_pipe_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid,
                        T* dx, float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
@@ -420,8 +422,9 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     const uint4* ds = reinterpret_cast<const uint4*>(ring + slot * 2 * SLOT + SLOT);
     // the residual gradient of this row is requested now and consumed in the second pass: its latency hides behind
     // the first pass and the row reduction
-    uint4 r_raw[CHUNKS];
-    if (resid != nullptr && live) {
+    constexpr bool EARLY = RESID && CHUNKS <= 3;  // wider rows fetch it where it is used instead
+    uint4 r_raw[EARLY ? CHUNKS : 1];
+    if (EARLY && live) {
 #pragma unroll
       for (int j = 0; j < CHUNKS; ++j)
         if (colj[j] < cols) r_raw[j] = *reinterpret_cast<const uint4*>(resid + row * cols + colj[j]);
@@ -479,9 +482,9 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
             dg[j][e] = fmaf(d[e], xhat, dg[j][e]);
             db[j][e] += d[e];
           }
-          if (resid) {
+          if (RESID) {
             float rv[V];
-            unpack<T>(r_raw[j], rv);
+            unpack<T>(EARLY ? r_raw[EARLY ? j : 0] : *reinterpret_cast<const uint4*>(resid + row * cols + colj[j]), rv);
 #pragma unroll
             for (int e = 0; e < V; ++e) o[e] += rv[e];
           }
@@ -594,7 +597,7 @@ int launch_bwd(const T* dy, const T* x, const T* g, const T* resid, T* dx, float
   const size_t pipe_smem = static_cast<size_t>(Shape<WPR>::WARPS) * LnStages<CHUNKS>::N * 2 * CHUNKS * 512;
   if (vec && pipe_smem + 1024 <= static_cast<size_t>(max_smem_optin())) {
     const size_t smem = pipe_smem;
-    auto k = ln_bwd_pipe_kernel<T, WPR, CHUNKS>;
+    auto k = resid ? ln_bwd_pipe_kernel<T, WPR, CHUNKS, true> : ln_bwd_pipe_kernel<T, WPR, CHUNKS, false>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     launch_pdl(k, dim3(grid), dim3(TH), smem, st, dy, x, g, resid, dx, part, rows, cols, eps);
     return check_launch("ln_bwd_pipe_kernel");
