@@ -121,10 +121,11 @@ class _Model:
         self.buckets = []
         hi = self.store.size
         while hi > 0:
-            lo = max(0, hi - per)
+            lo = max(0, (hi - per) // 128 * 128)  # 128-element boundaries keep every slice 16-byte aligned
             self.buckets.append((lo, hi))
             hi = lo
         self._next_bucket = 0
+        self._bucket_done = []  # (lo, hi, event recorded on the communication stream after the bucket's all-reduce)
 
     def _grads_ready_down_to(self, offset: int):
         """Everything in the flat gradient buffer at or above `offset` is final: exchange the buckets it covers."""
@@ -142,6 +143,9 @@ class _Model:
                 self.comm_stream.wait_event(ev)
                 with torch.cuda.stream(self.comm_stream):
                     dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
+                    done = torch.cuda.Event()
+                    done.record(self.comm_stream)
+                self._bucket_done.append((lo, hi, done))
             self.exchanged.append((lo, hi))
             self._next_bucket += 1
 
@@ -153,12 +157,13 @@ class _Model:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         self._next_bucket = 0
 
-    def optimizer_step(self):
-        self.step_count += 1
+    def optimizer_step(self, lo=0, hi=None):
+        """AdamW on the flat range [lo, hi) (everything by default); the caller advances step_count."""
         o = self.opt
         s = self.store
-        K.adamw_step(s.w, s.g, s.m, s.v, s.master, o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, self.step_count,
-                     grad_scale=1.0 / self.world_size)
+        hi = s.size if hi is None else hi
+        K.adamw_step(s.w[lo:hi], s.g[lo:hi], s.m[lo:hi], s.v[lo:hi], s.master[lo:hi], o.lr, o.beta1, o.beta2, o.eps,
+                     o.weight_decay, self.step_count, grad_scale=1.0 / self.world_size)
 
     # ---- host-facing call: host buffers in, loss out -------------------------------------
     def step(self, host_inputs, host_targets) -> float:
@@ -172,8 +177,21 @@ class _Model:
 
     def step_device(self):
         loss = self.forward_backward()
-        self._finish_exchange()
-        self.optimizer_step()
+        self.step_count += 1
+        if self.world_size > 1 and self.comm_stream is not None:
+            # The optimiser follows the exchange bucket by bucket: buckets reduced during the backward pass are
+            # updated while the last ones (the embedding gradient, final only when the backward pass ends) are
+            # still on the wire.
+            self._grads_ready_down_to(0)
+            main = torch.cuda.current_stream(self.device)
+            for lo, hi, done in self._bucket_done:
+                main.wait_event(done)
+                self.optimizer_step(lo, hi)
+            self._bucket_done.clear()
+            self._next_bucket = 0
+        else:
+            self._finish_exchange()
+            self.optimizer_step()
         return loss
 
 
