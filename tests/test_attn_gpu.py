@@ -43,7 +43,7 @@ def _run(cuda, q, k, v, dy, dt, causal, mask=None):
 
 # (B, S, H, D): tensor-core shapes (D 64 / 128; S multiple of 128, ragged, single tile, many tiles)
 TC_SHAPES = [(1, 128, 1, 64), (1, 128, 1, 128), (2, 256, 3, 64), (1, 384, 2, 128), (1, 200, 2, 64), (1, 80, 1, 128),
-             (2, 1024, 2, 64), (1, 1024, 1, 128)]
+             (2, 1024, 2, 64), (1, 1024, 1, 128), (1, 300, 2, 128), (1, 600, 1, 128), (1, 520, 1, 64)]
 
 
 @pytest.mark.parametrize("B,S,H,D", TC_SHAPES)
