@@ -24,10 +24,11 @@
 // D = 64 (drained one tile late, behind the next tile's MMAs); for D = 128 the
 // 512 columns are full, so dQ is accumulated over the dP columns once dP is read.
 //
-// Forward, per CTA = one query tile: S_j = Q K_j^T double-buffered in TMEM so
-// the next tile's scores are computed while 8 softmax warps work on this one;
-// P goes to shared memory as bf16, O += P V_j accumulates in TMEM and is
-// rescaled in place when a row maximum moves.
+// Forward: a softmax thread owns one query row (all 128 scores of a tile in registers: one TMEM read, no exchange
+// of row maxima); P goes to shared memory as bf16, O += P V_j accumulates in TMEM and is rescaled in place only
+// when the row maximum has grown by more than 2^8.  D = 128: one CTA owns two adjacent query tiles and walks the
+// key tiles once for both (the tensor pipe works for one tile while the other is in its exp phase); D = 64: small
+// six-warp CTAs, two per SM, run out of phase.
 #include <math.h>
 
 #include "attn.cuh"
@@ -509,282 +510,6 @@ __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ 
 }
 
 // =============================================================== forward
-template <int D>
-struct FwdCfg {
-  static constexpr int HALVES = D / 64;
-  static constexpr int TILE_BYTES = 128 * D * 2;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = TILE_BYTES;       // 2 stages
-  static constexpr int OFF_V = 3 * TILE_BYTES;   // 2 stages
-  static constexpr int OFF_P = 5 * TILE_BYTES;
-  static constexpr int OFF_X = OFF_P + kPsBytes;  // row-maximum exchange between the two warps of a quarter
-  static constexpr int OFF_BAR = OFF_X + 2 * 2 * 128 * 4;
-  static constexpr int SMEM = OFF_BAR + 256 + 1024;
-  static constexpr int COL_S = 0;    // two buffers of 128 columns
-  static constexpr int COL_O = 256;
-  static constexpr int TMEM_COLS = 512;
-  static constexpr int THREADS = 320;  // TMA warp, MMA warp, 8 softmax warps
-};
-
-template <int D>
-__global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
-    attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                       const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
-  using C = FwdCfg<D>;
-  extern __shared__ unsigned char smem_dyn[];
-  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
-  const uint32_t bar = base + C::OFF_BAR;
-  const uint32_t bar_q = bar;
-  auto bar_kf = [&](int s) { return bar + 8 + 8u * s; };
-  auto bar_ke = [&](int s) { return bar + 24 + 8u * s; };
-  auto bar_vf = [&](int s) { return bar + 40 + 8u * s; };
-  auto bar_ve = [&](int s) { return bar + 56 + 8u * s; };
-  auto bar_sf = [&](int s) { return bar + 72 + 8u * s; };   // S buffer full
-  auto bar_sr = [&](int s) { return bar + 88 + 8u * s; };   // S buffer read (free)
-  const uint32_t bar_pr = bar + 104;                        // P written (and O rescaled)
-  const uint32_t bar_pv = bar + 112;                        // O += P V complete
-  const uint32_t tmem_slot = bar + 120;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 120);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nq = (p.S + 127) / 128;
-  const int i = nq - 1 - static_cast<int>(blockIdx.x);  // heavy (late) query tiles first
-  const int bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
-  const int nkv = p.causal ? i + 1 : nq;
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar_q, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_kf(s), 1);
-      mbar_init(bar_ke(s), 1);
-      mbar_init(bar_vf(s), 1);
-      mbar_init(bar_ve(s), 1);
-      mbar_init(bar_sf(s), 1);
-      mbar_init(bar_sr(s), 8);
-    }
-    mbar_init(bar_pr, 8);
-    mbar_init(bar_pv, 1);
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot_gen;
-  pdl_launch_dependents();  // after the TMEM allocation: a successor takes the columns over only once they are freed
-  pdl_wait();
-
-  if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(bar_q, C::TILE_BYTES);
-#pragma unroll
-      for (int c = 0; c < C::HALVES; ++c) tma_load_4d(base + C::OFF_Q + c * kHalfBytes, &tm_q, bar_q, c * 64, h, i * 128, b);
-      for (int jt = 0; jt < nkv; ++jt) {
-        const int s = jt & 1;
-        const uint32_t ph = (jt >> 1) & 1u;
-        if (!mbar_wait(bar_ke(s), ph ^ 1u)) {
-          atomicExch(p.status, kErrFwdTma);
-          break;
-        }
-        mbar_expect_tx(bar_kf(s), C::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < C::HALVES; ++c)
-          tma_load_4d(base + C::OFF_K + s * C::TILE_BYTES + c * kHalfBytes, &tm_k, bar_kf(s), c * 64, h, jt * 128, b);
-        if (!mbar_wait(bar_ve(s), ph ^ 1u)) {
-          atomicExch(p.status, kErrFwdTma);
-          break;
-        }
-        mbar_expect_tx(bar_vf(s), C::TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < C::HALVES; ++c)
-          tma_load_4d(base + C::OFF_V + s * C::TILE_BYTES + c * kHalfBytes, &tm_v, bar_vf(s), c * 64, h, jt * 128, b);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
-      const uint64_t dQ = base_k(base + C::OFF_Q), dP = base_k(base + C::OFF_P);
-      auto issue_s = [&](int jt) -> bool {
-        const int s = jt & 1;
-        const uint32_t ph = (jt >> 1) & 1u;
-        if (!mbar_wait(bar_kf(s), ph)) return false;
-        if (jt >= 2 && !mbar_wait(bar_sr(s), ((jt - 2) >> 1) & 1u)) return false;
-        tc_fence_after();
-        const uint64_t dK = base_k(base + C::OFF_K + s * C::TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S + s * 128, desc_k(dQ, k), desc_k(dK, k), id_s, k > 0);
-        umma_commit(bar_ke(s));
-        umma_commit(bar_sf(s));
-        return true;
-      };
-      bool ok = mbar_wait(bar_q, 0) && issue_s(0);
-      for (int jt = 0; jt < nkv && ok; ++jt) {
-        if (jt + 1 < nkv) ok = issue_s(jt + 1);
-        const int s = jt & 1;
-        const uint32_t ph = (jt >> 1) & 1u;
-        ok = ok && mbar_wait(bar_pr, jt & 1u) && mbar_wait(bar_vf(s), ph);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t dV = base_mn(base + C::OFF_V + s * C::TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_O, desc_k(dP, k), desc_mn(dV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
-        umma_commit(bar_ve(s));
-        umma_commit(bar_pv);
-      }
-      if (!ok) atomicExch(p.status, kErrFwdMma);
-    }
-    __syncwarp();
-  } else {
-    // ------------------------------------------------------------ softmax
-    // 8 warps: TMEM lane quarter = warp % 4; the two warps of a quarter split the 128 key columns (and the D
-    // output columns) in halves and exchange their partial row maxima through shared memory once per tile.
-    const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const int r = quarter * 32 + lane;
-    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const int qrow = i * 128 + r;
-    const float scale_log2 = p.scale * kLog2e;
-    float* xmax = reinterpret_cast<float*>(gen + C::OFF_X);  // [2 parities][2 halves][128 rows]
-    constexpr int DH = D / 2;                                 // output columns this warp owns
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int jt = 0; jt < nkv && ok; ++jt) {
-      const int s = jt & 1;
-      if (!mbar_wait(bar_sf(s), (jt >> 1) & 1u)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const bool diag = p.causal && (jt == i);
-      const int kv0 = jt * 128 + half * 64;
-      const bool masked = diag || (jt * 128 + 128 > p.S);  // uniform over the CTA
-      const uint32_t s_cols = tmem + lane_base + C::COL_S + s * 128 + half * 64;
-      // this warp's 64 scores of the row are read from TMEM once and kept in registers for both passes; the
-      // score buffer goes back to the MMA warp as soon as the load has landed
-      uint32_t v[64];
-      tmem_ld32(s_cols, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-      tmem_ld32(s_cols + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_sr(s));
-      if (masked) {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          const int kvrow = kv0 + e;
-          const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
-          if (!keep) v[e] = __float_as_uint(-INFINITY);
-        }
-      }
-      float mx = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < 64; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-      xmax[(s * 2 + half) * 128 + r] = mx;
-      named_barrier(2, 256);
-      mx = fmaxf(mx, xmax[(s * 2 + (half ^ 1)) * 128 + r]);
-      // The reference maximum only follows the true one when it has grown by more than 2^8: until then the
-      // probabilities are at most 256 instead of 1, which bf16 and the fp32 accumulators hold equally well,
-      // and the accumulated output needs no rescaling pass through TMEM.  Tile 0 always sets it (every query
-      // row sees key 0), so it is finite from then on.
-      const float m_cand = fmaxf(m, mx * scale_log2);
-      const float m_new = (jt == 0 || m_cand - m > 8.f) ? m_cand : m;
-      const float corr = (jt == 0) ? 0.f : ex2(m - m_new);
-      // the previous P V product must be complete before P is overwritten or O rescaled
-      if (jt > 0 && !mbar_wait(bar_pv, (jt - 1) & 1u)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      if (jt > 0 && __any_sync(0xffffffffu, m_new != m)) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < DH; c0 += 16) {
-          uint32_t o[16];
-          tmem_ld16(tmem + lane_base + C::COL_O + half * DH + c0, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
-          tmem_st16(tmem + lane_base + C::COL_O + half * DH + c0, o);
-        }
-        tmem_st_wait();
-      }
-      // P = exp2(S*scale*log2e - m_new) -> bf16 in shared memory (masked scores are -inf -> 0)
-      float rs = 0.f;
-      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;  // a row with nothing to see yet stays all zero
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(v[c0 + e]), scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(v[c0 + e + 1]), scale_log2, neg_m));
-          rs += p0 + p1;
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-        }
-#pragma unroll
-        for (int t = 0; t < 4; ++t)
-          *reinterpret_cast<uint4*>(gen + C::OFF_P + ps_chunk_off(r, ((half * 64 + c0) >> 3) + t)) =
-              make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
-      }
-      l = l * corr + rs;
-      m = m_new;
-      fence_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pr);
-    }
-    if (ok && !mbar_wait(bar_pv, (nkv - 1) & 1u)) ok = false;
-    if (!ok) {
-      if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
-    } else {
-      tc_fence_after();
-      // the two halves hold partial row sums under the same maximum
-      float* xsum = xmax;  // all tiles are done: reuse the exchange buffer
-      named_barrier(2, 256);
-      xsum[half * 128 + r] = l;
-      named_barrier(2, 256);
-      l += xsum[(half ^ 1) * 128 + r];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int qr = qrow < p.S ? qrow : 0;
-      bf16* orow = p.out + (p.o_bshd ? ((static_cast<int64_t>(b) * p.S + qr) * p.H + h) * D
-                                     : (static_cast<int64_t>(bh) * p.S + qr) * D) + half * DH;
-#pragma unroll 1
-      for (int c0 = 0; c0 < DH; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(tmem + lane_base + C::COL_O + half * DH + c0, v);
-        tmem_ld_wait();
-        if (qrow < p.S) {
-#pragma unroll
-          for (int e = 0; e < 16; e += 8) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c0 + e) = o;
-          }
-        }
-      }
-      if (half == 0 && qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem, C::TMEM_COLS);
-  }
-}
-
 // ------------------------------------------------- forward, D = 64: two CTAs per SM
 // With 64-wide heads a query tile needs half the shared memory and TMEM of the D = 128 kernel, so two CTAs fit on
 // an SM and run out of phase: the fill and drain of one (Q/K/V loads, first scores, output epilogue) hide behind
@@ -1038,6 +763,286 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
   }
 }
 
+// ------------------------------------------- forward, D = 128: two query tiles per CTA
+// One CTA owns two adjacent 128-row query tiles (A = 2c, B = 2c + 1) and walks the key tiles once for both: every
+// K / V tile is loaded once and used twice, and while the four softmax warps of one tile are in their exp phase the
+// tensor pipe works for the other tile.  A softmax thread owns a whole row (128 scores in registers, one TMEM read,
+// no exchange of row maxima).  TMEM: S_A | S_B | O_A | O_B, 128 columns each; shared memory: Q_A, Q_B, two K
+// stages, one V stage, P_A, P_B (224 KB).  With a causal mask tile B has one key tile more than tile A.
+struct Fwd128Cfg {
+  static constexpr int D = 128;
+  static constexpr int TILE_BYTES = 128 * D * 2;  // 32 KB
+  static constexpr int OFF_Q = 0;                 // A, B
+  static constexpr int OFF_K = 2 * TILE_BYTES;    // 2 stages
+  static constexpr int OFF_V = 4 * TILE_BYTES;    // 1 stage
+  static constexpr int OFF_P = 5 * TILE_BYTES;    // A, B
+  static constexpr int OFF_BAR = 7 * TILE_BYTES;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int THREADS = 320;  // TMA, MMA, 4 softmax warps per query tile
+};
+
+__global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
+    attn_fwd_tc128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                            const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  using C = Fwd128Cfg;
+  constexpr int D = C::D;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
+  const uint32_t bar = base + C::OFF_BAR;
+  const uint32_t bar_q = bar;
+  auto bar_kf = [&](int s) { return bar + 8 + 8u * s; };
+  auto bar_ke = [&](int s) { return bar + 24 + 8u * s; };
+  const uint32_t bar_vf = bar + 40, bar_ve = bar + 48;
+  auto bar_sf = [&](int t) { return bar + 56 + 8u * t; };   // scores of tile t complete in TMEM
+  auto bar_sr = [&](int t) { return bar + 72 + 8u * t; };   // scores of tile t are in registers
+  auto bar_pr = [&](int t) { return bar + 88 + 8u * t; };   // P of tile t written (and O rescaled)
+  auto bar_pv = [&](int t) { return bar + 104 + 8u * t; };  // O_t += P_t V complete
+  const uint32_t tmem_slot = bar + 120;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 120);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.S + 127) / 128;
+  const int npair = (nq + 1) / 2;
+  const int c = npair - 1 - static_cast<int>(blockIdx.x);  // heavy (late) pairs first
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int qt[2] = {2 * c, 2 * c + 1};
+  int nkv[2];
+  nkv[0] = p.causal ? qt[0] + 1 : nq;
+  nkv[1] = qt[1] < nq ? (p.causal ? qt[1] + 1 : nq) : 0;
+  const int nmax = nkv[0] > nkv[1] ? nkv[0] : nkv[1];
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_kf(s), 1);
+      mbar_init(bar_ke(s), 1);
+      mbar_init(bar_sf(s), 1);
+      mbar_init(bar_sr(s), 4);
+      mbar_init(bar_pr(s), 4);
+      mbar_init(bar_pv(s), 1);
+    }
+    mbar_init(bar_vf, 1);
+    mbar_init(bar_ve, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_gen;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(bar_q, 2 * C::TILE_BYTES);  // rows past the sequence arrive as zeros
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_4d(base + C::OFF_Q + t * C::TILE_BYTES + hf * kHalfBytes, &tm_q, bar_q, hf * 64, h, qt[t] * 128, b);
+      bool ok = true;
+      auto load_k = [&](int jt) {
+        const int s = jt & 1;
+        if (!mbar_wait(bar_ke(s), ((jt >> 1) & 1u) ^ 1u)) return false;
+        mbar_expect_tx(bar_kf(s), C::TILE_BYTES);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_4d(base + C::OFF_K + s * C::TILE_BYTES + hf * kHalfBytes, &tm_k, bar_kf(s), hf * 64, h, jt * 128, b);
+        return true;
+      };
+      ok = load_k(0);
+      for (int jt = 0; jt < nmax && ok; ++jt) {
+        if (jt + 1 < nmax) ok = load_k(jt + 1);  // K runs a tile ahead of V
+        if (!ok || !mbar_wait(bar_ve, (jt & 1u) ^ 1u)) {
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(bar_vf, C::TILE_BYTES);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_4d(base + C::OFF_V + hf * kHalfBytes, &tm_v, bar_vf, hf * 64, h, jt * 128, b);
+      }
+      if (!ok) atomicExch(p.status, kErrFwdTma);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
+      const uint64_t dV = base_mn(base + C::OFF_V);
+      // scores of key tile jt for every query tile that still has work there
+      auto issue_s = [&](int jt) -> bool {
+        const int s = jt & 1;
+        if (!mbar_wait(bar_kf(s), (jt >> 1) & 1u)) return false;
+        const uint64_t dK = base_k(base + C::OFF_K + s * C::TILE_BYTES);
+        for (int t = 0; t < 2; ++t) {
+          if (jt >= nkv[t]) continue;
+          if (jt >= 1 && !mbar_wait(bar_sr(t), (jt - 1) & 1u)) return false;  // previous scores are in registers
+          tc_fence_after();
+          const uint64_t dQ = base_k(base + C::OFF_Q + t * C::TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) umma_ss(tmem + t * 128, desc_k(dQ, k), desc_k(dK, k), id_s, k > 0);
+          umma_commit(bar_sf(t));
+        }
+        umma_commit(bar_ke(s));
+        return true;
+      };
+      bool ok = mbar_wait(bar_q, 0) && issue_s(0);
+      for (int jt = 0; jt < nmax && ok; ++jt) {
+        if (jt + 1 < nmax) ok = issue_s(jt + 1);
+        ok = ok && mbar_wait(bar_vf, jt & 1u);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (jt >= nkv[t]) continue;
+          if (!mbar_wait(bar_pr(t), jt & 1u)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t dP = base_k(base + C::OFF_P + t * kPsBytes);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_ss(tmem + 256 + t * 128, desc_k(dP, k), desc_mn(dV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
+          umma_commit(bar_pv(t));
+        }
+        if (ok) umma_commit(bar_ve);  // after the last product that reads this V tile
+      }
+      if (!ok) atomicExch(p.status, kErrFwdMma);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax: one thread per query row
+    const int t = (warp - 2) >> 2;  // query tile of this warp
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t col_s = t * 128, col_o = 256 + t * 128;
+    unsigned char* ps = gen + C::OFF_P + t * kPsBytes;
+    const int i = qt[t];
+    const int qrow = i * 128 + r;
+    const int my_nkv = nkv[t];
+    const float scale_log2 = p.scale * kLog2e;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int jt = 0; jt < my_nkv && ok; ++jt) {
+      if (!mbar_wait(bar_sf(t), jt & 1u)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t v[128];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld32(tmem + lane_base + col_s + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[cc * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sr(t));
+      const bool diag = p.causal && (jt == i);
+      if (diag || (jt * 128 + 128 > p.S)) {
+#pragma unroll
+        for (int e = 0; e < 128; ++e) {
+          const int kvrow = jt * 128 + e;
+          const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
+          if (!keep) v[e] = __float_as_uint(-INFINITY);
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 128; e += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(v[e]));
+        mx1 = fmaxf(mx1, __uint_as_float(v[e + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(v[e + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(v[e + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const float m_cand = fmaxf(m, mx * scale_log2);
+      const float m_new = (jt == 0 || m_cand - m > 8.f) ? m_cand : m;  // lazy reference maximum
+      const float corr = (jt == 0) ? 0.f : ex2(m - m_new);
+      if (jt > 0 && !mbar_wait(bar_pv(t), (jt - 1) & 1u)) {  // P may be overwritten, O is stable
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (jt > 0 && __any_sync(0xffffffffu, m_new != m)) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(tmem + lane_base + col_o + c0, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+          tmem_st16(tmem + lane_base + col_o + c0, o);
+        }
+        tmem_st_wait();
+      }
+      float rs0 = 0.f, rs1 = 0.f;
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+#pragma unroll
+      for (int c8 = 0; c8 < 16; ++c8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2(fmaf(__uint_as_float(v[c8 * 8 + 2 * e]), scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2, neg_m));
+          rs0 += p0;
+          rs1 += p1;
+          pk[e] = pack_bf16x2(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(ps + ps_chunk_off(r, c8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l = l * corr + (rs0 + rs1);
+      m = m_new;
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pr(t));
+    }
+    if (ok && my_nkv > 0 && !mbar_wait(bar_pv(t), (my_nkv - 1) & 1u)) ok = false;
+    if (!ok) {
+      if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
+    } else if (my_nkv > 0) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int qr = qrow < p.S ? qrow : 0;
+      bf16* orow = p.out + (p.o_bshd ? ((static_cast<int64_t>(b) * p.S + qr) * p.H + h) * D
+                                     : (static_cast<int64_t>(bh) * p.S + qr) * D);
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 16) {
+        uint32_t o[16];
+        tmem_ld16(tmem + lane_base + col_o + c0, o);
+        tmem_ld_wait();
+        if (qrow < p.S) {
+#pragma unroll
+          for (int e = 0; e < 16; e += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + e) = w;
+          }
+        }
+      }
+      if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------ host
 bool map_bshd(CUtensorMap* m, const void* ptr, int B, int S, int H, int D, int64_t ld) {
   const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
@@ -1089,6 +1094,21 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
   return check_launch("attn_bwd_tc_kernel");
 }
 
+int run_fwd128x2(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
+  using C = Fwd128Cfg;
+  CUtensorMap mq, mk, mv;
+  if (!map_bshd(&mq, q, p.B, p.S, p.H, 128, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 128, ld_qkv) ||
+      !map_bshd(&mv, v, p.B, p.S, p.H, 128, ld_qkv))
+    return MGB_ECUDA;
+  auto kern = attn_fwd_tc128x2_kernel;
+  int rc = set_smem(kern, C::SMEM);
+  if (rc != MGB_OK) return rc;
+  const int nq = (p.S + 127) / 128;
+  dim3 grid(static_cast<unsigned>((nq + 1) / 2), static_cast<unsigned>(p.B * p.H));
+  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, p);
+  return check_launch("attn_fwd_tc128x2_kernel");
+}
+
 int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
   using C = Fwd64Cfg;
   CUtensorMap mq, mk, mv;
@@ -1101,21 +1121,6 @@ int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
   launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, p);
   return check_launch("attn_fwd_tc64_kernel");
-}
-
-template <int D>
-int run_fwd(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
-  using C = FwdCfg<D>;
-  CUtensorMap mq, mk, mv;
-  if (!map_bshd(&mq, q, p.B, p.S, p.H, D, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, D, ld_qkv) ||
-      !map_bshd(&mv, v, p.B, p.S, p.H, D, ld_qkv))
-    return MGB_ECUDA;
-  auto kern = attn_fwd_tc_kernel<D>;
-  int rc = set_smem(kern, C::SMEM);
-  if (rc != MGB_OK) return rc;
-  dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
-  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, p);
-  return check_launch("attn_fwd_tc_kernel");
 }
 
 }  // namespace
@@ -1138,7 +1143,7 @@ int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, i
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_fwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_fwd: B*H=%d exceeds 65535", B * H);
-  return D == 64 ? run_fwd64(q, k, v, p, lay.ld_qkv, st) : run_fwd<128>(q, k, v, p, lay.ld_qkv, st);
+  return D == 64 ? run_fwd64(q, k, v, p, lay.ld_qkv, st) : run_fwd128x2(q, k, v, p, lay.ld_qkv, st);
 }
 
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
