@@ -1049,15 +1049,18 @@ template <bool A_MN, bool B_MN>
 int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epilogue& ep, bf16* rowsum_out, int64_t M,
             int64_t N, int64_t K, void* ws, size_t ws_bytes, bool allow_split, cudaStream_t st) {
   const int BN = choose_bn(N);
-  // CTA pairs (256 x 256 tiles) for products large enough to fill the GPU with them and with a long contraction
-  // (measured: with 12 k-blocks per tile the pair's cluster-wide accumulator hand-off costs more than the saved
-  // L2 traffic; from 32 k-blocks on the pair wins); db is fused only in the single-CTA kernel
+  // CTA pairs (256 x 256 tiles) for products large enough to fill the GPU with them.  Measured at 12 k-blocks per
+  // tile: plain products are 2-5% faster on pairs (less L2 traffic per flop), products with an elementwise
+  // epilogue 3-7% slower (the longer drain meets the cluster-wide accumulator hand-off); from 32 k-blocks on the
+  // pair always wins.  db is fused only in the single-CTA kernel.
   const bool plain = !ep.relu_mask && !ep.residual && !ep.bits_out && !ep.bits_in;
   const bool may_split = allow_split && plain;
   const int64_t tiles1 = ((M + BM - 1) / BM) * ((N + BN - 1) / BN), tiles2 = ((M + 255) / 256) * ((N + 255) / 256);
   const int splits1 = may_split ? choose_splits(tiles1, K, sm_count()) : 1;
   const int splits2 = may_split ? choose_splits(tiles2, K, sm_count() / 2) : 1;
-  const bool pair = !rowsum_out && BN == 256 && M >= 512 && K >= 32 * BK && tiles2 * splits2 >= sm_count() / 4;
+  const bool fused_ep = ep.bias || ep.act || ep.relu_mask || ep.residual || ep.bits_out || ep.bits_in;
+  const bool pair = !rowsum_out && BN == 256 && M >= 512 && K >= (fused_ep ? 32 : 8) * BK &&
+                    tiles2 * splits2 >= sm_count() / 4;
   const int bm = pair ? 256 : BM;
   GemmParams p{};
   p.M = static_cast<int>(M);
