@@ -183,7 +183,7 @@ def dominant_gemm_roofline(cfg, peaks, device):
     ms = time_launches(lambda: K.matmul_bias_strided(a, w, None, out=out), 10, flush)
     flops = 2.0 * M * N * Kd
     ach = flops / (ms * 1e-3) / 1e12
-    return dict(bound="tensor", kernel=f"gemm_tc2_kernel (matmul_bias_bt {M}x{N}x{Kd})" if cfg["kind"] != "mlp" else f"gemm_tc_kernel (matmul_bias_bt {M}x{N}x{Kd})", achieved=round(ach, 1),
+    return dict(bound="tensor", kernel=f"gemm_tc2_kernel (matmul_bias_bt {M}x{N}x{Kd})", achieved=round(ach, 1),
                 peak=peaks["tflops"], unit="TFLOP/s", frac=round(ach / peaks["tflops"], 4), traffic=ROOFLINE_TRAFFIC.get(cfg.get("name")),
                 algorithmic_flops=flops, algorithmic_bytes=2.0 * (M * Kd + N * Kd + M * N),
                 peak_source=peaks["source"], ms_per_launch=round(ms, 4))
