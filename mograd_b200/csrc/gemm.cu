@@ -1035,7 +1035,6 @@ int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st
       n = sm_count() / 2;
     }
     resident = n < sm_count() / 2 ? n : sm_count() / 2;
-    if (getenv("MGB_DEBUG")) fprintf(stderr, "gemm_tc2: %d resident CTA pairs\n", resident);
   }
   const int max_clusters = resident;
   const int clusters = total < max_clusters ? total : max_clusters;
