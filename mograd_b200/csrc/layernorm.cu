@@ -119,18 +119,25 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     b_raw[j] = load_chunk<T, VEC>(beta, col, cols);
   }
 
-  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * S::TEAMS; r0 < rows;
-       r0 += static_cast<int64_t>(gridDim.x) * S::TEAMS) {
-    const int64_t row = r0 + team;
-    const bool live = row < rows;
-    const T* xr = x + (live ? row : 0) * cols;
-    uint4 x_raw[CHUNKS];
-    float sx = 0.f;
+  // the next row of this team is requested before the current one is reduced: one row is always in flight
+  const int64_t r_step = static_cast<int64_t>(gridDim.x) * S::TEAMS;
+  uint4 x_next[CHUNKS];
+  auto fetch = [&](int64_t row) {
 #pragma unroll
     for (int j = 0; j < CHUNKS; ++j) {
       const int64_t col = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
-      x_raw[j] = live ? load_chunk<T, VEC>(xr, col, cols) : make_uint4(0, 0, 0, 0);
+      x_next[j] = row < rows ? load_chunk<T, VEC>(x + row * cols, col, cols) : make_uint4(0, 0, 0, 0);
     }
+  };
+  fetch(static_cast<int64_t>(blockIdx.x) * S::TEAMS + team);
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * S::TEAMS; r0 < rows; r0 += r_step) {
+    const int64_t row = r0 + team;
+    const bool live = row < rows;
+    uint4 x_raw[CHUNKS];
+    float sx = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) x_raw[j] = x_next[j];
+    fetch(row + r_step);
 #pragma unroll
     for (int j = 0; j < CHUNKS; ++j) {
       float v[V];
