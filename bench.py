@@ -116,16 +116,16 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- model + data
-def build_model(cfg, device, world, pg, seed):
+def build_model(cfg, device, world, pg, seed, bucket_mb=64):
     import torch
     from mograd_b200.train import MLP, TinyTransformer
 
     if cfg["kind"] == "mlp":
         return MLP(cfg["dims"], cfg["batch"], dtype=torch.bfloat16, device=device, seed=seed, world_size=world,
-                   process_group=pg)
+                   process_group=pg, bucket_bytes=bucket_mb << 20)
     return TinyTransformer(cfg["vocab"], cfg["d_model"], cfg["d_ff"], cfg["n_layers"], cfg["n_heads"], cfg["batch"],
                            cfg["seq"], dtype=torch.bfloat16, device=device, seed=seed, world_size=world,
-                           process_group=pg)
+                           process_group=pg, bucket_bytes=bucket_mb << 20)
 
 
 def make_batch(cfg, seed, pinned=True):
@@ -374,6 +374,7 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="skip the standalone kernel section")
     ap.add_argument("--case", default=None, help="run one small kernel case --reps times and exit (for profiling)")
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--bucket-mb", type=int, default=64, help="gradient all-reduce bucket size (N > 1)")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to stdout; the contract is one JSON line there.  Everything
     # but that line goes to stderr: fd 1 is pointed at fd 2 until emit() restores it.
@@ -443,7 +444,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
         pg = dist.group.WORLD
     peaks = load_peaks()
-    model = build_model(cfg, device, world, pg, seed=0)
+    model = build_model(cfg, device, world, pg, seed=0, bucket_mb=args.bucket_mb)
     hx, hy = make_batch(cfg, seed=100 + rank)
     model.d_inputs.copy_(hx)
     model.d_targets.copy_(hy)
