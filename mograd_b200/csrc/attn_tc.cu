@@ -115,6 +115,10 @@ struct BwdCfg {
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
   static constexpr int COL_DQ = LATE ? 384 : COL_DP;
+  // D = 64 also has 64 columns left for dS as a bf16 TMEM operand: dQ = dS K then reads its A operand from TMEM
+  // instead of shared memory (one operand stream less on the shared-memory port)
+  static constexpr bool DS_TMEM = LATE;
+  static constexpr int COL_DSA = 448;
   static constexpr int TMEM_COLS = 512;
   static constexpr int THREADS = 608;  // TMA warp, MMA warp, 16 compute warps, dQ reduction warp
 };
@@ -256,7 +260,12 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
           umma_ss(tmem + C::COL_DK, desc_mn(dDS_mn, k), desc_mn(dQ_mn, k), id_mm, k > 0 ? 1u : acc);
         umma_commit(bar_qe(it % C::QST));
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_DQ, desc_k(dDS_k, k), desc_mn(dK_mn, k), id_km, k > 0);
+        for (int k = 0; k < 8; ++k) {
+          if (C::DS_TMEM)
+            umma_ts(tmem + C::COL_DQ, tmem + C::COL_DSA + k * 8, desc_mn(dK_mn, k), id_km, k > 0);
+          else
+            umma_ss(tmem + C::COL_DQ, desc_k(dDS_k, k), desc_mn(dK_mn, k), id_km, k > 0);
+        }
         umma_commit(bar_dqf);
       };
       auto wait_q = [&](int it) { return mbar_wait(bar_qf(it % C::QST), (it / C::QST) & 1u); };
@@ -438,7 +447,12 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         *reinterpret_cast<uint4*>(gen + C::OFF_P + off) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
         *reinterpret_cast<uint4*>(gen + C::OFF_DS + off) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
       }
+      if (C::DS_TMEM) {  // dS once more as packed bf16 pairs: 16 TMEM columns per 32 key columns
+        tmem_st16(tmem + lane_base + C::COL_DSA + cg * 16, dk);
+        tmem_st_wait();
+      }
       fence_async_smem();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pds);
       if (C::LATE) {
