@@ -530,17 +530,17 @@ __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ 
 // the steady state of the other, and their softmax phases interleave on the MUFU pipe.  To make them fit, a CTA is
 // 6 warps (TMA, MMA, 4 softmax warps), a softmax thread owns a whole row (all 128 scores in registers, so no
 // exchange of row maxima and a single TMEM read), S has one 128-column buffer that goes back to the MMA warp as
-// soon as it is in registers, V has one stage, and 256 TMEM columns are allocated.
+// soon as it is in registers, V has one stage, and 256 TMEM columns are allocated: S 128, O 64, and P as packed bf16
+// pairs in the last 64, so the P V product reads its A operand from TMEM and P never touches shared memory.
 struct Fwd64Cfg {
   static constexpr int D = 64;
   static constexpr int TILE_BYTES = 128 * D * 2;  // 16 KB
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = TILE_BYTES;        // 2 stages
   static constexpr int OFF_V = 3 * TILE_BYTES;    // 1 stage
-  static constexpr int OFF_P = 4 * TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_P + kPsBytes;
+  static constexpr int OFF_BAR = 4 * TILE_BYTES;  // P lives in TMEM
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
-  static constexpr int COL_S = 0, COL_O = 128;
+  static constexpr int COL_S = 0, COL_O = 128, COL_P = 192;  // P: 128 bf16 per row as 64 packed columns
   static constexpr int TMEM_COLS = 256;
   static constexpr int THREADS = 192;
 };
@@ -629,7 +629,7 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
     if (lane == 0) {
       constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
-      const uint64_t dQ = base_k(base + C::OFF_Q), dP = base_k(base + C::OFF_P);
+      const uint64_t dQ = base_k(base + C::OFF_Q);
       const uint64_t dV = base_mn(base + C::OFF_V);
       auto issue_s = [&](int jt) -> bool {
         const int s = jt & 1;
@@ -650,7 +650,8 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_O, desc_k(dP, k), desc_mn(dV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 8; ++k)  // P is a TMEM operand: 8 packed columns per 16 keys
+          umma_ts(tmem + C::COL_O, tmem + C::COL_P + k * 8, desc_mn(dV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
         umma_commit(bar_ve);
         umma_commit(bar_pv);
       }
@@ -721,21 +722,21 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
       float rs0 = 0.f, rs1 = 0.f;
       const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
 #pragma unroll
-      for (int c8 = 0; c8 < 16; ++c8) {
-        uint32_t pk[4];
+      for (int c32 = 0; c32 < 4; ++c32) {
+        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(v[c8 * 8 + 2 * e]), scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2, neg_m));
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = ex2(fmaf(__uint_as_float(v[c32 * 32 + 2 * e]), scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(v[c32 * 32 + 2 * e + 1]), scale_log2, neg_m));
           rs0 += p0;
           rs1 += p1;
           pk[e] = pack_bf16x2(p0, p1);
         }
-        *reinterpret_cast<uint4*>(gen + C::OFF_P + ps_chunk_off(r, c8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        tmem_st16(tmem + lane_base + C::COL_P + c32 * 16, pk);
       }
+      tmem_st_wait();
       l = l * corr + (rs0 + rs1);
       m = m_new;
-      fence_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pr);
