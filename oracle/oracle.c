@@ -29,16 +29,43 @@
 /* ------------------------------------------------------------------------ */
 ORC_API void orc_matmul_bias_bt(const float* a, const float* w, const float* bias, float* y,
                                 int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldy) {
-#pragma omp parallel for schedule(static)
-  for (int64_t m = 0; m < M; ++m) {
-    const float* ar = a + m * lda;
-    for (int64_t n = 0; n < N; ++n) {
-      const float* wr = w + n * ldw;
-      double acc = 0.0;
+  /* 4 x 4 output blocks share their operand loads; every output is still one float64 dot product over k. */
+  const int64_t MB = (M + 3) / 4, NB = (N + 3) / 4;
+#pragma omp parallel for schedule(static) collapse(2)
+  for (int64_t mb = 0; mb < MB; ++mb) {
+    for (int64_t nb = 0; nb < NB; ++nb) {
+      const int64_t m0 = mb * 4, n0 = nb * 4;
+      const int64_t mr = M - m0 < 4 ? M - m0 : 4, nr = N - n0 < 4 ? N - n0 : 4;
+      if (mr == 4 && nr == 4) {
+        const float *a0 = a + m0 * lda, *a1 = a0 + lda, *a2 = a1 + lda, *a3 = a2 + lda;
+        const float *w0 = w + n0 * ldw, *w1 = w0 + ldw, *w2 = w1 + ldw, *w3 = w2 + ldw;
+        double c00 = 0, c01 = 0, c02 = 0, c03 = 0, c10 = 0, c11 = 0, c12 = 0, c13 = 0;
+        double c20 = 0, c21 = 0, c22 = 0, c23 = 0, c30 = 0, c31 = 0, c32 = 0, c33 = 0;
+#pragma omp simd reduction(+ : c00, c01, c02, c03, c10, c11, c12, c13, c20, c21, c22, c23, c30, c31, c32, c33)
+        for (int64_t k = 0; k < K; ++k) {
+          const double x0 = a0[k], x1 = a1[k], x2 = a2[k], x3 = a3[k];
+          const double v0 = w0[k], v1 = w1[k], v2 = w2[k], v3 = w3[k];
+          c00 += x0 * v0; c01 += x0 * v1; c02 += x0 * v2; c03 += x0 * v3;
+          c10 += x1 * v0; c11 += x1 * v1; c12 += x1 * v2; c13 += x1 * v3;
+          c20 += x2 * v0; c21 += x2 * v1; c22 += x2 * v2; c23 += x2 * v3;
+          c30 += x3 * v0; c31 += x3 * v1; c32 += x3 * v2; c33 += x3 * v3;
+        }
+        const double c[4][4] = {{c00, c01, c02, c03}, {c10, c11, c12, c13}, {c20, c21, c22, c23}, {c30, c31, c32, c33}};
+        for (int i = 0; i < 4; ++i)
+          for (int j = 0; j < 4; ++j)
+            y[(m0 + i) * ldy + n0 + j] = (float)(c[i][j] + (bias ? (double)bias[n0 + j] : 0.0));
+      } else {
+        for (int64_t m = m0; m < m0 + mr; ++m)
+          for (int64_t n = n0; n < n0 + nr; ++n) {
+            const float* ar = a + m * lda;
+            const float* wr = w + n * ldw;
+            double acc = 0.0;
 #pragma omp simd reduction(+ : acc)
-      for (int64_t k = 0; k < K; ++k) acc += (double)ar[k] * (double)wr[k];
-      if (bias) acc += (double)bias[n];
-      y[m * ldy + n] = (float)acc;
+            for (int64_t k = 0; k < K; ++k) acc += (double)ar[k] * (double)wr[k];
+            if (bias) acc += (double)bias[n];
+            y[m * ldy + n] = (float)acc;
+          }
+      }
     }
   }
 }
@@ -53,20 +80,33 @@ ORC_API void orc_matmul_bias_bt(const float* a, const float* w, const float* bia
 ORC_API void orc_matmul_bias_bt_bwd(const float* dy, const float* x, const float* w, float* dx, float* dw,
                                     float* db, int64_t M, int64_t N, int64_t K, int64_t lddy, int64_t ldx,
                                     int64_t ldw, int64_t lddx, int64_t lddw) {
+  /* dX and dW: four output rows share every load of the streamed operand; float64 accumulators per row. */
   if (dx) {
 #pragma omp parallel
     {
-      double* acc = (double*)malloc(sizeof(double) * (size_t)K);
+      double* acc = (double*)malloc(sizeof(double) * (size_t)K * 4);
+      double *q0 = acc, *q1 = acc + K, *q2 = acc + 2 * K, *q3 = acc + 3 * K;
 #pragma omp for schedule(static)
-      for (int64_t m = 0; m < M; ++m) {
-        for (int64_t k = 0; k < K; ++k) acc[k] = 0.0;
+      for (int64_t mb = 0; mb < (M + 3) / 4; ++mb) {
+        const int64_t m0 = mb * 4, mr = M - m0 < 4 ? M - m0 : 4;
+        for (int64_t k = 0; k < 4 * K; ++k) acc[k] = 0.0;
         for (int64_t n = 0; n < N; ++n) {
-          const double g = (double)dy[m * lddy + n];
+          const double g0 = (double)dy[m0 * lddy + n];
+          const double g1 = mr > 1 ? (double)dy[(m0 + 1) * lddy + n] : 0.0;
+          const double g2 = mr > 2 ? (double)dy[(m0 + 2) * lddy + n] : 0.0;
+          const double g3 = mr > 3 ? (double)dy[(m0 + 3) * lddy + n] : 0.0;
           const float* wr = w + n * ldw;
 #pragma omp simd
-          for (int64_t k = 0; k < K; ++k) acc[k] += g * (double)wr[k];
+          for (int64_t k = 0; k < K; ++k) {
+            const double wv = (double)wr[k];
+            q0[k] += g0 * wv;
+            q1[k] += g1 * wv;
+            q2[k] += g2 * wv;
+            q3[k] += g3 * wv;
+          }
         }
-        for (int64_t k = 0; k < K; ++k) dx[m * lddx + k] = (float)acc[k];
+        for (int64_t i = 0; i < mr; ++i)
+          for (int64_t k = 0; k < K; ++k) dx[(m0 + i) * lddx + k] = (float)acc[i * K + k];
       }
       free(acc);
     }
@@ -74,17 +114,30 @@ ORC_API void orc_matmul_bias_bt_bwd(const float* dy, const float* x, const float
   if (dw) {
 #pragma omp parallel
     {
-      double* acc = (double*)malloc(sizeof(double) * (size_t)K);
+      double* acc = (double*)malloc(sizeof(double) * (size_t)K * 4);
+      double *q0 = acc, *q1 = acc + K, *q2 = acc + 2 * K, *q3 = acc + 3 * K;
 #pragma omp for schedule(static)
-      for (int64_t n = 0; n < N; ++n) {
-        for (int64_t k = 0; k < K; ++k) acc[k] = 0.0;
+      for (int64_t nb = 0; nb < (N + 3) / 4; ++nb) {
+        const int64_t n0 = nb * 4, nr = N - n0 < 4 ? N - n0 : 4;
+        for (int64_t k = 0; k < 4 * K; ++k) acc[k] = 0.0;
         for (int64_t m = 0; m < M; ++m) {
-          const double g = (double)dy[m * lddy + n];
+          const float* dr = dy + m * lddy + n0;
+          const double g0 = (double)dr[0];
+          const double g1 = nr > 1 ? (double)dr[1] : 0.0;
+          const double g2 = nr > 2 ? (double)dr[2] : 0.0;
+          const double g3 = nr > 3 ? (double)dr[3] : 0.0;
           const float* xr = x + m * ldx;
 #pragma omp simd
-          for (int64_t k = 0; k < K; ++k) acc[k] += g * (double)xr[k];
+          for (int64_t k = 0; k < K; ++k) {
+            const double xv = (double)xr[k];
+            q0[k] += g0 * xv;
+            q1[k] += g1 * xv;
+            q2[k] += g2 * xv;
+            q3[k] += g3 * xv;
+          }
         }
-        for (int64_t k = 0; k < K; ++k) dw[n * lddw + k] = (float)acc[k];
+        for (int64_t i = 0; i < nr; ++i)
+          for (int64_t k = 0; k < K; ++k) dw[(n0 + i) * lddw + k] = (float)acc[i * K + k];
       }
       free(acc);
     }
