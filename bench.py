@@ -10,8 +10,13 @@ by rank 0:
   value        whole-job tokens/s with the batch already resident in HBM,
                timed with CUDA events over exactly K steps, max over ranks
   e2e          the same metric through the host-facing call Model.step(): the
-               batch comes from pinned host memory every step and the loss is
-               read back to the host every step
+               batch comes from pinned host memory every step (the copy of the
+               next batch is issued under the current step's kernels) and the
+               loss is read back to the host every step
+  dp           N > 1 only: a check that the overlapped bf16 bucket exchange
+               gives the gradients a plain fp32 all-reduce gives, that the
+               replicas hold identical parameters after the timed steps, and
+               how long per step the main stream stood waiting for a bucket
   roofline     the dominant kernel of the step, timed live here with CUDA
                events on the launching stream
   kernels      the standalone kernels the metric names (flash-attention
@@ -50,8 +55,9 @@ WORKLOADS = {
                        desc="GPT-2-small-shaped decoder L12 H12 d768 ctx 1024 vocab 50304, per-GPU batch 16, bf16"),
 }
 DEFAULT_WORKLOAD = "gpt2_small"
-# DRAM bytes (read + write) of one launch of the roofline kernel, from one profiler capture of that exact launch
-# (dram__bytes_read.sum + dram__bytes_write.sum; profiles/matmul_bias_bt_16384x50304x768_bf16.md)
+# DRAM bytes (read + write) of one launch of the roofline kernel: dram__bytes_read.sum + dram__bytes_write.sum of
+# one profiler capture of that exact launch.  A stored figure, not something this run measures (a profiler cannot
+# run inside a timed benchmark); the JSON line says so in roofline.traffic_source.
 ROOFLINE_TRAFFIC = {"gpt2_small": 137.9e6 + 1596.0e6}
 
 
@@ -146,16 +152,23 @@ def make_batch(cfg, seed, pinned=True):
 
 # ----------------------------------------------------------------------------- kernel micro-benchmarks
 def time_launches(fn, reps, flush=None):
-    """Average device time of fn() in ms, CUDA events on the current stream, L2 flushed before each launch."""
+    """Average device time of fn() in ms, CUDA events on the current stream, L2 flushed before each launch.
+
+    The flush doubles as a head start for the host: it is repeated until it keeps the GPU busy for about 150 us,
+    so the start event, the launch and the stop event are all queued before the GPU reaches them.  (With a
+    shorter flush the GPU passes the start event and then idles until the host has prepared the launch, which
+    adds the host's 15-20 us of launch preparation to every kernel shorter than that.)"""
     import torch
 
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    repeat = 1 if flush is None else max(1, int((1 << 30) // max(1, flush.numel() * flush.element_size())))
     total = 0.0
     for _ in range(reps):
         if flush is not None:
-            flush.fill_(1)
+            for _ in range(repeat):
+                flush.fill_(1)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         fn()
@@ -186,7 +199,8 @@ def dominant_gemm_roofline(cfg, peaks, device):
     return dict(bound="tensor", kernel=f"gemm_tc2_kernel (matmul_bias_bt {M}x{N}x{Kd})", achieved=round(ach, 1),
                 peak=peaks["tflops"], unit="TFLOP/s", frac=round(ach / peaks["tflops"], 4), traffic=ROOFLINE_TRAFFIC.get(cfg.get("name")),
                 algorithmic_flops=flops, algorithmic_bytes=2.0 * (M * Kd + N * Kd + M * N),
-                peak_source=peaks["source"], ms_per_launch=round(ms, 4))
+                peak_source=peaks["source"], ms_per_launch=round(ms, 4),
+                traffic_source="stored profiler capture of this launch (dram read + write bytes), not measured by this run")
 
 
 def standalone_kernels(peaks, device):
@@ -217,7 +231,7 @@ def standalone_kernels(peaks, device):
                                                          algorithmic_bytes=nbytes)
     del x, dl
     # LayerNorm backward
-    for rows, cols in ((16384, 768), (65536, 4096)):
+    for rows, cols in ((16384, 768), (131072, 768), (65536, 4096)):
         xx = torch.randn((rows, cols), generator=g, device=device).bfloat16()
         dy = torch.randn((rows, cols), generator=g, device=device).bfloat16()
         gm = torch.ones(cols, device=device).bfloat16()
@@ -229,24 +243,26 @@ def standalone_kernels(peaks, device):
                                                          frac_hbm=round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4),
                                                          algorithmic_bytes=nbytes)
         del xx, dy, dx
-    # flash-attention backward, B=4 H=16 S=4096 D=128 causal
-    try:
-        B, S, H, D = 4, 4096, 16, 128
-        q, k, v = (torch.randn((B, S, H, D), generator=g, device=device).bfloat16() for _ in range(3))
-        do = torch.randn((B, H, S, D), generator=g, device=device).bfloat16()
-        o, lse = K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False)
-        outs = (torch.empty_like(q), torch.empty_like(q), torch.empty_like(q))
-        ms_f = time_launches(lambda: K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False, out=o, lse_out=lse), 5,
-                             flush)
-        ms_b = time_launches(lambda: K.flash_attn_bwd_dispatch(do, o, q, k, v, None, lse, None, True, False, out=outs),
-                             5, flush)
-        ff, fb = 2.0 * B * H * S * S * D, 5.0 * B * H * S * S * D
-        out["flash_attn_fwd_B4_H16_S4096_D128_causal"] = dict(ms=round(ms_f, 4), tflops=round(ff / ms_f / 1e9, 1),
-                                                              frac_tensor=round(ff / ms_f / 1e9 / peaks["tflops"], 4))
-        out["flash_attn_bwd_B4_H16_S4096_D128_causal"] = dict(ms=round(ms_b, 4), tflops=round(fb / ms_b / 1e9, 1),
-                                                              frac_tensor=round(fb / ms_b / 1e9 / peaks["tflops"], 4))
-    except Exception as e:  # reported, never hidden
-        out["flash_attn"] = dict(error=str(e)[:200])
+    # flash-attention forward / backward, causal: the standalone shape and the train step's own shape
+    for B, S, H, D in ((4, 4096, 16, 128), (16, 1024, 12, 64)):
+        try:
+            q, k, v = (torch.randn((B, S, H, D), generator=g, device=device).bfloat16() for _ in range(3))
+            do = torch.randn((B, H, S, D), generator=g, device=device).bfloat16()
+            o, lse = K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False)
+            outs = (torch.empty_like(q), torch.empty_like(q), torch.empty_like(q))
+            ms_f = time_launches(lambda: K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False, out=o, lse_out=lse),
+                                 10, flush)
+            ms_b = time_launches(lambda: K.flash_attn_bwd_dispatch(do, o, q, k, v, None, lse, None, True, False,
+                                                                   out=outs), 10, flush)
+            ff, fb = 2.0 * B * H * S * S * D, 5.0 * B * H * S * S * D
+            tag = f"B{B}_H{H}_S{S}_D{D}_causal"
+            out[f"flash_attn_fwd_{tag}"] = dict(ms=round(ms_f, 4), tflops=round(ff / ms_f / 1e9, 1),
+                                                frac_tensor=round(ff / ms_f / 1e9 / peaks["tflops"], 4))
+            out[f"flash_attn_bwd_{tag}"] = dict(ms=round(ms_b, 4), tflops=round(fb / ms_b / 1e9, 1),
+                                                frac_tensor=round(fb / ms_b / 1e9 / peaks["tflops"], 4))
+            del q, k, v, do, o, outs
+        except Exception as e:  # reported, never hidden
+            out[f"flash_attn_B{B}_S{S}"] = dict(error=str(e)[:200])
     return out
 
 
@@ -445,9 +461,18 @@ def main():
         pg = dist.group.WORLD
     peaks = load_peaks()
     model = build_model(cfg, device, world, pg, seed=0, bucket_mb=args.bucket_mb)
-    hx, hy = make_batch(cfg, seed=100 + rank)
-    model.d_inputs.copy_(hx)
-    model.d_targets.copy_(hy)
+    # two different batches per rank, alternated step by step (both resident for the device-timed loop)
+    batches = [make_batch(cfg, seed=100 + rank), make_batch(cfg, seed=7100 + rank)]
+    for k, (bx, by) in enumerate(batches):
+        model.use_slot(k)
+        model.d_inputs.copy_(bx)
+        model.d_targets.copy_(by)
+    hx, hy = batches[0]
+    dp = None
+    if world > 1:
+        # the overlapped bf16 bucket exchange against a plain fp32 all-reduce of the same local gradients
+        err = model.check_data_parallel()
+        dp = dict(grad_exchange_max_rel_err=round(err, 6), grad_exchange_ok=bool(err <= 2e-2))
 
     def barrier():
         if world > 1:
@@ -457,17 +482,22 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    for _ in range(max(3, args.warmup)):
+    for i in range(max(3, args.warmup)):
+        model.use_slot(i & 1)
         model.step_device()
     barrier()
     l0 = lib.mograd_b200_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        model.use_slot(i & 1)
         loss = model.step_device()
     e1.record()
     barrier()
     launches = lib.mograd_b200_launch_count() - l0
+    from mograd_b200 import _lib as _abi
+
+    _abi.check_device_status("bench: timed steps")  # a bounded device-side wait that gave up voids the run
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device=device)
@@ -477,12 +507,12 @@ def main():
     value = cfg["tokens_per_step"] * world / (ms_per_step * 1e-3)
 
     # end to end through the host-facing call: host batch in, loss out, every step
-    for _ in range(2):
-        model.step(hx, hy)
+    for i in range(2):
+        model.step(*batches[i & 1], prefetch=batches[(i + 1) & 1])
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        last = model.step(hx, hy)
+    for i in range(args.steps):
+        last = model.step(*batches[i & 1], prefetch=batches[(i + 1) & 1])
     barrier()
     e2e_s = time.perf_counter() - t0
     if world > 1:
@@ -490,6 +520,23 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = t.item()
     clocks = sampler.stop() if rank == 0 else None  # samples span warm-up, the timed steps and the end-to-end steps
+    if world > 1:
+        # how long the main stream stands waiting for each bucket's all-reduce (CUDA events around every wait)
+        model.time_exposed = True
+        for i in range(4):
+            model.use_slot(i & 1)
+            model.step_device()
+        torch.cuda.synchronize()
+        model.time_exposed = False
+        per_step = [[b.elapsed_time(a) for _, _, b, a in marks] for marks in model.exposed_events[1:]]
+        tot = torch.tensor([sum(map(sum, per_step)) / max(1, len(per_step)),
+                            sum(p[-1] for p in per_step if p) / max(1, len(per_step))], device=device)
+        dist.all_reduce(tot, op=dist.ReduceOp.MAX)
+        dp.update(allreduce_exposed_ms_per_step=round(float(tot[0]), 4),
+                  last_bucket_exposed_ms_per_step=round(float(tot[1]), 4), buckets=len(model.buckets),
+                  in_sync=model.replicas_in_sync(),
+                  note="exposed = time the main stream waited on a bucket's all-reduce before its AdamW launch, max "
+                       "over ranks; the last bucket holds the embedding gradient, final only when backward ends")
     e2e_val = cfg["tokens_per_step"] * world * args.steps / e2e_s
     h2d = hx.numel() * hx.element_size() + hy.numel() * hy.element_size()
 
@@ -497,6 +544,11 @@ def main():
         line = dict(base, value=round(value, 1), ms_per_step=round(ms_per_step, 4), clocks=clocks,
                     e2e=dict(value=round(e2e_val, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4),
                     gpu_launches=int(launches), loss=round(float(last), 4))
+        line["config"]["batches"] = "two seeded batches per rank, alternated every step"
+        if dp is not None:
+            line["dp"] = dp
+            line["dp_in_sync"] = dp["in_sync"]
+            line["allreduce_exposed_ms"] = dp["allreduce_exposed_ms_per_step"]
         line["roofline"] = dominant_gemm_roofline(cfg, peaks, device)
         if world == 1:
             if not args.no_kernels:

@@ -62,11 +62,30 @@ unsigned long long mograd_b200_launch_count(void);
 /* Message for the last negative status returned on this host thread. */
 const char* mograd_b200_last_error(void);
 
-/* Debug aid, synchronises the device: reads (and clears) the status word the
+/* Synchronises the device: reads (and clears) the status word the
  * tensor-core kernels write when one of their bounded waits on a TMA or MMA
  * barrier gives up (code 0 = none; 101 producer, 102 MMA issuer, 103 epilogue
- * of the GEMM; 2xx attention).  No counterpart in the reference. */
+ * of the GEMM; 2xx attention; 901 the self-test below).  A wait that gives up
+ * is discovered on the GPU after the entry point has returned, so a 0 return
+ * code of an entry point does NOT cover it: a host that wants that assurance
+ * reads this word at a point where it synchronises anyway (the train-step
+ * runner does so once per step) and must treat the outputs of the affected
+ * step as garbage when the code is non-zero.  No counterpart in the
+ * reference. */
 int mograd_b200_device_status(int* code, int* detail);
+
+/* The same word without a synchronisation of its own: enqueues a copy of the
+ * status word (4 ints: code, detail, 2 reserved) into host_words (pinned
+ * host memory) on `stream`; the caller looks at host_words[0] after its own
+ * next synchronisation of that stream.  Does not clear the word: call
+ * mograd_b200_device_status for that once a non-zero code has been seen. */
+int mograd_b200_device_status_async(int* host_words, void* stream);
+
+/* Self-test of the bounded waits: one warp waits up to limit_us microseconds
+ * (1..100000) on a barrier that nothing completes, then records code 901 and
+ * the microseconds it waited (detail) in the status word and returns; the
+ * context stays usable.  No counterpart in the reference. */
+int mograd_b200_selftest_wait_expiry(unsigned int limit_us, void* stream);
 
 /* ------------------------------------------------------------------------
  * matmul_bias_bt:  Y[m,n] = sum_k A[m,k] * W[n,k] + bias[n]
@@ -117,7 +136,8 @@ int mograd_b200_layer_norm_fwd(const void* x, const void* gamma, const void* bet
  * 1337-1366; signature LayerNormBwdKernel, dispatch.mojo:317-329; kernels
  * mograd/runtime/gpu/kernels/normalization.mojo:85-400).  dgamma / dbeta are
  * plain stores: the caller need not zero them (the reference's dispatch
- * does, dispatch.mojo:343-344).  cols <= 16384, as in the reference.
+ * does, dispatch.mojo:343-344).  cols <= 16384, as in the reference.  dx may
+ * alias dy (every row's dy is read before its dx is written).
  * ---------------------------------------------------------------------- */
 size_t mograd_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t cols, int dtype);
 int mograd_b200_layer_norm_bwd(const void* dy, const void* x, const void* gamma, void* dx, void* dgamma,

@@ -35,6 +35,8 @@ SIGNATURES = {
     "mograd_b200_launch_count": (ctypes.c_ulonglong, []),
     "mograd_b200_last_error": (ctypes.c_char_p, []),
     "mograd_b200_device_status": (_int, [ctypes.POINTER(_int), ctypes.POINTER(_int)]),
+    "mograd_b200_device_status_async": (_int, [_p, _p]),
+    "mograd_b200_selftest_wait_expiry": (_int, [ctypes.c_uint, _p]),
     "mograd_b200_matmul_bias_bt": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _p]),
     "mograd_b200_matmul_bias_bt_bwd_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "mograd_b200_matmul_bias_bt_bwd": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
@@ -114,3 +116,18 @@ def call(name: str, *args) -> None:
 
 def query(name: str, *args) -> int:
     return int(getattr(load(), name)(*args))
+
+
+def device_status() -> tuple[int, int]:
+    """(code, detail) of the device status word, cleared by the read; synchronises the device."""
+    code, detail = _int(0), _int(0)
+    call("mograd_b200_device_status", ctypes.byref(code), ctypes.byref(detail))
+    return code.value, detail.value
+
+
+def check_device_status(where: str) -> None:
+    """Raise KernelError when a kernel's bounded wait gave up since the last check (its outputs are garbage)."""
+    code, detail = device_status()
+    if code != 0:
+        raise KernelError(where, ECUDA, f"a bounded device-side wait gave up (status {code}, detail {detail}); "
+                                        "the results of the kernels launched since the last check are invalid")

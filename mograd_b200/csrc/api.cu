@@ -112,18 +112,61 @@ static bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, const void* ba
 __device__ int g_device_status[4];
 
 int* device_status_ptr() {
-  static int* ptrs[kMaxDev] = {};
+  struct Slot {
+    std::once_flag once;
+    int* ptr = nullptr;
+  };
+  static Slot slots[kMaxDev];
   int d = 0;
   cudaGetDevice(&d);
   if (d < 0 || d >= kMaxDev) d = 0;
-  if (!ptrs[d]) {
+  Slot& sl = slots[d];
+  std::call_once(sl.once, [&] {  // once per device, with that device current
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_device_status) == cudaSuccess) ptrs[d] = static_cast<int*>(p);
+    if (cudaGetSymbolAddress(&p, g_device_status) == cudaSuccess) sl.ptr = static_cast<int*>(p);
+  });
+  return sl.ptr;
+}
+
+// One warp waits, with the given limit, on an mbarrier phase that nothing ever completes; when the wait gives up
+// it records code 901 and the elapsed microseconds in the status word and the kernel returns normally.
+__global__ void __launch_bounds__(32) wait_expiry_kernel(unsigned long long limit_ns, int* status) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  const uint32_t bar = sm100::smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(bar, 1);
+    sm100::mbar_fence_init();
   }
-  return ptrs[d];
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const unsigned long long t0 = sm100::global_ns();
+    if (!sm100::mbar_wait_limit(bar, 0, limit_ns)) {
+      status[1] = static_cast<int>((sm100::global_ns() - t0) / 1000ull);
+      atomicExch(status, 901);
+    }
+  }
 }
 
 }  // namespace mgb
+
+MGB_EXPORT int mograd_b200_device_status_async(int* host_words, void* stream) {
+  MGB_REQUIRE(host_words, MGB_EINVAL, "device_status_async: host_words is NULL");
+  int* p = mgb::device_status_ptr();
+  if (!p) return mgb::fail(MGB_ECUDA, "device_status_async: status word not addressable on this device");
+  const cudaError_t e =
+      cudaMemcpyAsync(host_words, p, 4 * sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return mgb::fail(MGB_ECUDA, "device_status_async: %s", cudaGetErrorString(e));
+  return MGB_OK;
+}
+
+MGB_EXPORT int mograd_b200_selftest_wait_expiry(unsigned int limit_us, void* stream) {
+  MGB_REQUIRE(limit_us >= 1 && limit_us <= 100000, MGB_EINVAL, "selftest_wait_expiry: limit_us=%u outside 1..100000",
+              limit_us);
+  int* st = mgb::device_status_ptr();
+  if (!st) return mgb::fail(MGB_ECUDA, "selftest_wait_expiry: status word not addressable on this device");
+  mgb::wait_expiry_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(1000ull * limit_us, st);
+  return mgb::check_launch("wait_expiry_kernel");
+}
 
 MGB_EXPORT int mograd_b200_abi_version(void) { return MOGRAD_B200_ABI_VERSION; }
 MGB_EXPORT unsigned long long mograd_b200_launch_count(void) { return mgb::g_launches.load(std::memory_order_relaxed); }

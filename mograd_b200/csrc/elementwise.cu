@@ -15,10 +15,10 @@ inline int ew_grid(int64_t work_items) {
   return g < 1 ? 1 : static_cast<int>(g);
 }
 
-// dx = dy where y > 0 else 0 (y is the ReLU output)
+// dx = dy where y > 0 else 0 (y is the ReLU output).  dx may alias dy: no __restrict__ on either.
 template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
-    relu_grad_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, int64_t n, int vec) {
+    relu_grad_kernel(const T* __restrict__ y, const T* dy, T* dx, int64_t n, int vec) {
   constexpr int V = Vec<T>::N;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kEwThreads;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x;
@@ -34,9 +34,10 @@ __global__ void __launch_bounds__(kEwThreads)
   for (int64_t i = nv * V + tid; i < n; i += stride) dx[i] = to_f32(y[i]) > 0.f ? dy[i] : from_f32<T>(0.f);
 }
 
+// dst may alias a or b: no __restrict__.
 template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
-    add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ dst, int64_t n, int vec) {
+    add_kernel(const T* a, const T* b, T* dst, int64_t n, int vec) {
   constexpr int V = Vec<T>::N;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kEwThreads;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x;

@@ -10,8 +10,14 @@
 // dgamma / dbeta contributions in fp32 registers across all rows its team
 // visits, teams are folded inside the CTA, each CTA writes one partial row to
 // the workspace and a second small kernel sums the partial rows in a fixed
-// order.  Both statistics and partials are fp32 (the reference accumulates
-// the partials in the I/O dtype, normalization.mojo:114-115).
+// order (folding them inside the first launch was measured: whichever CTAs
+// finish last have too few loads in flight, 20 -> 42 us at 16384 x 768).
+// Both statistics and partials are fp32 (the reference accumulates the
+// partials in the I/O dtype, normalization.mojo:114-115).  The row arithmetic
+// uses the packed fp32 pair instructions of sm_100 (two lanes per issue
+// slot): the kernel is bound by instruction issue, not by DRAM latency.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mgb {
@@ -30,6 +36,24 @@ __device__ __forceinline__ uint4 pack(const float (&v)[Vec<T>::N]) {
   uint4 r;
   store_vec(reinterpret_cast<T*>(&r), v);
   return r;
+}
+
+// The same 16 bytes as fp32 pairs (element 2i in .x, 2i+1 in .y), the operand shape of the packed fp32 instructions.
+__device__ __forceinline__ void unpack2(const uint4& r, float2 (&v)[4], const __nv_bfloat16*) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+}
+__device__ __forceinline__ void unpack2(const uint4& r, float2 (&v)[2], const float*) {
+  v[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+  v[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
+}
+__device__ __forceinline__ uint4 pack2(const float2 (&v)[4], const __nv_bfloat16*) {
+  return make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y), pack_bf16x2(v[2].x, v[2].y),
+                    pack_bf16x2(v[3].x, v[3].y));
+}
+__device__ __forceinline__ uint4 pack2(const float2 (&v)[2], const float*) {
+  return make_uint4(__float_as_uint(v[0].x), __float_as_uint(v[0].y), __float_as_uint(v[1].x), __float_as_uint(v[1].y));
 }
 
 // Loads Vec<T>::N elements starting at column `col` of a row; out-of-range
@@ -187,8 +211,8 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
 
 template <typename T, int WPR, int CHUNKS, bool VEC>
 __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
-    ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid,
-                  T* dx, float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
+    ln_bwd_kernel(const T* dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid, T* dx,
+                  float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
   constexpr int V = Vec<T>::N;
   using S = Shape<WPR>;
   extern __shared__ float fold[];  // [2][cols]: dgamma then dbeta, folded over the CTA's teams
@@ -357,24 +381,25 @@ __device__ __forceinline__ void team_sum4(float (&v)[4], float* red, int parity,
   }
 }
 
-// Row pass count is what bounds this kernel once the loads are asynchronous:
-// per element it issues ~14 instructions (two passes) instead of the ~24 of
-// the three-pass form.  Pass A forms sum x, sum x^2, sum dy*g and sum dy*g*x
-// together; c2 = mean(dy*g*xhat) then follows as rstd*(sum dy*g*x - mu*sum dy*g)/n.
-// Pass B writes dx = dy*g*rstd - rstd*c1 - xhat*rstd*c2 with two FMAs and
-// accumulates dgamma / dbeta.  When a lane's slice is small (KEEP) the
-// unpacked x and dy stay in registers between the passes.
+// Instruction issue is what bounds this kernel once the loads are asynchronous, so the row is visited twice, not
+// three times, and all row arithmetic is done on fp32 pairs (fma.rn.f32x2 and friends: two elements per issue
+// slot; a 32-bit word of two bf16 values unpacks straight into one pair).  Pass A forms sum x, sum x^2, sum dy*g
+// and sum dy*g*x together; c2 = mean(dy*g*xhat) then follows as rstd*(sum dy*g*x - mu*sum dy*g)/n.  Pass B writes
+// dx = dy*g*rstd - rstd*c1 - xhat*rstd*c2 with two FMAs and accumulates dgamma / dbeta.  When a lane's slice is
+// small (KEEP) the unpacked x and dy stay in registers between the passes.
 // RESID: a residual gradient is added to dx (compiled out otherwise: the wide-row instantiations have no
-// registers to spare).
+// registers to spare).  dy may alias dx (a row's dy is in shared memory before its dx is written).
 template <typename T, int WPR, int CHUNKS, bool RESID>
 __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
-    ln_bwd_pipe_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid,
-                       T* dx, float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
+    ln_bwd_pipe_kernel(const T* dy, const T* __restrict__ x, const T* __restrict__ gamma, const T* resid, T* dx,
+                       float* __restrict__ part, int64_t rows, int64_t cols, float eps) {
   constexpr int V = Vec<T>::N;
+  constexpr int P = V / 2;  // fp32 pairs per 16-byte chunk
   using S = Shape<WPR>;
   constexpr int SLOT = CHUNKS * 512;  // bytes of one array (x or dy) of one row slot of one warp
   constexpr int kLnStages = LnStages<CHUNKS>::N;
   constexpr bool KEEP = CHUNKS * V <= 16;
+  const T* const tag = nullptr;
   extern __shared__ __align__(16) unsigned char dsm[];
   unsigned char* ring_base = dsm;
   __shared__ float red[2 * S::WARPS * 4];
@@ -388,16 +413,16 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
   const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
 
   uint4 g_raw[CHUNKS];
-  float dg[CHUNKS][V], db[CHUNKS][V];
+  float2 dg[CHUNKS][P], db[CHUNKS][P];
   int64_t colj[CHUNKS];
 #pragma unroll
   for (int j = 0; j < CHUNKS; ++j) {
     colj[j] = (static_cast<int64_t>(j) * WPR * 32 + lt) * V;
     g_raw[j] = load_chunk<T, true>(gamma, colj[j], cols);
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      dg[j][e] = 0.f;
-      db[j][e] = 0.f;
+    for (int e = 0; e < P; ++e) {
+      dg[j][e] = make_float2(0.f, 0.f);
+      db[j][e] = make_float2(0.f, 0.f);
     }
   }
 
@@ -436,66 +461,68 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
       for (int j = 0; j < CHUNKS; ++j)
         if (colj[j] < cols) r_raw[j] = *reinterpret_cast<const uint4*>(resid + row * cols + colj[j]);
     }
-    float xk[KEEP ? CHUNKS : 1][V], dk[KEEP ? CHUNKS : 1][V];
-    float sums[4] = {0.f, 0.f, 0.f, 0.f};  // sum x, sum x^2, sum dy*g, sum dy*g*x
+    float2 xk[KEEP ? CHUNKS : 1][P], dk[KEEP ? CHUNKS : 1][P];
+    float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;  // sum x, sum x^2, sum dy*g, sum dy*g*x
 #pragma unroll
     for (int j = 0; j < CHUNKS; ++j) {
-      float v[V], d[V], g[V];
+      float2 v[P], d[P], g[P];
       const bool in = live && colj[j] < cols;
-      unpack<T>(in ? xs[j * 32 + lane] : make_uint4(0, 0, 0, 0), v);
-      unpack<T>(in ? ds[j * 32 + lane] : make_uint4(0, 0, 0, 0), d);
-      unpack<T>(g_raw[j], g);
+      unpack2(in ? xs[j * 32 + lane] : make_uint4(0, 0, 0, 0), v, tag);
+      unpack2(in ? ds[j * 32 + lane] : make_uint4(0, 0, 0, 0), d, tag);
+      unpack2(g_raw[j], g, tag);
 #pragma unroll
-      for (int e = 0; e < V; ++e) {
-        const float dyg = d[e] * g[e];
-        sums[0] += v[e];
-        sums[1] = fmaf(v[e], v[e], sums[1]);
-        sums[2] += dyg;
-        sums[3] = fmaf(dyg, v[e], sums[3]);
+      for (int e = 0; e < P; ++e) {
+        const float2 dyg = __fmul2_rn(d[e], g[e]);
+        s0 = __fadd2_rn(s0, v[e]);
+        s1 = __ffma2_rn(v[e], v[e], s1);
+        s2 = __fadd2_rn(s2, dyg);
+        s3 = __ffma2_rn(dyg, v[e], s3);
         if (KEEP) {
           xk[j][e] = v[e];
           dk[j][e] = d[e];
         }
       }
     }
+    float sums[4] = {s0.x + s0.y, s1.x + s1.y, s2.x + s2.y, s3.x + s3.y};
     team_sum4<WPR>(sums, red, parity, S::WARPS, warp, team, lane);
     parity ^= 1;
     const float mu = sums[0] * inv_n;
     const float rs = rsqrtf(fmaxf(sums[1] * inv_n - mu * mu, 0.f) + eps);
     const float c1 = sums[2] * inv_n;
     const float c2 = rs * (sums[3] - mu * sums[2]) * inv_n;
-    const float nmr = -mu * rs, k1 = -rs * c1, k2 = -rs * c2;
+    const float2 rs2 = make_float2(rs, rs), nmr2 = make_float2(-mu * rs, -mu * rs);
+    const float2 k12 = make_float2(-rs * c1, -rs * c1), k22 = make_float2(-rs * c2, -rs * c2);
     if (live) {
       T* dxr = dx + row * cols;
 #pragma unroll
       for (int j = 0; j < CHUNKS; ++j) {
         if (colj[j] < cols) {
-          float v[V], d[V], g[V], o[V];
+          float2 v[P], d[P], g[P], o[P];
           if (KEEP) {
 #pragma unroll
-            for (int e = 0; e < V; ++e) {
+            for (int e = 0; e < P; ++e) {
               v[e] = xk[j][e];
               d[e] = dk[j][e];
             }
           } else {
-            unpack<T>(xs[j * 32 + lane], v);
-            unpack<T>(ds[j * 32 + lane], d);
+            unpack2(xs[j * 32 + lane], v, tag);
+            unpack2(ds[j * 32 + lane], d, tag);
           }
-          unpack<T>(g_raw[j], g);
+          unpack2(g_raw[j], g, tag);
 #pragma unroll
-          for (int e = 0; e < V; ++e) {
-            const float xhat = fmaf(v[e], rs, nmr);
-            o[e] = fmaf(xhat, k2, fmaf(d[e] * g[e], rs, k1));
-            dg[j][e] = fmaf(d[e], xhat, dg[j][e]);
-            db[j][e] += d[e];
+          for (int e = 0; e < P; ++e) {
+            const float2 xhat = __ffma2_rn(v[e], rs2, nmr2);
+            o[e] = __ffma2_rn(xhat, k22, __ffma2_rn(__fmul2_rn(d[e], g[e]), rs2, k12));
+            dg[j][e] = __ffma2_rn(d[e], xhat, dg[j][e]);
+            db[j][e] = __fadd2_rn(db[j][e], d[e]);
           }
           if (RESID) {
-            float rv[V];
-            unpack<T>(EARLY ? r_raw[EARLY ? j : 0] : *reinterpret_cast<const uint4*>(resid + row * cols + colj[j]), rv);
+            float2 rv[P];
+            unpack2(EARLY ? r_raw[EARLY ? j : 0] : *reinterpret_cast<const uint4*>(resid + row * cols + colj[j]), rv, tag);
 #pragma unroll
-            for (int e = 0; e < V; ++e) o[e] += rv[e];
+            for (int e = 0; e < P; ++e) o[e] = __fadd2_rn(o[e], rv[e]);
           }
-          *reinterpret_cast<uint4*>(dxr + colj[j]) = pack<T>(o);
+          *reinterpret_cast<uint4*>(dxr + colj[j]) = pack2(o, tag);
         }
       }
     }
@@ -514,16 +541,20 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
   for (int j = 0; j < CHUNKS; ++j) {
     if (colj[j] + V <= cols) {
 #pragma unroll
-      for (int e = 0; e < V; e += 4) {
-        *reinterpret_cast<float4*>(mine + colj[j] + e) = make_float4(dg[j][e], dg[j][e + 1], dg[j][e + 2], dg[j][e + 3]);
-        *reinterpret_cast<float4*>(mine + cols + colj[j] + e) = make_float4(db[j][e], db[j][e + 1], db[j][e + 2], db[j][e + 3]);
+      for (int e = 0; e < P; e += 2) {
+        *reinterpret_cast<float4*>(mine + colj[j] + 2 * e) = make_float4(dg[j][e].x, dg[j][e].y, dg[j][e + 1].x, dg[j][e + 1].y);
+        *reinterpret_cast<float4*>(mine + cols + colj[j] + 2 * e) = make_float4(db[j][e].x, db[j][e].y, db[j][e + 1].x, db[j][e + 1].y);
       }
     } else {
 #pragma unroll
-      for (int e = 0; e < V; ++e) {
-        if (colj[j] + e < cols) {
-          mine[colj[j] + e] = dg[j][e];
-          mine[cols + colj[j] + e] = db[j][e];
+      for (int e = 0; e < P; ++e) {
+        if (colj[j] + 2 * e < cols) {
+          mine[colj[j] + 2 * e] = dg[j][e].x;
+          mine[cols + colj[j] + 2 * e] = db[j][e].x;
+        }
+        if (colj[j] + 2 * e + 1 < cols) {
+          mine[colj[j] + 2 * e + 1] = dg[j][e].y;
+          mine[cols + colj[j] + 2 * e + 1] = db[j][e].y;
         }
       }
     }
@@ -537,6 +568,7 @@ __global__ void __launch_bounds__(Shape<WPR>::THREADS, Shape<WPR>::MIN_CTAS)
     prow[c] = acc;
   }
 }
+
 // dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c], fixed order.
 template <typename T>
 __global__ void __launch_bounds__(kFinCols* kFinLanes)
@@ -605,18 +637,19 @@ int launch_bwd(const T* dy, const T* x, const T* g, const T* resid, T* dx, float
   if (vec && pipe_smem + 1024 <= static_cast<size_t>(max_smem_optin())) {
     const size_t smem = pipe_smem;
     auto k = resid ? ln_bwd_pipe_kernel<T, WPR, CHUNKS, true> : ln_bwd_pipe_kernel<T, WPR, CHUNKS, false>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    // static shared memory (reduction buffers) counts against the 48 KB default too: opt in well below it
+    if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     launch_pdl(k, dim3(grid), dim3(TH), smem, st, dy, x, g, resid, dx, part, rows, cols, eps);
     return check_launch("ln_bwd_pipe_kernel");
   }
   if (vec) {  // very wide rows: the ring does not fit next to the fold buffer, keep the row in registers instead
     auto k = ln_bwd_kernel<T, WPR, CHUNKS, true>;
-    if (fold_bytes > 48 * 1024)
+    if (fold_bytes > 40 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fold_bytes));
     k<<<grid, TH, fold_bytes, st>>>(dy, x, g, resid, dx, part, rows, cols, eps);
   } else {
     auto k = ln_bwd_kernel<T, WPR, CHUNKS, false>;
-    if (fold_bytes > 48 * 1024)
+    if (fold_bytes > 40 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fold_bytes));
     k<<<grid, TH, fold_bytes, st>>>(dy, x, g, resid, dx, part, rows, cols, eps);
   }
@@ -692,19 +725,25 @@ static __device__ __align__(256) float g_ln_bwd_static_scratch[kStaticScratchFlo
 // runtime and cached; the resolved pointer is what the kernels receive.
 int static_scratch_ptr(float** out) {
   constexpr int kDevs = 64;
-  static float* cache[kDevs] = {};
+  struct Slot {
+    std::once_flag once;
+    float* ptr = nullptr;
+    cudaError_t err = cudaSuccess;
+  };
+  static Slot slots[kDevs];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(MGB_ECUDA, "layer_norm_bwd_static: cudaGetDevice: %s", cudaGetErrorString(e));
   MGB_REQUIRE(dev >= 0 && dev < kDevs, MGB_EUNSUPPORTED, "layer_norm_bwd_static: device ordinal %d out of range", dev);
-  if (!cache[dev]) {
+  Slot& sl = slots[dev];
+  std::call_once(sl.once, [&] {  // once per device, with that device current; safe when two host threads call first
     float* p = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_bwd_static_scratch);
-    if (e != cudaSuccess || !p)
-      return fail(MGB_ECUDA, "layer_norm_bwd_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    cache[dev] = p;
-  }
-  *out = cache[dev];
+    sl.err = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_bwd_static_scratch);
+    sl.ptr = p;
+  });
+  if (sl.err != cudaSuccess || !sl.ptr)
+    return fail(MGB_ECUDA, "layer_norm_bwd_static: cudaGetSymbolAddress: %s", cudaGetErrorString(sl.err));
+  *out = sl.ptr;
   return MGB_OK;
 }
 

@@ -53,16 +53,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Waits for the phase with the given parity; false after kWaitLimitNs.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Waits for the phase with the given parity; false once limit_ns of wall-clock time have passed.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - t0 > kWaitLimitNs) return false;
+    if (global_ns() - t0 > limit_ns) return false;
   }
+}
+// The form every kernel uses: false after kWaitLimitNs.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, kWaitLimitNs);
 }
 
 // ----------------------------------------------------------------------- TMA

@@ -71,6 +71,22 @@ def _rows2d(t: torch.Tensor) -> tuple[int, int, int]:
     return rows, cols, ld
 
 
+def _packed_rows(t, rows, cols, who, name):
+    """A (rows, cols) operand the kernels index as packed rows: shape and contiguity are checked here because the
+    C ABI takes a bare pointer for it."""
+    if t is None:
+        return
+    if t.numel() != rows * cols or t.shape[-1] != cols or not t.is_contiguous():
+        raise KernelError(who, _lib.EINVAL, f"{name}: expected a contiguous ({rows}, {cols}) buffer, got shape "
+                                            f"{tuple(t.shape)} strides {tuple(t.stride())}")
+
+
+def _packed_vec(t, n, who, name):
+    if t is not None and (t.numel() != n or not t.is_contiguous()):
+        raise KernelError(who, _lib.EINVAL, f"{name}: expected a contiguous vector of {n} elements, got shape "
+                                            f"{tuple(t.shape)} strides {tuple(t.stride())}")
+
+
 # ----------------------------------------------------------------------------
 # matmul_bias_bt (dispatch.mojo:247-278)
 # ----------------------------------------------------------------------------
@@ -82,9 +98,14 @@ def matmul_bias_strided(a, w, bias=None, act: int = 0, out=None, residual=None, 
     N, K2, ldw = _rows2d(w)
     if K2 != K:
         raise KernelError("matmul_bias_bt", _lib.EINVAL, f"inner dims differ: {K} vs {K2}")
+    _packed_vec(bias, N, "matmul_bias_bt", "bias")
     if out is None:
         out = torch.empty(a.shape[:-1] + (N,), dtype=a.dtype, device=a.device)
-    _, _, ldy = _rows2d(out)
+    Mo, No, ldy = _rows2d(out)
+    if (Mo, No) != (M, N):
+        raise KernelError("matmul_bias_bt", _lib.EINVAL, f"out is {Mo}x{No}, expected {M}x{N}")
+    if residual is not None and _rows2d(residual)[:2] != (M, N):
+        raise KernelError("matmul_bias_bt", _lib.EINVAL, f"residual must be {M}x{N}")
     if relu_bits is not None:
         if act != 1 or residual is not None:
             raise KernelError("matmul_bias_bt", _lib.EINVAL, "relu_bits goes with act=1 and no residual")
@@ -137,6 +158,9 @@ def layer_norm_fwd_dispatch(x, gamma, beta, eps: float = 1e-5, save_stats: bool 
     cols = x.shape[-1]
     rows = x.numel() // cols
     out = torch.empty_like(x) if out is None else out
+    _packed_rows(out, rows, cols, "layer_norm_fwd", "out")
+    _packed_vec(gamma, cols, "layer_norm_fwd", "gamma")
+    _packed_vec(beta, cols, "layer_norm_fwd", "beta")
     mean = rstd = None
     if save_stats:
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
@@ -157,6 +181,12 @@ def layer_norm_bwd_dispatch(dy, x, gamma, eps: float = 1e-5, dx_out=None, dgamma
     dx = torch.empty_like(x) if dx_out is None else dx_out
     dgamma = torch.empty_like(gamma) if dgamma_out is None else dgamma_out
     dbeta = torch.empty_like(gamma) if dbeta_out is None else dbeta_out
+    who = "layer_norm_bwd"
+    _packed_rows(dy, rows, cols, who, "dy")
+    _packed_rows(dx, rows, cols, who, "dx")
+    _packed_rows(dx_residual, rows, cols, who, "dx_residual")
+    for name, t in (("gamma", gamma), ("dgamma", dgamma), ("dbeta", dbeta)):
+        _packed_vec(t, cols, who, name)
     code = dtype_code(x)
     nbytes = query("mograd_b200_layer_norm_bwd_workspace_bytes", rows, cols, code)
     ws = scratch_take(nbytes, x.device)
@@ -224,6 +254,18 @@ def _token_stride(t, name):
     return t.stride(1)
 
 
+def _attn_layout_checks(who, B, S, H, D, oshape, mask, has_bias, lse, **packed):
+    """O / dO are packed tensors of the agreed layout, LSE is packed (B, H, S) float32, the mask packed (B, H, S, S)."""
+    for name, t in packed.items():
+        if tuple(t.shape) != tuple(oshape) or not t.is_contiguous():
+            raise KernelError(who, _lib.EINVAL, f"{name}: expected a contiguous {tuple(oshape)} tensor, got shape "
+                                                f"{tuple(t.shape)} strides {tuple(t.stride())}")
+    if tuple(lse.shape) != (B, H, S) or lse.dtype != torch.float32 or not lse.is_contiguous():
+        raise KernelError(who, _lib.EINVAL, "lse must be a contiguous float32 (B, H, S) tensor")
+    if has_bias and (mask is None or tuple(mask.shape) != (B, H, S, S) or not mask.is_contiguous()):
+        raise KernelError(who, _lib.EINVAL, "has_bias needs a contiguous (B, H, S, S) mask")
+
+
 def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_bias=None, out=None, lse_out=None,
                             o_bshd=False):
     """srcs [Q, K, V, mask] all BSHD -> [O (BHSD, or BSHD when o_bshd), LSE (B,H,S) float32].
@@ -240,6 +282,7 @@ def flash_attn_fwd_dispatch(q, k, v, mask=None, scale=None, is_causal=True, has_
     oshape = (B, S, H, D) if o_bshd else (B, H, S, D)
     dst = torch.empty(oshape, dtype=q.dtype, device=q.device) if out is None else out
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if lse_out is None else lse_out
+    _attn_layout_checks("flash_attn_fwd", B, S, H, D, oshape, mask, has_bias, lse, out=dst)
     call("mograd_b200_flash_attn_fwd_ex", _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(dst), _ptr(lse), B, S, H, D,
          float(scale), int(bool(is_causal)), int(bool(has_bias)), ld, int(bool(o_bshd)), dtype_code(q), _stream())
     return [dst, lse]
@@ -255,6 +298,8 @@ def flash_attn_bwd_dispatch(dy, o, q, k, v, mask, lse, scale=None, is_causal=Tru
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     dy = dy if dy.is_contiguous() else dy.contiguous()  # the rule makes dO contiguous (grad.mojo:336-339)
+    oshape = (B, S, H, D) if o_bshd else (B, H, S, D)
+    _attn_layout_checks("flash_attn_bwd", B, S, H, D, oshape, mask, has_bias, lse, dy=dy, o=o)
     ld = _token_stride(q, "q")
     if _token_stride(k, "k") != ld or _token_stride(v, "v") != ld:
         raise KernelError("flash_attn_bwd", _lib.EINVAL, "q, k and v must share one token stride")

@@ -15,11 +15,13 @@ PyTorch supplies device memory, streams and the NCCL process group only.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from dataclasses import dataclass
 
 import torch
 
+from . import _lib
 from . import dispatch as K
 
 
@@ -110,6 +112,43 @@ class _Model:
         self.step_count = 0
         self.comm_stream = None
         self.exchanged = []  # (lo, hi) slices all-reduced so far, in issue order (cleared by the caller)
+        self.exchange_enabled = True
+        self.time_exposed = False   # record how long the main stream waits for each bucket's all-reduce
+        self.exposed_events = []    # per step: [(lo, hi, before, after)] CUDA events around each wait
+        self._staged = None         # input slot whose host->device copy has been issued ahead of its step
+        self._slot = 0
+
+    # ---- host-side input staging ---------------------------------------------------------
+    def _setup_io(self, in_shape, in_dtype, tgt_shape):
+        """Two device slots for the batch (the copy of step k+1 may run while step k computes), a pinned word for
+        the loss and pinned words for the device status."""
+        dev = self.device
+        self._in = [torch.empty(in_shape, dtype=in_dtype, device=dev) for _ in range(2)]
+        self._tgt = [torch.empty(tgt_shape, dtype=torch.int64, device=dev) for _ in range(2)]
+        self.d_inputs, self.d_targets = self._in[0], self._tgt[0]
+        on_gpu = dev.type == "cuda"
+        self.h_loss = torch.empty((), dtype=torch.float32).pin_memory() if on_gpu else torch.empty(())
+        self.h_status = torch.zeros(4, dtype=torch.int32).pin_memory() if on_gpu else torch.zeros(4, dtype=torch.int32)
+        self.copy_stream = torch.cuda.Stream(device=dev) if on_gpu else None
+        self._copied = [None, None]  # event per slot: its host->device copy has finished
+
+    def use_slot(self, k: int):
+        """Make input slot k (0 or 1) the batch the next step_device() reads."""
+        self._slot = k
+        self.d_inputs, self.d_targets = self._in[k], self._tgt[k]
+
+    def _prefetch(self, host_inputs, host_targets):
+        """Issue the host->device copy of the next step's batch on the copy stream, into the slot the current step
+        is not using (that slot was last read by the step before this one, which step() has synchronised with)."""
+        k = self._slot ^ 1
+        cs = self.copy_stream
+        with torch.cuda.stream(cs):
+            self._in[k].copy_(host_inputs, non_blocking=True)
+            self._tgt[k].copy_(host_targets, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(cs)
+        self._copied[k] = ev
+        self._staged = (k, host_inputs)
 
     # ---- data-parallel gradient exchange -------------------------------------------------
     def _setup_buckets(self):
@@ -129,7 +168,7 @@ class _Model:
 
     def _grads_ready_down_to(self, offset: int):
         """Everything in the flat gradient buffer at or above `offset` is final: exchange the buckets it covers."""
-        if self.world_size == 1:
+        if self.world_size == 1 or not self.exchange_enabled:
             return
         import torch.distributed as dist
 
@@ -166,13 +205,31 @@ class _Model:
                      o.weight_decay, self.step_count, grad_scale=1.0 / self.world_size)
 
     # ---- host-facing call: host buffers in, loss out -------------------------------------
-    def step(self, host_inputs, host_targets) -> float:
-        """One train step from pinned host tensors; returns the loss as a Python float (device->host read)."""
-        self.d_inputs.copy_(host_inputs, non_blocking=True)
-        self.d_targets.copy_(host_targets, non_blocking=True)
+    def step(self, host_inputs, host_targets, prefetch=None) -> float:
+        """One train step from pinned host tensors; returns the loss as a Python float (device->host read).
+
+        prefetch=(next_inputs, next_targets): the next step's batch; its host->device copy is issued on a second
+        stream right after this step's kernels are queued, so it runs under them, and the next step(next_inputs,
+        ...) finds its batch on the device.  Raises KernelError when a kernel's bounded wait gave up during the
+        step (the status word rides back with the loss)."""
+        main = torch.cuda.current_stream(self.device)
+        if self._staged is not None and self._staged[1] is host_inputs:
+            k, self._staged = self._staged[0], None
+            self.use_slot(k)
+            main.wait_event(self._copied[k])
+        else:
+            self._staged = None
+            self.d_inputs.copy_(host_inputs, non_blocking=True)
+            self.d_targets.copy_(host_targets, non_blocking=True)
         loss = self.step_device()
+        if prefetch is not None:
+            self._prefetch(*prefetch)
         self.h_loss.copy_(loss, non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
+        _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self.h_status.data_ptr()),
+                  ctypes.c_void_p(main.cuda_stream))
+        main.synchronize()
+        if int(self.h_status[0]) != 0:
+            _lib.check_device_status("Model.step")
         return float(self.h_loss.item())
 
     def step_device(self):
@@ -184,15 +241,64 @@ class _Model:
             # still on the wire.
             self._grads_ready_down_to(0)
             main = torch.cuda.current_stream(self.device)
+            marks = []
             for lo, hi, done in self._bucket_done:
+                if self.time_exposed:
+                    before = torch.cuda.Event(enable_timing=True)
+                    before.record(main)
                 main.wait_event(done)
+                if self.time_exposed:
+                    after = torch.cuda.Event(enable_timing=True)
+                    after.record(main)
+                    marks.append((lo, hi, before, after))
                 self.optimizer_step(lo, hi)
+            if self.time_exposed:
+                self.exposed_events.append(marks)
             self._bucket_done.clear()
             self._next_bucket = 0
         else:
             self._finish_exchange()
             self.optimizer_step()
         return loss
+
+
+    # ---- data-parallel self-check ---------------------------------------------------------
+    def check_data_parallel(self):
+        """Compares the bucketed, overlapped gradient exchange with a plain one on the current batch.
+
+        Runs forward+backward twice without touching the parameters: once with the exchange switched off (the
+        local gradients, summed over ranks in fp32 by a single all-reduce on the main stream) and once through
+        the product path (bf16 buckets on the communication stream behind events).  Returns
+        max |product - plain| / max |plain| over the whole flat gradient buffer, the same on every rank."""
+        import torch.distributed as dist
+
+        if self.world_size == 1:
+            return 0.0
+        self.exchange_enabled = False
+        self.forward_backward()
+        self.exchange_enabled = True
+        plain = self.store.g.float()
+        dist.all_reduce(plain, op=dist.ReduceOp.SUM, group=self.pg)
+        self.forward_backward()
+        self._finish_exchange()
+        self._bucket_done.clear()
+        got = self.store.g.float()
+        err = (got - plain).abs().max() / plain.abs().max().clamp_min(1e-30)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX, group=self.pg)
+        return float(err.item())
+
+    def replicas_in_sync(self):
+        """True when every rank holds bit-identical parameters and optimiser master copies."""
+        import torch.distributed as dist
+
+        if self.world_size == 1:
+            return True
+        w = self.store.w.view(torch.int16).to(torch.int64)
+        sums = torch.stack([w.sum(), (w * w).sum(), self.store.master.view(torch.int32).to(torch.int64).sum()])
+        lo, hi = sums.clone(), sums.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.pg)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.pg)
+        return bool(torch.equal(lo, hi))
 
 
 class MLP(_Model):
@@ -222,9 +328,7 @@ class MLP(_Model):
         st.load(vals)
         self._setup_buckets()
         dev, B = self.device, batch
-        self.d_inputs = torch.empty((B, dims[0]), dtype=dtype, device=dev)
-        self.d_targets = torch.empty((B,), dtype=torch.int64, device=dev)
-        self.h_loss = torch.empty((), dtype=torch.float32).pin_memory() if dev.type == "cuda" else torch.empty(())
+        self._setup_io((B, dims[0]), dtype, (B,))
         self.act = [torch.empty((B, dims[i + 1]), dtype=dtype, device=dev) for i in range(self.nl - 1)]
         self.ln_out = torch.empty((B, dims[1]), dtype=dtype, device=dev)
         self.C = dims[-1]
@@ -305,9 +409,7 @@ class TinyTransformer(_Model):
         self._setup_buckets()
         dev, T, d = self.device, self.T, d_model
         new = lambda *shape: torch.empty(shape, dtype=dtype, device=dev)
-        self.d_inputs = torch.empty((batch, seq), dtype=torch.int64, device=dev)
-        self.d_targets = torch.empty((batch, seq), dtype=torch.int64, device=dev)
-        self.h_loss = torch.empty((), dtype=torch.float32).pin_memory() if dev.type == "cuda" else torch.empty(())
+        self._setup_io((batch, seq), torch.int64, (batch, seq))
         self.x = [new(T, d) for _ in range(n_layers + 1)]  # block inputs, x[L] = final hidden state
         self.saved = []
         for _ in range(n_layers):

@@ -128,3 +128,53 @@ def test_bwd_with_residual_gradient(cuda, oracle, rows, cols, dt):
     assert dx.data_ptr() == rbuf.data_ptr()
     assert rel_err(dx.float().cpu().numpy(), wdx + res) <= tol
     assert rel_err(dg.float().cpu().numpy(), wdg) <= tol and rel_err(db.float().cpu().numpy(), wdb) <= tol
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 768), (65, 4096), (9, 37), (40, 16384)])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_bwd_in_place_on_dy(cuda, oracle, rows, cols, dt):
+    """dx may be written over dy (the train-step runner does so): a row's dy is read before its dx is stored."""
+    import torch
+    from mograd_b200 import dispatch as K
+
+    rng = np.random.default_rng(rows * 7 + cols)
+    x, dy = (rng.standard_normal((rows, cols)).astype(np.float32) for _ in range(2))
+    g = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    tdt = torch.float32 if dt == "f32" else torch.bfloat16
+    if dt == "bf16":
+        x, dy, g = (bf16_round(t) for t in (x, dy, g))
+    wdx, wdg, wdb = oracle.layer_norm_bwd(dy, x, g)
+    dev = lambda t: torch.from_numpy(t).to(cuda).to(tdt)
+    buf = dev(dy)
+    dx, dg, db = K.layer_norm_bwd_dispatch(buf, dev(x), dev(g), dx_out=buf)
+    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    assert dx.data_ptr() == buf.data_ptr()
+    assert rel_err(dx.float().cpu().numpy(), wdx) <= tol
+    assert rel_err(dg.float().cpu().numpy(), wdg) <= tol and rel_err(db.float().cpu().numpy(), wdb) <= tol
+
+
+def test_bwd_many_launches_alternating_shapes(cuda, oracle):
+    """Eighty back-to-back launches of alternating shapes share one workspace in stream order: the first of each
+    shape matches the oracle and every repeat is bit-identical to it."""
+    import torch
+    from mograd_b200 import dispatch as K
+
+    cases = []
+    for i, (rows, cols) in enumerate([(5000, 768), (777, 1024), (64, 8192), (3000, 384)]):
+        rng = np.random.default_rng(100 + i)
+        x, dy = (bf16_round(rng.standard_normal((rows, cols)).astype(np.float32)) for _ in range(2))
+        g = bf16_round((1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32))
+        dev = lambda t: torch.from_numpy(t).to(cuda).bfloat16()
+        cases.append((dev(dy), dev(x), dev(g), oracle.layer_norm_bwd(dy, x, g)))
+    first = {}
+    for it in range(80):
+        dyd, xd, gd, want = cases[it % len(cases)]
+        dx, dg, db = K.layer_norm_bwd_dispatch(dyd, xd, gd)
+        if it % len(cases) not in first:
+            first[it % len(cases)] = (dx.clone(), dg.clone(), db.clone())
+            assert rel_err(dx.float().cpu().numpy(), want[0]) <= TOL_BF16
+            assert rel_err(dg.float().cpu().numpy(), want[1]) <= TOL_BF16
+            assert rel_err(db.float().cpu().numpy(), want[2]) <= TOL_BF16
+        else:
+            f = first[it % len(cases)]
+            assert torch.equal(dx, f[0]) and torch.equal(dg, f[1]) and torch.equal(db, f[2])
