@@ -45,9 +45,13 @@ enum mgb_status {
   MGB_EUNSUPPORTED = -6  /* valid request outside what the kernels implement  */
 };
 
+/* Storage types.  bfloat16 and float16 run on the tensor cores (fp32
+ * accumulation); float32 runs on the CUDA cores.  float16 is the half type
+ * mograd's buffers can carry today (mograd/buffer.mojo:136). */
 enum mgb_dtype {
   MGB_BF16 = 0,
-  MGB_F32 = 1
+  MGB_F32 = 1,
+  MGB_F16 = 2
 };
 
 /* Library identity.  No counterpart in the reference, whose Mojo ABI is

@@ -20,6 +20,7 @@ _sz = ctypes.c_size_t
 
 BF16 = 0
 F32 = 1
+F16 = 2
 
 OK = 0
 EINVAL = -1

@@ -1,5 +1,5 @@
 // Attention entry points: argument checks and routing between the tcgen05
-// kernels (bf16, D = 64 / 128, no bias) and the CUDA-core kernels (the rest).
+// kernels (bf16 / fp16, D = 64 / 128, no bias) and the CUDA-core kernels (the rest).
 #include "attn.cuh"
 #include "common.cuh"
 
@@ -12,7 +12,8 @@ int check_attn(const char* who, int64_t B, int64_t S, int64_t H, int64_t D, int 
               (long long)S, (long long)H);
   MGB_REQUIRE(D >= 1 && D <= 512, MGB_EUNSUPPORTED, "%s: head dim %lld outside [1, 512]", who, (long long)D);
   MGB_REQUIRE(!(causal && has_bias), MGB_EINVAL, "%s: causal and has_bias cannot both be set", who);
-  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32, MGB_EDTYPE, "%s: unsupported dtype code %d", who, dtype);
+  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32 || dtype == MGB_F16, MGB_EDTYPE, "%s: unsupported dtype code %d",
+              who, dtype);
   MGB_REQUIRE(B * H * S < (1LL << 31) && S < (1 << 30), MGB_EUNSUPPORTED, "%s: B*H*S exceeds 2^31", who);
   return MGB_OK;
 }
@@ -47,7 +48,9 @@ MGB_EXPORT int mograd_b200_flash_attn_fwd_ex(const void* q, const void* k, const
     return attn::generic_fwd<float>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, lay, st);
   const void* ptrs[] = {q, k, v, dst};
   if (attn::tc_supported(d, has_bias, lay, ptrs, 4))
-    return attn::tc_fwd(q, k, v, dst, lse, b, s, h, d, scale, causal, lay, st);
+    return attn::tc_fwd(q, k, v, dst, lse, b, s, h, d, scale, causal, dtype == MGB_F16, lay, st);
+  if (dtype == MGB_F16)
+    return attn::generic_fwd<__half>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, lay, st);
   return attn::generic_fwd<__nv_bfloat16>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, lay, st);
 }
 
@@ -61,7 +64,7 @@ MGB_EXPORT int mograd_b200_flash_attn_fwd(const void* q, const void* k, const vo
 MGB_EXPORT size_t mograd_b200_flash_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype) {
   if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return 0;
   size_t n = delta_bytes(B, S, H);
-  if (dtype == MGB_BF16 && (D == 64 || D == 128)) n += dq_acc_bytes(B, S, H, D);
+  if (dtype != MGB_F32 && (D == 64 || D == 128)) n += dq_acc_bytes(B, S, H, D);
   return n;
 }
 
@@ -93,9 +96,15 @@ MGB_EXPORT int mograd_b200_flash_attn_bwd_ex(const void* dy, const void* o, cons
   const bool tc = attn::tc_supported(d, has_bias, lay, ptrs, 7);
   float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes(B, S, H));
   bool acc_zeroed = false;
-  rc = attn::launch_delta<__nv_bfloat16>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st);
+  const bool f16 = dtype == MGB_F16;
+  rc = f16 ? attn::launch_delta<__half>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st)
+           : attn::launch_delta<__nv_bfloat16>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st);
   if (rc != MGB_OK) return rc;
-  if (tc) return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, acc_zeroed, dq, dk, dv, b, s, h, d, scale, causal, lay, st);
+  if (tc)
+    return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, acc_zeroed, dq, dk, dv, b, s, h, d, scale, causal, f16, lay, st);
+  if (f16)
+    return attn::generic_bwd<__half>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal, has_bias, lay,
+                                     st);
   return attn::generic_bwd<__nv_bfloat16>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal,
                                           has_bias, lay, st);
 }

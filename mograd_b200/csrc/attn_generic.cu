@@ -301,6 +301,7 @@ int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int 
 }
 template int launch_delta<float>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
 template int launch_delta<__nv_bfloat16>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
+template int launch_delta<__half>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
 
 template <typename T>
 int generic_fwd(const void* q, const void* k, const void* v, const void* mask, void* dst, float* lse, int B, int S,
@@ -323,6 +324,8 @@ template int generic_fwd<float>(const void*, const void*, const void*, const voi
                                 float, int, int, const Layouts&, cudaStream_t);
 template int generic_fwd<__nv_bfloat16>(const void*, const void*, const void*, const void*, void*, float*, int, int,
                                         int, int, float, int, int, const Layouts&, cudaStream_t);
+template int generic_fwd<__half>(const void*, const void*, const void*, const void*, void*, float*, int, int, int, int,
+                                 float, int, int, const Layouts&, cudaStream_t);
 
 template <typename T>
 int generic_bwd(const void* dy, const void* q, const void* k, const void* v, const void* mask, const float* lse,
@@ -356,6 +359,9 @@ template int generic_bwd<float>(const void*, const void*, const void*, const voi
 template int generic_bwd<__nv_bfloat16>(const void*, const void*, const void*, const void*, const void*, const float*,
                                         const float*, void*, void*, void*, int, int, int, int, float, int, int,
                                         const Layouts&, cudaStream_t);
+template int generic_bwd<__half>(const void*, const void*, const void*, const void*, const void*, const float*,
+                                 const float*, void*, void*, void*, int, int, int, int, float, int, int, const Layouts&,
+                                 cudaStream_t);
 
 }  // namespace attn
 }  // namespace mgb

@@ -1,5 +1,8 @@
 // Flash-attention forward and backward on the tcgen05 tensor cores
-// (bf16 storage, fp32 accumulation in TMEM, D = 64 or 128, causal or full).
+// (bf16 or fp16 storage, a template parameter that only selects the operand
+// format of the MMAs and the packing of P, dS and the outputs; fp32
+// accumulation in TMEM, D = 64 or 128, causal or full).  Pointers to 16-bit
+// tensors are typed bf16* throughout: they are only used for addressing.
 //
 // Tiles are 128 query rows x 128 key rows.  Q / K / V / dO tiles are brought
 // in by TMA as [128 rows][D] bf16 with the 128-byte swizzle (one 16 KB box per
@@ -123,7 +126,7 @@ struct BwdCfg {
   static constexpr int THREADS = 608;  // TMA warp, MMA warp, 16 compute warps, dQ reduction warp
 };
 
-template <int D>
+template <int D, typename T>
 __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -230,9 +233,9 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA
     if (lane == 0) {
-      constexpr uint32_t id_ss = umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t id_mm = umma_idesc_bf16(128, D, 1, 1);
-      constexpr uint32_t id_km = umma_idesc_bf16(128, D, 0, 1);
+      constexpr uint32_t id_ss = umma_idesc_16<T>(128, 128, 0, 0);
+      constexpr uint32_t id_mm = umma_idesc_16<T>(128, D, 1, 1);
+      constexpr uint32_t id_km = umma_idesc_16<T>(128, D, 0, 1);
       const uint32_t sK = base + C::OFF_K, sV = base + C::OFF_V, sP = base + C::OFF_P, sDS = base + C::OFF_DS;
       auto q_tile = [&](int it) { return base + C::OFF_Q + (it % C::QST) * C::TILE_BYTES; };
       auto do_tile = [&](int it) { return base + C::OFF_DO + (it % C::DOST) * C::TILE_BYTES; };
@@ -416,8 +419,8 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         for (int e = 0; e < 32; e += 2) {
           const float p0 = ex2(fmaf(__uint_as_float(sv[e]), scale_log2, -lse2));
           const float p1 = ex2(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -lse2));
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-          dk[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dpv[e]) - dlt), p1 * (__uint_as_float(dpv[e + 1]) - dlt));
+          pk[e >> 1] = pack_pair<T>(p0, p1);
+          dk[e >> 1] = pack_pair<T>(p0 * (__uint_as_float(dpv[e]) - dlt), p1 * (__uint_as_float(dpv[e + 1]) - dlt));
         }
       } else {
 #pragma unroll
@@ -431,8 +434,8 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
             pv[u] = pe;
             dv[u] = pe * (__uint_as_float(dpv[e + u]) - dlt);
           }
-          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
+          pk[e >> 1] = pack_pair<T>(pv[0], pv[1]);
+          dk[e >> 1] = pack_pair<T>(dv[0], dv[1]);
         }
       }
       // P | dS may be rewritten once the previous tile's MMAs have read them (LATE: bar_dqf of that tile;
@@ -480,14 +483,14 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
 #pragma unroll
           for (int e = 0; e < 16; e += 8) {
             uint4 o1, o2;
-            o1.x = pack_bf16x2(__uint_as_float(a[e]) * sc, __uint_as_float(a[e + 1]) * sc);
-            o1.y = pack_bf16x2(__uint_as_float(a[e + 2]) * sc, __uint_as_float(a[e + 3]) * sc);
-            o1.z = pack_bf16x2(__uint_as_float(a[e + 4]) * sc, __uint_as_float(a[e + 5]) * sc);
-            o1.w = pack_bf16x2(__uint_as_float(a[e + 6]) * sc, __uint_as_float(a[e + 7]) * sc);
-            o2.x = pack_bf16x2(__uint_as_float(c[e]), __uint_as_float(c[e + 1]));
-            o2.y = pack_bf16x2(__uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
-            o2.z = pack_bf16x2(__uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
-            o2.w = pack_bf16x2(__uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
+            o1.x = pack_pair<T>(__uint_as_float(a[e]) * sc, __uint_as_float(a[e + 1]) * sc);
+            o1.y = pack_pair<T>(__uint_as_float(a[e + 2]) * sc, __uint_as_float(a[e + 3]) * sc);
+            o1.z = pack_pair<T>(__uint_as_float(a[e + 4]) * sc, __uint_as_float(a[e + 5]) * sc);
+            o1.w = pack_pair<T>(__uint_as_float(a[e + 6]) * sc, __uint_as_float(a[e + 7]) * sc);
+            o2.x = pack_pair<T>(__uint_as_float(c[e]), __uint_as_float(c[e + 1]));
+            o2.y = pack_pair<T>(__uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
+            o2.z = pack_pair<T>(__uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
+            o2.w = pack_pair<T>(__uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
             *reinterpret_cast<uint4*>(dk_row + c0 + e) = o1;
             *reinterpret_cast<uint4*>(dv_row + c0 + e) = o2;
           }
@@ -504,6 +507,7 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
 }
 
 // acc is packed (tokens x HD) fp32; dq rows are ld elements apart.
+template <typename T>
 __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8,
                                                       int hd8, int64_t ld, float scale) {
   pdl_launch_dependents();
@@ -515,10 +519,10 @@ __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ 
     const float4 a = reinterpret_cast<const float4*>(acc)[2 * i];
     const float4 c = reinterpret_cast<const float4*>(acc)[2 * i + 1];
     uint4 o;
-    o.x = pack_bf16x2(a.x * scale, a.y * scale);
-    o.y = pack_bf16x2(a.z * scale, a.w * scale);
-    o.z = pack_bf16x2(c.x * scale, c.y * scale);
-    o.w = pack_bf16x2(c.z * scale, c.w * scale);
+    o.x = pack_pair<T>(a.x * scale, a.y * scale);
+    o.y = pack_pair<T>(a.z * scale, a.w * scale);
+    o.z = pack_pair<T>(c.x * scale, c.y * scale);
+    o.w = pack_pair<T>(c.z * scale, c.w * scale);
     *reinterpret_cast<uint4*>(dq + tok * ld + c8 * 8) = o;
   }
 }
@@ -545,6 +549,7 @@ struct Fwd64Cfg {
   static constexpr int THREADS = 192;
 };
 
+template <typename T>
 __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
     attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -627,8 +632,8 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
+      constexpr uint32_t id_s = umma_idesc_16<T>(128, 128, 0, 0);
+      constexpr uint32_t id_o = umma_idesc_16<T>(128, D, 0, 1);
       const uint64_t dQ = base_k(base + C::OFF_Q);
       const uint64_t dV = base_mn(base + C::OFF_V);
       auto issue_s = [&](int jt) -> bool {
@@ -730,7 +735,7 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
           const float p1 = ex2(fmaf(__uint_as_float(v[c32 * 32 + 2 * e + 1]), scale_log2, neg_m));
           rs0 += p0;
           rs1 += p1;
-          pk[e] = pack_bf16x2(p0, p1);
+          pk[e] = pack_pair<T>(p0, p1);
         }
         tmem_st16(tmem + lane_base + C::COL_P + c32 * 16, pk);
       }
@@ -759,10 +764,10 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
 #pragma unroll
           for (int e = 0; e < 16; e += 8) {
             uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+            w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+            w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+            w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+            w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
             *reinterpret_cast<uint4*>(orow + c0 + e) = w;
           }
         }
@@ -797,6 +802,7 @@ struct Fwd128Cfg {
   static constexpr int THREADS = 320;  // TMA, MMA, 4 softmax warps per query tile
 };
 
+template <typename T>
 __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
     attn_fwd_tc128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                             const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -892,8 +898,8 @@ __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t id_s = umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t id_o = umma_idesc_bf16(128, D, 0, 1);
+      constexpr uint32_t id_s = umma_idesc_16<T>(128, 128, 0, 0);
+      constexpr uint32_t id_o = umma_idesc_16<T>(128, D, 0, 1);
       const uint64_t dV = base_mn(base + C::OFF_V);
       // scores of key tile jt for every query tile that still has work there
       auto issue_s = [&](int jt) -> bool {
@@ -1010,7 +1016,7 @@ __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
           const float p1 = ex2(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2, neg_m));
           rs0 += p0;
           rs1 += p1;
-          pk[e] = pack_bf16x2(p0, p1);
+          pk[e] = pack_pair<T>(p0, p1);
         }
         *reinterpret_cast<uint4*>(ps + ps_chunk_off(r, c8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
@@ -1039,10 +1045,10 @@ __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
 #pragma unroll
           for (int e = 0; e < 16; e += 8) {
             uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+            w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+            w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+            w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+            w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
             *reinterpret_cast<uint4*>(orow + c0 + e) = w;
           }
         }
@@ -1081,7 +1087,7 @@ int set_smem(K kern, int bytes) {
   return MGB_OK;
 }
 
-template <int D>
+template <int D, typename T>
 int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv,
             cudaStream_t st) {
   using C = BwdCfg<D>;
@@ -1101,7 +1107,7 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
     const uint32_t box[4] = {32, 1, 128, 1};
     if (!encode_tmap_f32(&mdq, p.dq_acc, 4, dims, strides, box)) return MGB_ECUDA;
   }
-  auto kern = attn_bwd_tc_kernel<D>;
+  auto kern = attn_bwd_tc_kernel<D, T>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
@@ -1109,13 +1115,14 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
   return check_launch("attn_bwd_tc_kernel");
 }
 
+template <typename T>
 int run_fwd128x2(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
   using C = Fwd128Cfg;
   CUtensorMap mq, mk, mv;
   if (!map_bshd(&mq, q, p.B, p.S, p.H, 128, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 128, ld_qkv) ||
       !map_bshd(&mv, v, p.B, p.S, p.H, 128, ld_qkv))
     return MGB_ECUDA;
-  auto kern = attn_fwd_tc128x2_kernel;
+  auto kern = attn_fwd_tc128x2_kernel<T>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   const int nq = (p.S + 127) / 128;
@@ -1124,13 +1131,14 @@ int run_fwd128x2(const void* q, const void* k, const void* v, AttnParams p, int6
   return check_launch("attn_fwd_tc128x2_kernel");
 }
 
+template <typename T>
 int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t ld_qkv, cudaStream_t st) {
   using C = Fwd64Cfg;
   CUtensorMap mq, mk, mv;
   if (!map_bshd(&mq, q, p.B, p.S, p.H, 64, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 64, ld_qkv) ||
       !map_bshd(&mv, v, p.B, p.S, p.H, 64, ld_qkv))
     return MGB_ECUDA;
-  auto kern = attn_fwd_tc64_kernel;
+  auto kern = attn_fwd_tc64_kernel<T>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
@@ -1149,7 +1157,7 @@ bool tc_supported(int D, int has_bias, const Layouts& lay, const void* const* pt
 }
 
 int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, int B, int S, int H, int D, float scale,
-           int causal, const Layouts& lay, cudaStream_t st) {
+           int causal, int f16, const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
   p.out = static_cast<bf16*>(dst);
   p.lse_out = lse;
@@ -1158,12 +1166,13 @@ int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, i
   p.status = device_status_ptr();
   if (!p.status) return fail(MGB_ECUDA, "flash_attn_fwd: device status word unavailable");
   MGB_REQUIRE(static_cast<int64_t>(B) * H <= 65535, MGB_EUNSUPPORTED, "flash_attn_fwd: B*H=%d exceeds 65535", B * H);
-  return D == 64 ? run_fwd64(q, k, v, p, lay.ld_qkv, st) : run_fwd128x2(q, k, v, p, lay.ld_qkv, st);
+  if (f16) return D == 64 ? run_fwd64<__half>(q, k, v, p, lay.ld_qkv, st) : run_fwd128x2<__half>(q, k, v, p, lay.ld_qkv, st);
+  return D == 64 ? run_fwd64<bf16>(q, k, v, p, lay.ld_qkv, st) : run_fwd128x2<bf16>(q, k, v, p, lay.ld_qkv, st);
 }
 
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
            float* dq_acc, bool acc_zeroed, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale,
-           int causal, const Layouts& lay, cudaStream_t st) {
+           int causal, int f16, const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
   p.lse = lse;
   p.delta = delta;
@@ -1181,12 +1190,21 @@ int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const fl
     const cudaError_t e = cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(n) * sizeof(float), st);
     if (e != cudaSuccess) return fail(MGB_ECUDA, "flash_attn_bwd: memset of the dQ accumulator: %s", cudaGetErrorString(e));
   }
-  int rc = D == 64 ? run_bwd<64>(dy, q, k, v, p, lay.ld_qkv, st) : run_bwd<128>(dy, q, k, v, p, lay.ld_qkv, st);
+  int rc;
+  if (f16)
+    rc = D == 64 ? run_bwd<64, __half>(dy, q, k, v, p, lay.ld_qkv, st) : run_bwd<128, __half>(dy, q, k, v, p, lay.ld_qkv, st);
+  else
+    rc = D == 64 ? run_bwd<64, bf16>(dy, q, k, v, p, lay.ld_qkv, st) : run_bwd<128, bf16>(dy, q, k, v, p, lay.ld_qkv, st);
   if (rc != MGB_OK) return rc;
   const int64_t n8 = n / 8;
   int grid = static_cast<int>((n8 + 255) / 256);
   if (grid > sm_count() * 8) grid = sm_count() * 8;
-  launch_pdl(cast_dq_kernel, dim3(grid), dim3(256), 0, st, dq_acc, static_cast<bf16*>(dq), n8, H * D / 8, lay.ld_dqkv, scale);
+  if (f16)
+    launch_pdl(cast_dq_kernel<__half>, dim3(grid), dim3(256), 0, st, dq_acc, static_cast<bf16*>(dq), n8, H * D / 8,
+               lay.ld_dqkv, scale);
+  else
+    launch_pdl(cast_dq_kernel<bf16>, dim3(grid), dim3(256), 0, st, dq_acc, static_cast<bf16*>(dq), n8, H * D / 8,
+               lay.ld_dqkv, scale);
   return check_launch("cast_dq_kernel");
 }
 

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -68,9 +69,14 @@ template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
 };
+template <>
+struct Vec<__half> {
+  static constexpr int N = 8;
+};
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
 template <typename T>
 __device__ __forceinline__ T from_f32(float v);
 template <>
@@ -80,6 +86,10 @@ __device__ __forceinline__ float from_f32<float>(float v) {
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) {
+  return __float2half_rn(v);
 }
 
 // 16-byte global load / store of Vec<T>::N elements, widened to float.
@@ -99,12 +109,45 @@ __device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&out)[8]
     out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
+__device__ __forceinline__ void load_vec(const __half* p, float (&out)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
 __device__ __forceinline__ void store_vec(float* p, const float (&in)[4]) {
   *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// Two floats -> one 32-bit word of two 16-bit elements of type T (element 0 in the low half).
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  return pack_bf16x2(lo, hi);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  return pack_f16x2(lo, hi);
+}
+__device__ __forceinline__ void store_vec(__half* p, const float (&in)[8]) {
+  uint4 v;
+  v.x = pack_f16x2(in[0], in[1]);
+  v.y = pack_f16x2(in[2], in[3]);
+  v.z = pack_f16x2(in[4], in[5]);
+  v.w = pack_f16x2(in[6], in[7]);
+  *reinterpret_cast<uint4*>(p) = v;
 }
 __device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&in)[8]) {
   uint4 v;

@@ -181,6 +181,10 @@ using namespace mgb;
       using T = float;                                                      \
       __VA_ARGS__;                                                          \
     } break;                                                                \
+    case MGB_F16: {                                                         \
+      using T = __half;                                                     \
+      __VA_ARGS__;                                                          \
+    } break;                                                                \
     default:                                                                \
       return fail(MGB_EDTYPE, who ": unsupported dtype code %d", dtype);    \
   }
@@ -244,14 +248,21 @@ MGB_EXPORT int mograd_b200_scatter_add_rows(const void* dout, const int64_t* idx
                                                                            rows, vocab, d);
     return check_launch("scatter_add_rows_kernel");
   }
-  MGB_REQUIRE(dtype == MGB_BF16, MGB_EDTYPE, "scatter_add_rows: unsupported dtype code %d", dtype);
+  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F16, MGB_EDTYPE, "scatter_add_rows: unsupported dtype code %d", dtype);
   float* acc = static_cast<float*>(workspace);
   if (cudaMemsetAsync(acc, 0, n * sizeof(float), st) != cudaSuccess) return fail(MGB_ECUDA, "scatter_add_rows: memset failed");
-  scatter_add_rows_kernel<__nv_bfloat16><<<ew_grid(rows * d), kEwThreads, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(dout), idx, acc, rows, vocab, d);
+  if (dtype == MGB_BF16)
+    scatter_add_rows_kernel<__nv_bfloat16><<<ew_grid(rows * d), kEwThreads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dout), idx, acc, rows, vocab, d);
+  else
+    scatter_add_rows_kernel<__half><<<ew_grid(rows * d), kEwThreads, 0, st>>>(static_cast<const __half*>(dout), idx, acc,
+                                                                            rows, vocab, d);
   int rc = check_launch("scatter_add_rows_kernel");
   if (rc != MGB_OK) return rc;
-  cast_from_f32_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>(acc, static_cast<__nv_bfloat16*>(dtable), n);
+  if (dtype == MGB_BF16)
+    cast_from_f32_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>(acc, static_cast<__nv_bfloat16*>(dtable), n);
+  else
+    cast_from_f32_kernel<__half><<<ew_grid(n), kEwThreads, 0, st>>>(acc, static_cast<__half*>(dtable), n);
   return check_launch("cast_from_f32_kernel");
 }
 

@@ -1,6 +1,9 @@
 // matmul_bias_bt forward and its backward (dX, dW, db).
 //
-// bf16 path: one persistent, warp-specialised tcgen05 kernel computes
+// 16-bit path (bf16 or fp16 storage: a template parameter T that selects the
+// operand format of the MMAs and the conversions in the epilogue; pointers to
+// 16-bit tensors are typed bf16* throughout, they are only used for
+// addressing): one persistent, warp-specialised tcgen05 kernel computes
 //     D[i,j] = sum_l A(i,l) * B(j,l)      (fp32 accumulation in TMEM)
 // for the three products of a Linear layer, which differ only in which
 // operand is K-major (contraction index contiguous in memory) or MN-major:
@@ -35,6 +38,16 @@ constexpr int kGemmThreads = 448;  // warp 0 TMA, 1 MMA, 2-9 epilogue, 10-13 col
 constexpr int kMaxSplits = 16;
 
 enum : int { kErrTmaWait = 101, kErrMmaWait = 102, kErrEpiWait = 103 };
+
+// One element of a 16-bit tensor of storage type T, addressed through the untyped bf16* the parameters carry.
+template <typename T>
+__device__ __forceinline__ float ld16(const bf16* p) {
+  return to_f32(*reinterpret_cast<const T*>(p));
+}
+template <typename T>
+__device__ __forceinline__ void st16(bf16* p, float v) {
+  *reinterpret_cast<T*>(p) = from_f32<T>(v);
+}
 
 template <int BN>
 struct Tile {
@@ -103,7 +116,7 @@ struct EpilogueOut {
 // thread, t_row the TMEM address of its lane at the accumulator's first column.
 // FUSED = false compiles the elementwise epilogue (bias, ReLU, mask, residual) out: plain products keep the
 // shortest possible drain loop.
-template <int BN, bool FUSED>
+template <int BN, bool FUSED, typename T>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_row, int row, int n_blk, int split,
                                                   int chalf, const EpilogueOut& eo, int lane_row) {
   const bf16* const e_bias = FUSED ? p.bias : nullptr;
@@ -191,14 +204,14 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             float bv[8];
-            load_vec(reinterpret_cast<const bf16*>(&ep_bias[j >> 3]), bv);
+            load_vec(reinterpret_cast<const T*>(&ep_bias[j >> 3]), bv);
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[j + e] += bv[e];
           }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __bfloat162float(e_bias[col0 + j]);
+            if (col0 + j < p.N) v[j] += ld16<T>(e_bias + col0 + j);
         }
       }
       if (e_act == 1) {
@@ -224,7 +237,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             float mv[8];
-            load_vec(reinterpret_cast<const bf16*>(&ep_mask[j >> 3]), mv);
+            load_vec(reinterpret_cast<const T*>(&ep_mask[j >> 3]), mv);
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[j + e] = mv[e] > 0.f ? v[j + e] : 0.f;
           }
@@ -232,7 +245,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
           const bf16* mk = e_mask + static_cast<int64_t>(row) * p.ldm + col0;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] = __bfloat162float(mk[j]) > 0.f ? v[j] : 0.f;
+            if (col0 + j < p.N) v[j] = ld16<T>(mk + j) > 0.f ? v[j] : 0.f;
         }
       }
       if (e_res) {
@@ -240,7 +253,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             float rv[8];
-            load_vec(reinterpret_cast<const bf16*>(&ep_res[j >> 3]), rv);
+            load_vec(reinterpret_cast<const T*>(&ep_res[j >> 3]), rv);
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[j + e] += rv[e];
           }
@@ -248,7 +261,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
           const bf16* rs = e_res + static_cast<int64_t>(row) * p.ldr + col0;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __bfloat162float(rs[j]);
+            if (col0 + j < p.N) v[j] += ld16<T>(rs + j);
         }
       }
     }
@@ -258,10 +271,10 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         uint4 o;
-        o.x = pack_bf16x2(v[8 * t], v[8 * t + 1]);
-        o.y = pack_bf16x2(v[8 * t + 2], v[8 * t + 3]);
-        o.z = pack_bf16x2(v[8 * t + 4], v[8 * t + 5]);
-        o.w = pack_bf16x2(v[8 * t + 6], v[8 * t + 7]);
+        o.x = pack_pair<T>(v[8 * t], v[8 * t + 1]);
+        o.y = pack_pair<T>(v[8 * t + 2], v[8 * t + 3]);
+        o.z = pack_pair<T>(v[8 * t + 4], v[8 * t + 5]);
+        o.w = pack_pair<T>(v[8 * t + 6], v[8 * t + 7]);
         *reinterpret_cast<uint4*>(brow + (((sub * 4 + t) ^ (lane_row & 7)) << 4)) = o;
       }
       const bool last_of_box = sub == 1 || col0 + 32 >= p.N;
@@ -292,43 +305,43 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
           uint4 o;
-          o.x = pack_bf16x2(v[j], v[j + 1]);
-          o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-          o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-          o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+          o.x = pack_pair<T>(v[j], v[j + 1]);
+          o.y = pack_pair<T>(v[j + 2], v[j + 3]);
+          o.z = pack_pair<T>(v[j + 4], v[j + 5]);
+          o.w = pack_pair<T>(v[j + 6], v[j + 7]);
           *reinterpret_cast<uint4*>(dst + j) = o;
         }
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+          if (col0 + j < p.N) st16<T>(dst + j, v[j]);
       }
     }
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FUSED>
+template <int BN, bool A_MN, bool B_MN, bool FUSED, typename T>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                    const GemmParams p) {
-  using T = Tile<BN>;
+  using TL = Tile<BN>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const uint32_t stg_base = smem_base + T::STAGES * T::STAGE_BYTES;
-  const uint32_t bar_base = stg_base + T::STG_BYTES;
+  const uint32_t stg_base = smem_base + TL::STAGES * TL::STAGE_BYTES;
+  const uint32_t bar_base = stg_base + TL::STG_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (T::STAGES + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + 2 + a); };
-  const uint32_t tmem_slot = bar_base + 8u * (2 * T::STAGES + 4);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (TL::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * TL::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * TL::STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * TL::STAGES + 4);
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + T::STAGES * T::STAGE_BYTES +
-                                                                          T::STG_BYTES + 8 * (2 * T::STAGES + 4));
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + TL::STAGES * TL::STAGE_BYTES +
+                                                                          TL::STG_BYTES + 8 * (2 * TL::STAGES + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < T::STAGES; ++s) {
+    for (int s = 0; s < TL::STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), (A_MN && p.rowsum_partial) ? 5 : 1);  // MMA commit (+ the four row-sum warps)
     }
@@ -339,7 +352,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, T::TMEM_COLS);
+    tmem_alloc(tmem_slot, TL::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -373,9 +386,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             ok = false;
             break;
           }
-          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
-          const uint32_t sb = sa + T::A_BYTES;
-          mbar_expect_tx(full_bar(stage), T::STAGE_BYTES);
+          const uint32_t sa = smem_base + stage * TL::STAGE_BYTES;
+          const uint32_t sb = sa + TL::A_BYTES;
+          mbar_expect_tx(full_bar(stage), TL::STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i)
@@ -390,7 +403,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           } else {
             tma_load_2d(sb, &tma_b, full_bar(stage), kb * BK, n_blk * BN);
           }
-          if (++stage == T::STAGES) {
+          if (++stage == TL::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
@@ -401,7 +414,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = umma_idesc_16<T>(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -425,8 +438,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
-          const uint32_t sb = sa + T::A_BYTES;
+          const uint32_t sa = smem_base + stage * TL::STAGE_BYTES;
+          const uint32_t sb = sa + TL::A_BYTES;
           // one descriptor per operand and stage; contraction step k adds a constant to the start-address field
           const uint64_t a0 = A_MN ? smem_desc_sw128(sa, 64 * BK * 2, 1024) : smem_desc_sw128(sa, 16, 1024);
           const uint64_t b0 = B_MN ? smem_desc_sw128(sb, 64 * BK * 2, 1024) : smem_desc_sw128(sb, 16, 1024);
@@ -437,7 +450,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             umma_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
-          if (++stage == T::STAGES) {
+          if (++stage == TL::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
@@ -480,18 +493,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           if (n_blk == 0) {
-            const unsigned char* src = smem_gen + stage * T::STAGE_BYTES + lane_off;
+            const unsigned char* src = smem_gen + stage * TL::STAGE_BYTES + lane_off;
 #pragma unroll
             for (int rr = 0; rr < BK / 8; ++rr) {
               float v[8];
-              load_vec(reinterpret_cast<const bf16*>(src + rr * 8 * 128), v);
+              load_vec(reinterpret_cast<const T*>(src + rr * 8 * 128), v);
 #pragma unroll
               for (int e = 0; e < 8; ++e) acc[e] += v[e];
             }
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(empty_bar(stage));
-          if (++stage == T::STAGES) {
+          if (++stage == TL::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
@@ -519,7 +532,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int chalf = (warp - 2) >> 2;  // the two warps of a lane quarter split the tile's columns
     EpilogueOut eo;
     eo.vec = p.d_vec != 0;
-    eo.stg = smem_gen + T::STAGES * T::STAGE_BYTES + chalf * (128 * 128);
+    eo.stg = smem_gen + TL::STAGES * TL::STAGE_BYTES + chalf * (128 * 128);
     eo.m0 = 0;
     eo.lane = lane;
     eo.policy = l2_policy_evict_first();
@@ -539,7 +552,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       eo.m0 = m_blk * BM;
-      drain_accumulator<BN, FUSED>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
+      drain_accumulator<BN, FUSED, T>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -551,7 +564,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, T::TMEM_COLS);
+    tmem_dealloc(tmem_base, TL::TMEM_COLS);
   }
 }
 
@@ -575,29 +588,29 @@ struct Tile2 {
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
-template <bool A_MN, bool B_MN, bool FUSED>
+template <bool A_MN, bool B_MN, bool FUSED, typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_tc2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const GemmParams p) {
-  using T = Tile2;
-  constexpr int BN = T::BN;
+  using TL = Tile2;
+  constexpr int BN = TL::BN;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const uint32_t stg_base = smem_base + T::STAGES * T::STAGE_BYTES;
-  const uint32_t bar_base = stg_base + T::STG_BYTES;
+  const uint32_t stg_base = smem_base + TL::STAGES * TL::STAGE_BYTES;
+  const uint32_t bar_base = stg_base + TL::STG_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (T::STAGES + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * T::STAGES + 2 + a); };
-  const uint32_t tmem_slot = bar_base + 8u * (2 * T::STAGES + 4);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (TL::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * TL::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * TL::STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * TL::STAGES + 4);
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + T::STAGES * T::STAGE_BYTES +
-                                                                          T::STG_BYTES + 8 * (2 * T::STAGES + 4));
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + TL::STAGES * TL::STAGE_BYTES +
+                                                                          TL::STG_BYTES + 8 * (2 * TL::STAGES + 4));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < T::STAGES; ++s) {
+    for (int s = 0; s < TL::STAGES; ++s) {
       mbar_init(full_bar(s), 1);   // rank 0: its producer's arrive.expect_tx (bytes of both CTAs)
       mbar_init(empty_bar(s), 1);  // one MMA commit
     }
@@ -608,7 +621,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc_2cta(tmem_slot, T::TMEM_COLS);
+    tmem_alloc_2cta(tmem_slot, TL::TMEM_COLS);
     tmem_relinquish_2cta();
   }
   tc_fence_before();
@@ -645,10 +658,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             ok = false;
             break;
           }
-          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
-          const uint32_t sb = sa + T::A_BYTES;
+          const uint32_t sa = smem_base + stage * TL::STAGE_BYTES;
+          const uint32_t sb = sa + TL::A_BYTES;
           const uint32_t full0 = map_to_cta(full_bar(stage), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * TL::STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) tma_load_2d_2cta(sa + i * (64 * BK * 2), &tma_a, full0, m0 + i * 64, kb * BK);
@@ -661,7 +674,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           } else {
             tma_load_2d_2cta(sb, &tma_b, full0, kb * BK, n0);
           }
-          if (++stage == T::STAGES) {
+          if (++stage == TL::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
@@ -672,7 +685,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer (rank 0 only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = umma_idesc_16<T>(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -696,8 +709,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * T::STAGE_BYTES;
-          const uint32_t sb = sa + T::A_BYTES;
+          const uint32_t sa = smem_base + stage * TL::STAGE_BYTES;
+          const uint32_t sb = sa + TL::A_BYTES;
           const uint64_t a0 = A_MN ? smem_desc_sw128(sa, 64 * BK * 2, 1024) : smem_desc_sw128(sa, 16, 1024);
           const uint64_t b0 = B_MN ? smem_desc_sw128(sb, 64 * BK * 2, 1024) : smem_desc_sw128(sb, 16, 1024);
 #pragma unroll
@@ -708,7 +721,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           }
           umma_commit_2cta(map_to_cta(empty_bar(stage), 0));  // both CTAs may refill this stage
           umma_commit_2cta(map_to_cta(empty_bar(stage), 1));
-          if (++stage == T::STAGES) {
+          if (++stage == TL::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
@@ -729,7 +742,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int chalf = (warp - 2) >> 2;
     EpilogueOut eo;
     eo.vec = p.d_vec != 0;
-    eo.stg = smem_gen + T::STAGES * T::STAGE_BYTES + chalf * (128 * 128);
+    eo.stg = smem_gen + TL::STAGES * TL::STAGE_BYTES + chalf * (128 * 128);
     eo.m0 = 0;
     eo.lane = lane;
     eo.policy = l2_policy_evict_first();
@@ -749,7 +762,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const int row = m_blk * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       eo.m0 = m_blk * 256 + static_cast<int>(rank) * 128;
-      drain_accumulator<BN, FUSED>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
+      drain_accumulator<BN, FUSED, T>(p, t_row, row, n_blk, split, chalf, eo, quarter * 32 + lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
@@ -761,13 +774,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   cluster_sync_all();  // no CTA retires while its peer may still signal its barriers or read its shared memory
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc_2cta(tmem_base, T::TMEM_COLS);
+    tmem_dealloc_2cta(tmem_base, TL::TMEM_COLS);
   }
 }
 
 // out[r][c] = T(sum_s partial[s][r][c]) (+ bias[c], ReLU); fixed summation order.
 // VEC: four columns per thread (N, ldd multiples of 4, 8-byte aligned output), 32-bit indices.
-template <bool VEC>
+template <bool VEC, typename T>
 __global__ void __launch_bounds__(256)
     splitk_finalize_kernel(const float* __restrict__ partial, int splits, int M, int N, bf16* __restrict__ out,
                            int64_t ldd, const bf16* __restrict__ bias, int act) {
@@ -789,10 +802,10 @@ __global__ void __launch_bounds__(256)
       }
       const int r = i / n4, c = (i - r * n4) << 2;
       if (bias) {
-        acc.x += __bfloat162float(bias[c]);
-        acc.y += __bfloat162float(bias[c + 1]);
-        acc.z += __bfloat162float(bias[c + 2]);
-        acc.w += __bfloat162float(bias[c + 3]);
+        acc.x += ld16<T>(bias + c);
+        acc.y += ld16<T>(bias + c + 1);
+        acc.z += ld16<T>(bias + c + 2);
+        acc.w += ld16<T>(bias + c + 3);
       }
       if (act == 1) {
         acc.x = fmaxf(acc.x, 0.f);
@@ -801,8 +814,8 @@ __global__ void __launch_bounds__(256)
         acc.w = fmaxf(acc.w, 0.f);
       }
       uint2 o;
-      o.x = pack_bf16x2(acc.x, acc.y);
-      o.y = pack_bf16x2(acc.z, acc.w);
+      o.x = pack_pair<T>(acc.x, acc.y);
+      o.y = pack_pair<T>(acc.z, acc.w);
       *reinterpret_cast<uint2*>(out + static_cast<int64_t>(r) * ldd + c) = o;
     }
     return;
@@ -812,13 +825,14 @@ __global__ void __launch_bounds__(256)
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partial[s * total + i];
     const int64_t r = i / N, c = i - r * N;
-    if (bias) acc += __bfloat162float(bias[c]);
+    if (bias) acc += ld16<T>(bias + c);
     if (act == 1) acc = fmaxf(acc, 0.f);
-    out[r * ldd + c] = __float2bfloat16_rn(acc);
+    st16<T>(out + r * ldd + c, acc);
   }
 }
 
 // db[i] = sum_s rowsum_partial[s][i], fixed order.
+template <typename T>
 __global__ void __launch_bounds__(256)
     rowsum_finalize_kernel(const float* __restrict__ partial, int splits, int M, bf16* __restrict__ out) {
   pdl_launch_dependents();
@@ -827,7 +841,7 @@ __global__ void __launch_bounds__(256)
   if (i >= M) return;
   float acc = 0.f;
   for (int s = 0; s < splits; ++s) acc += partial[static_cast<int64_t>(s) * M + i];
-  out[i] = __float2bfloat16_rn(acc);
+  st16<T>(out + i, acc);
 }
 
 // ------------------------------------------------------- CUDA-core fallback
@@ -972,43 +986,43 @@ int choose_splits(int64_t tiles, int64_t K, int slots) {
 
 int choose_bn(int64_t N) { return N > 128 ? 256 : 128; }
 
-template <int BN, bool A_MN, bool B_MN, bool FUSED>
+template <int BN, bool A_MN, bool B_MN, bool FUSED, typename T>
 int launch_tc(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st) {
-  using T = Tile<BN>;
+  using TL = Tile<BN>;
   CUtensorMap ma, mb;
   if (!make_map(&ma, a, 64, A_MN ? BK : BM)) return MGB_ECUDA;
   if (!make_map(&mb, b, 64, B_MN ? BK : BN)) return MGB_ECUDA;
-  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, FUSED>;
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, FUSED, T>;
   static bool attr_done = false;  // per instantiation; the attribute is per function and device
   static int attr_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done || attr_dev != dev) {
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(MGB_ECUDA, "gemm smem opt-in (%d B): %s", T::SMEM_BYTES, cudaGetErrorString(e));
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TL::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(MGB_ECUDA, "gemm smem opt-in (%d B): %s", TL::SMEM_BYTES, cudaGetErrorString(e));
     attr_done = true;
     attr_dev = dev;
   }
   const int total = p.num_m * p.num_n * p.splits;
   const int grid = total < sm_count() ? total : sm_count();
-  launch_pdl(kern, dim3(grid), dim3(kGemmThreads), T::SMEM_BYTES, st, ma, mb, p);
+  launch_pdl(kern, dim3(grid), dim3(kGemmThreads), TL::SMEM_BYTES, st, ma, mb, p);
   return check_launch("gemm_tc_kernel");
 }
 
-template <bool A_MN, bool B_MN, bool FUSED>
+template <bool A_MN, bool B_MN, bool FUSED, typename T>
 int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st) {
-  using T = Tile2;
+  using TL = Tile2;
   CUtensorMap ma, mb;
   if (!make_map(&ma, a, 64, A_MN ? BK : 128)) return MGB_ECUDA;
   if (!make_map(&mb, b, 64, B_MN ? BK : 128)) return MGB_ECUDA;
-  auto kern = gemm_tc2_kernel<A_MN, B_MN, FUSED>;
+  auto kern = gemm_tc2_kernel<A_MN, B_MN, FUSED, T>;
   static bool attr_done = false;
   static int attr_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done || attr_dev != dev) {
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(MGB_ECUDA, "gemm smem opt-in (%d B): %s", T::SMEM_BYTES, cudaGetErrorString(e));
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TL::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(MGB_ECUDA, "gemm smem opt-in (%d B): %s", TL::SMEM_BYTES, cudaGetErrorString(e));
     attr_done = true;
     attr_dev = dev;
   }
@@ -1021,7 +1035,7 @@ int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st
     cudaLaunchConfig_t occ = {};
     occ.gridDim = dim3(sm_count() / 2 * 2);
     occ.blockDim = dim3(kGemmThreads);
-    occ.dynamicSmemBytes = T::SMEM_BYTES;
+    occ.dynamicSmemBytes = TL::SMEM_BYTES;
     cudaLaunchAttribute ca[1];
     ca[0].id = cudaLaunchAttributeClusterDimension;
     ca[0].val.clusterDim.x = 2;
@@ -1038,13 +1052,13 @@ int launch_tc2(const Operand& a, const Operand& b, GemmParams p, cudaStream_t st
   }
   const int max_clusters = resident;
   const int clusters = total < max_clusters ? total : max_clusters;
-  launch_pdl(kern, dim3(2 * clusters), dim3(kGemmThreads), T::SMEM_BYTES, st, ma, mb, p);
+  launch_pdl(kern, dim3(2 * clusters), dim3(kGemmThreads), TL::SMEM_BYTES, st, ma, mb, p);
   return check_launch("gemm_tc2_kernel");
 }
 
 // D[M,N] = A . B^T style product on tensor cores; operands described as they lie in memory.
 // rowsum_out (A_MN only): bf16[M] = sum over the contraction of A(i, :), produced inside the same kernel.
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, typename T>
 int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epilogue& ep, bf16* rowsum_out, int64_t M,
             int64_t N, int64_t K, void* ws, size_t ws_bytes, bool allow_split, cudaStream_t st) {
   const int BN = choose_bn(N);
@@ -1106,11 +1120,13 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
   const bool fused = p.bias || p.act || p.relu_mask || p.residual || p.bits_out || p.bits_in;
   int rc;
   if (fused)
-    rc = pair ? launch_tc2<A_MN, B_MN, true>(a, b, p, st)
-              : (BN == 256 ? launch_tc<256, A_MN, B_MN, true>(a, b, p, st) : launch_tc<128, A_MN, B_MN, true>(a, b, p, st));
+    rc = pair ? launch_tc2<A_MN, B_MN, true, T>(a, b, p, st)
+              : (BN == 256 ? launch_tc<256, A_MN, B_MN, true, T>(a, b, p, st)
+                           : launch_tc<128, A_MN, B_MN, true, T>(a, b, p, st));
   else
-    rc = pair ? launch_tc2<A_MN, B_MN, false>(a, b, p, st)
-              : (BN == 256 ? launch_tc<256, A_MN, B_MN, false>(a, b, p, st) : launch_tc<128, A_MN, B_MN, false>(a, b, p, st));
+    rc = pair ? launch_tc2<A_MN, B_MN, false, T>(a, b, p, st)
+              : (BN == 256 ? launch_tc<256, A_MN, B_MN, false, T>(a, b, p, st)
+                           : launch_tc<128, A_MN, B_MN, false, T>(a, b, p, st));
   if (rc != MGB_OK) return rc;
   if (p.splits > 1) {
     const int64_t total = M * N;
@@ -1119,14 +1135,14 @@ int gemm_tc(const Operand& a, const Operand& b, bf16* d, int64_t ldd, const Epil
     int grid = static_cast<int>(((vec ? total / 4 : total) + 255) / 256);
     if (grid > sm_count() * 8) grid = sm_count() * 8;
     if (vec)
-      launch_pdl(splitk_finalize_kernel<true>, dim3(grid), dim3(256), 0, st, p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
+      launch_pdl(splitk_finalize_kernel<true, T>, dim3(grid), dim3(256), 0, st, p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
     else
-      launch_pdl(splitk_finalize_kernel<false>, dim3(grid), dim3(256), 0, st, p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
+      launch_pdl(splitk_finalize_kernel<false, T>, dim3(grid), dim3(256), 0, st, p.partial, p.splits, p.M, p.N, d, ldd, bias, ep.act);
     rc = check_launch("splitk_finalize_kernel");
     if (rc != MGB_OK) return rc;
   }
   if (rowsum_out) {
-    launch_pdl(rowsum_finalize_kernel, dim3((p.M + 255) / 256), dim3(256), 0, st, p.rowsum_partial, p.splits, p.M, rowsum_out);
+    launch_pdl(rowsum_finalize_kernel<T>, dim3((p.M + 255) / 256), dim3(256), 0, st, p.rowsum_partial, p.splits, p.M, rowsum_out);
     rc = check_launch("rowsum_finalize_kernel");
   }
   return rc;
@@ -1183,14 +1199,21 @@ int matmul_fwd_impl(const void* a, const void* w, const void* bias, const void* 
   ep.bits_out = static_cast<uint32_t*>(relu_bits);
   ep.ldbits = ld_bits;
   const Operand oa{a, M, K, lda}, ow{w, N, K, ldw};
-  const bool tc = dtype == MGB_BF16 && tma_ok(oa) && tma_ok(ow);
+  const bool half16 = dtype == MGB_BF16 || dtype == MGB_F16;
+  const bool tc = half16 && tma_ok(oa) && tma_ok(ow);
   MGB_REQUIRE(!relu_bits || tc, MGB_EUNSUPPORTED,
-              "matmul_bias_bt_relu_bits: needs bf16 operands with 16-byte-aligned rows (the tensor-core path)");
+              "matmul_bias_bt_relu_bits: needs 16-bit operands with 16-byte-aligned rows (the tensor-core path)");
   if (dtype == MGB_F32)
     return gemm_simt<float>(static_cast<const float*>(a), static_cast<const float*>(w), static_cast<float*>(y), M, N, K,
                             lda, 1, ldw, 1, ldy, ep, st);
-  MGB_REQUIRE(dtype == MGB_BF16, MGB_EDTYPE, "matmul_bias_bt: unsupported dtype code %d", dtype);
-  if (tc) return gemm_tc<false, false>(oa, ow, static_cast<bf16*>(y), ldy, ep, nullptr, M, N, K, nullptr, 0, false, st);
+  MGB_REQUIRE(half16, MGB_EDTYPE, "matmul_bias_bt: unsupported dtype code %d", dtype);
+  if (dtype == MGB_F16) {
+    if (tc)
+      return gemm_tc<false, false, __half>(oa, ow, static_cast<bf16*>(y), ldy, ep, nullptr, M, N, K, nullptr, 0, false, st);
+    return gemm_simt<__half>(static_cast<const __half*>(a), static_cast<const __half*>(w), static_cast<__half*>(y), M, N,
+                             K, lda, 1, ldw, 1, ldy, ep, st);
+  }
+  if (tc) return gemm_tc<false, false, bf16>(oa, ow, static_cast<bf16*>(y), ldy, ep, nullptr, M, N, K, nullptr, 0, false, st);
   return gemm_simt<bf16>(static_cast<const bf16*>(a), static_cast<const bf16*>(w), static_cast<bf16*>(y), M, N, K, lda,
                          1, ldw, 1, ldy, ep, st);
 }
@@ -1217,12 +1240,48 @@ MGB_EXPORT int mograd_b200_matmul_bias_bt(const void* a, const void* w, const vo
 }
 
 MGB_EXPORT size_t mograd_b200_matmul_bias_bt_bwd_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
-  if (dtype != MGB_BF16 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((dtype != MGB_BF16 && dtype != MGB_F16) || M <= 0 || N <= 0 || K <= 0) return 0;
   // dW is N x K with contraction M (may be split); db partials ride along.  dX (contraction N) is never split.
   return rowsum_bytes(N) + splitk_bytes(N, K, kMaxSplits);
 }
 
 namespace {
+// dX, dW, db of a 16-bit (bf16 / fp16) Linear layer: tensor cores where TMA can address the operands, the CUDA-core
+// kernel otherwise.
+template <typename T>
+int matmul_bwd_16(const void* dy, const void* x, const void* w, const Epilogue& epx, void* dx, void* dw, void* db,
+                  int64_t M, int64_t N, int64_t K, int64_t lddy, int64_t ldx, int64_t ldw, int64_t lddx, int64_t lddw,
+                  void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  int rc = MGB_OK;
+  const Epilogue none;
+  const T* dyb = static_cast<const T*>(dy);
+  const Operand ody{dy, M, N, lddy};
+  if (dx) {
+    const Operand ow{w, N, K, ldw};
+    if (tma_ok(ody) && tma_ok(ow))
+      rc = gemm_tc<false, true, T>(ody, ow, static_cast<bf16*>(dx), lddx, epx, nullptr, M, K, N, nullptr, 0, false, st);
+    else
+      rc = gemm_simt<T>(dyb, static_cast<const T*>(w), static_cast<T*>(dx), M, K, N, lddy, 1, 1, ldw, lddx, epx, st);
+    if (rc != MGB_OK) return rc;
+  }
+  bool db_done = false;
+  if (dw) {
+    const Operand ox{x, M, K, ldx};
+    if (tma_ok(ody) && tma_ok(ox)) {
+      // db comes out of the same kernel when the workspace has room for its partial sums
+      bf16* db_fused = (db && workspace && workspace_bytes >= rowsum_bytes(N)) ? static_cast<bf16*>(db) : nullptr;
+      rc = gemm_tc<true, true, T>(ody, ox, static_cast<bf16*>(dw), lddw, none, db_fused, N, K, M, workspace,
+                                  workspace_bytes, true, st);
+      db_done = db_fused != nullptr;
+    } else {
+      rc = gemm_simt<T>(dyb, static_cast<const T*>(x), static_cast<T*>(dw), N, K, M, 1, lddy, 1, ldx, lddw, none, st);
+    }
+    if (rc != MGB_OK) return rc;
+  }
+  if (db && !db_done) rc = colsum<T>(dy, db, M, N, lddy, st);
+  return rc;
+}
+
 int matmul_bwd_impl(const void* dy, const void* x, const void* w, const void* relu_y, const void* relu_bits,
                     const void* dx_residual, void* dx, void* dw, void* db, int64_t M, int64_t N, int64_t K, int64_t lddy,
                     int64_t ldx, int64_t ldw, int64_t ld_relu_y, int64_t ld_bits, int64_t ld_dx_residual, int64_t lddx,
@@ -1236,7 +1295,8 @@ int matmul_bwd_impl(const void* dy, const void* x, const void* w, const void* re
   MGB_REQUIRE(lddy >= N && (!dx || (ldw >= K && lddx >= K)) && (!dw || (ldx >= K && lddw >= K)) &&
                   (!relu_y || ld_relu_y >= K) && (!dx_residual || ld_dx_residual >= K),
               MGB_EINVAL, "matmul_bias_bt_bwd: leading dimension too small");
-  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32, MGB_EDTYPE, "matmul_bias_bt_bwd: unsupported dtype code %d", dtype);
+  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32 || dtype == MGB_F16, MGB_EDTYPE,
+              "matmul_bias_bt_bwd: unsupported dtype code %d", dtype);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Epilogue epx;  // dX = (dY W) masked by relu_y > 0, plus dx_residual
   epx.relu_mask = relu_y;
@@ -1247,8 +1307,8 @@ int matmul_bwd_impl(const void* dy, const void* x, const void* w, const void* re
   epx.ldbits = ld_bits;
   if (relu_bits && dx) {
     const Operand ody0{dy, M, N, lddy}, ow0{w, N, K, ldw};
-    MGB_REQUIRE(dtype == MGB_BF16 && tma_ok(ody0) && tma_ok(ow0), MGB_EUNSUPPORTED,
-                "matmul_bias_bt_bwd_relu_bits: needs bf16 operands with 16-byte-aligned rows (the tensor-core path)");
+    MGB_REQUIRE(dtype != MGB_F32 && tma_ok(ody0) && tma_ok(ow0), MGB_EUNSUPPORTED,
+                "matmul_bias_bt_bwd_relu_bits: needs 16-bit operands with 16-byte-aligned rows (the tensor-core path)");
   }
   const Epilogue none;
   if (dtype == MGB_F32) {
@@ -1268,34 +1328,11 @@ int matmul_bwd_impl(const void* dy, const void* x, const void* w, const void* re
     if (db) rc = colsum<float>(dy, db, M, N, lddy, st);
     return rc;
   }
-  const bf16* dyb = static_cast<const bf16*>(dy);
-  const Operand ody{dy, M, N, lddy};
-  if (dx) {
-    const Operand ow{w, N, K, ldw};
-    if (tma_ok(ody) && tma_ok(ow))
-      rc = gemm_tc<false, true>(ody, ow, static_cast<bf16*>(dx), lddx, epx, nullptr, M, K, N, nullptr, 0, false, st);
-    else
-      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(w), static_cast<bf16*>(dx), M, K, N, lddy, 1, 1, ldw, lddx,
-                           epx, st);
-    if (rc != MGB_OK) return rc;
-  }
-  bool db_done = false;
-  if (dw) {
-    const Operand ox{x, M, K, ldx};
-    if (tma_ok(ody) && tma_ok(ox)) {
-      // db comes out of the same kernel when the workspace has room for its partial sums
-      bf16* db_fused = (db && workspace && workspace_bytes >= rowsum_bytes(N)) ? static_cast<bf16*>(db) : nullptr;
-      rc = gemm_tc<true, true>(ody, ox, static_cast<bf16*>(dw), lddw, none, db_fused, N, K, M, workspace,
-                               workspace_bytes, true, st);
-      db_done = db_fused != nullptr;
-    } else {
-      rc = gemm_simt<bf16>(dyb, static_cast<const bf16*>(x), static_cast<bf16*>(dw), N, K, M, 1, lddy, 1, ldx, lddw,
-                           none, st);
-    }
-    if (rc != MGB_OK) return rc;
-  }
-  if (db && !db_done) rc = colsum<bf16>(dy, db, M, N, lddy, st);
-  return rc;
+  if (dtype == MGB_F16)
+    return matmul_bwd_16<__half>(dy, x, w, epx, dx, dw, db, M, N, K, lddy, ldx, ldw, lddx, lddw, workspace,
+                                 workspace_bytes, st);
+  return matmul_bwd_16<bf16>(dy, x, w, epx, dx, dw, db, M, N, K, lddy, ldx, ldw, lddx, lddw, workspace, workspace_bytes,
+                             st);
 }
 }  // namespace
 

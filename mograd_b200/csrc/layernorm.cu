@@ -44,6 +44,11 @@ __device__ __forceinline__ void unpack2(const uint4& r, float2 (&v)[4], const __
 #pragma unroll
   for (int i = 0; i < 4; ++i) v[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
 }
+__device__ __forceinline__ void unpack2(const uint4& r, float2 (&v)[4], const __half*) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+}
 __device__ __forceinline__ void unpack2(const uint4& r, float2 (&v)[2], const float*) {
   v[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
   v[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
@@ -51,6 +56,10 @@ __device__ __forceinline__ void unpack2(const uint4& r, float2 (&v)[2], const fl
 __device__ __forceinline__ uint4 pack2(const float2 (&v)[4], const __nv_bfloat16*) {
   return make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y), pack_bf16x2(v[2].x, v[2].y),
                     pack_bf16x2(v[3].x, v[3].y));
+}
+__device__ __forceinline__ uint4 pack2(const float2 (&v)[4], const __half*) {
+  return make_uint4(pack_f16x2(v[0].x, v[0].y), pack_f16x2(v[1].x, v[1].y), pack_f16x2(v[2].x, v[2].y),
+                    pack_f16x2(v[3].x, v[3].y));
 }
 __device__ __forceinline__ uint4 pack2(const float2 (&v)[2], const float*) {
   return make_uint4(__float_as_uint(v[0].x), __float_as_uint(v[0].y), __float_as_uint(v[1].x), __float_as_uint(v[1].y));
@@ -771,6 +780,8 @@ MGB_EXPORT int mograd_b200_layer_norm_fwd(const void* x, const void* gamma, cons
       return ln_fwd<__nv_bfloat16>(x, gamma, beta, y, mean, rstd, rows, cols, eps, st);
     case MGB_F32:
       return ln_fwd<float>(x, gamma, beta, y, mean, rstd, rows, cols, eps, st);
+    case MGB_F16:
+      return ln_fwd<__half>(x, gamma, beta, y, mean, rstd, rows, cols, eps, st);
     default:
       return fail(MGB_EDTYPE, "layer_norm_fwd: unsupported dtype code %d", dtype);
   }
@@ -779,7 +790,7 @@ MGB_EXPORT int mograd_b200_layer_norm_fwd(const void* x, const void* gamma, cons
 MGB_EXPORT size_t mograd_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int64_t cols, int dtype) {
   if (rows <= 0 || cols <= 0 || cols > 16384) return 0;
   Plan pl;
-  const bool ok = dtype == MGB_BF16 ? make_plan<__nv_bfloat16>(rows, cols, pl) : make_plan<float>(rows, cols, pl);
+  const bool ok = dtype == MGB_F32 ? make_plan<float>(rows, cols, pl) : make_plan<__nv_bfloat16>(rows, cols, pl);
   if (!ok) return 0;
   return round_up(static_cast<size_t>(pl.grid) * 2 * cols * sizeof(float), 256);
 }
@@ -811,6 +822,8 @@ MGB_EXPORT int mograd_b200_layer_norm_bwd_ex(const void* dy, const void* x, cons
                                    st);
     case MGB_F32:
       return ln_bwd<float>(dy, x, gamma, resid, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes, st);
+    case MGB_F16:
+      return ln_bwd<__half>(dy, x, gamma, resid, dx, dgamma, dbeta, rows, cols, eps, workspace, workspace_bytes, st);
     default:
       return fail(MGB_EDTYPE, "layer_norm_bwd: unsupported dtype code %d", dtype);
   }
@@ -825,8 +838,8 @@ MGB_EXPORT int mograd_b200_layer_norm_bwd_static(const void* dy, const void* x, 
   MGB_REQUIRE(dy && x && gamma && dx && dgamma && dbeta, MGB_EINVAL, "layer_norm_bwd_static: NULL argument");
   int rc = check_ln("layer_norm_bwd_static", rows, cols);
   if (rc != MGB_OK) return rc;
-  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32, MGB_EDTYPE, "layer_norm_bwd_static: unsupported dtype code %d",
-              dtype);
+  MGB_REQUIRE(dtype == MGB_BF16 || dtype == MGB_F32 || dtype == MGB_F16, MGB_EDTYPE,
+              "layer_norm_bwd_static: unsupported dtype code %d", dtype);
   const size_t need = mograd_b200_layer_norm_bwd_workspace_bytes(rows, cols, dtype);
   const size_t have = kStaticScratchFloats * sizeof(float);
   MGB_REQUIRE(need > 0 && need <= have, MGB_EUNSUPPORTED,
@@ -839,5 +852,7 @@ MGB_EXPORT int mograd_b200_layer_norm_bwd_static(const void* dy, const void* x, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == MGB_BF16)
     return ln_bwd<__nv_bfloat16>(dy, x, gamma, nullptr, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
+  if (dtype == MGB_F16)
+    return ln_bwd<__half>(dy, x, gamma, nullptr, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
   return ln_bwd<float>(dy, x, gamma, nullptr, dx, dgamma, dbeta, rows, cols, eps, scratch, have, st);
 }

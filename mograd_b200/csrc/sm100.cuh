@@ -10,6 +10,8 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -312,11 +314,30 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn, i
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// The same for a 16-bit storage type T (bfloat16 or float16): only the A / B format fields differ.
+template <typename T>
+struct UmmaFormat;
+template <>
+struct UmmaFormat<__nv_bfloat16> {
+  static constexpr uint32_t kCode = 1;
+};
+template <>
+struct UmmaFormat<__half> {
+  static constexpr uint32_t kCode = 0;
+};
+template <typename T>
+__host__ __device__ constexpr uint32_t umma_idesc_16(int M, int N, int a_mn, int b_mn) {
+  return (1u << 4) | (UmmaFormat<T>::kCode << 7) | (UmmaFormat<T>::kCode << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 }  // namespace sm100
 
 // ------------------------------------------------------------ host: TMA maps
-// Encodes a tiled tensor map for a bf16 tensor (up to 4 dims, innermost first)
-// with 128-byte swizzle and zero fill outside the tensor.  Returns false and
+// Encodes a tiled tensor map for a tensor of 16-bit elements (bf16 or fp16: a
+// tile copy moves the elements unchanged, so one encoding serves both; up to
+// 4 dims, innermost first) with 128-byte swizzle and zero fill outside the tensor.  Returns false and
 // sets the error text when the driver entry point is unavailable or rejects
 // the arguments.
 bool encode_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,

@@ -593,6 +593,8 @@ MGB_EXPORT int mograd_b200_softmax_xent_fwd_bwd(const void* logits, const int64_
       return xent_index<__nv_bfloat16>(logits, labels, loss, dlogits, N, C, ldx, lddx, upstream, workspace, st);
     case MGB_F32:
       return xent_index<float>(logits, labels, loss, dlogits, N, C, ldx, lddx, upstream, workspace, st);
+    case MGB_F16:
+      return xent_index<__half>(logits, labels, loss, dlogits, N, C, ldx, lddx, upstream, workspace, st);
     default:
       return fail(MGB_EDTYPE, "softmax_xent_fwd_bwd: unsupported dtype code %d", dtype);
   }
@@ -614,6 +616,8 @@ MGB_EXPORT int mograd_b200_cross_entropy(const void* logits, const void* labels,
       return xent_dense_fwd<__nv_bfloat16>(logits, labels, loss, N, C, ldx, ldl, workspace, st);
     case MGB_F32:
       return xent_dense_fwd<float>(logits, labels, loss, N, C, ldx, ldl, workspace, st);
+    case MGB_F16:
+      return xent_dense_fwd<__half>(logits, labels, loss, N, C, ldx, ldl, workspace, st);
     default:
       return fail(MGB_EDTYPE, "cross_entropy: unsupported dtype code %d", dtype);
   }
@@ -632,6 +636,8 @@ MGB_EXPORT int mograd_b200_cross_entropy_grad(const void* upstream, const void* 
       return xent_dense_bwd<__nv_bfloat16>(upstream, logits, labels, dst, N, C, ldx, ldl, lddst, st);
     case MGB_F32:
       return xent_dense_bwd<float>(upstream, logits, labels, dst, N, C, ldx, ldl, lddst, st);
+    case MGB_F16:
+      return xent_dense_bwd<__half>(upstream, logits, labels, dst, N, C, ldx, ldl, lddst, st);
     default:
       return fail(MGB_EDTYPE, "cross_entropy_grad: unsupported dtype code %d", dtype);
   }

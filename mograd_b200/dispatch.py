@@ -18,7 +18,7 @@ import torch
 from . import _lib
 from ._lib import KernelError, call, query
 
-_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32, torch.float16: _lib.F16}
 _workspaces: dict = {}
 
 

@@ -416,9 +416,9 @@ class TinyTransformer(_Model):
             self.saved.append(dict(ln1=new(T, d), qkv=new(T, 3 * d), ctx=new(T, d),
                                    lse=torch.empty((batch, n_heads, seq), dtype=torch.float32, device=dev),
                                    h=new(T, d), ln2=new(T, d), f1=new(T, d_ff)))
-        # ReLU mask of the feed-forward activation as one bit per element (bf16 tensor-core path only): the backward
+        # ReLU mask of the feed-forward activation as one bit per element (16-bit tensor-core path only): the backward
         # GEMM fetches T*d_ff/8 bytes instead of re-reading the activation
-        self.relu_bits = dtype == torch.bfloat16 and dev.type == "cuda" and d % 8 == 0 and d_ff % 8 == 0
+        self.relu_bits = dtype in (torch.bfloat16, torch.float16) and dev.type == "cuda" and d % 8 == 0 and d_ff % 8 == 0
         if self.relu_bits:
             for sv in self.saved:
                 sv["f1_bits"] = torch.empty((T, (d_ff + 31) // 32), dtype=torch.int32, device=dev)

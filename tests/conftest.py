@@ -29,6 +29,29 @@ def rel_err(got, want):
 # max-abs-err / max-abs-ref <= 2e-2 against the fp32/f64 CPU result.
 TOL_F32 = 1e-4
 TOL_BF16 = 2e-2
+# float16 storage: the reference's own gate for its half-precision tensor-core kernels
+# (tests/kernels/attention/mma.mojo:423-424, f16 backward 8e-3)
+TOL_F16 = 8e-3
+
+
+def tol_of(dt):
+    return {"f32": TOL_F32, "bf16": TOL_BF16, "f16": TOL_F16}[dt]
+
+
+def torch_dtype(dt):
+    import torch
+
+    return {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[dt]
+
+
+def round_to(dt, x):
+    """float32 numpy array rounded through the storage type dt (identity for f32)."""
+    x = np.asarray(x, dtype=np.float32)
+    if dt == "bf16":
+        return bf16_round(x)
+    if dt == "f16":
+        return x.astype(np.float16).astype(np.float32)
+    return x
 
 
 @pytest.fixture(scope="session")

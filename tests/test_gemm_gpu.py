@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err
+from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err, round_to, tol_of, torch_dtype
 
 pytestmark = pytest.mark.gpu
 
@@ -17,15 +17,14 @@ def _mk(M, N, K, dt, seed):
     w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
     b = rng.standard_normal(N).astype(np.float32)
     dy = rng.standard_normal((M, N)).astype(np.float32)
-    if dt == "bf16":
-        a, w, b, dy = (bf16_round(t) for t in (a, w, b, dy))
+    a, w, b, dy = (round_to(dt, t) for t in (a, w, b, dy))
     return a, w, b, dy
 
 
 def _dev(t, cuda, dt):
     import torch
 
-    return torch.from_numpy(t).to(cuda).to(torch.float32 if dt == "f32" else torch.bfloat16)
+    return torch.from_numpy(t).to(cuda).to(torch_dtype(dt))
 
 
 def _status():
@@ -38,7 +37,7 @@ def _status():
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("dt", ["bf16", "f32", "f16"])
 def test_forward(cuda, oracle, M, N, K, dt):
     from mograd_b200 import dispatch as Kx
 
@@ -46,15 +45,15 @@ def test_forward(cuda, oracle, M, N, K, dt):
     want = oracle.matmul_bias_bt(a, w, b)
     y = Kx.matmul_bias_strided(_dev(a, cuda, dt), _dev(w, cuda, dt), _dev(b, cuda, dt))
     assert _status() == 0
-    assert rel_err(y.float().cpu().numpy(), want) <= (TOL_F32 if dt == "f32" else TOL_BF16)
+    assert rel_err(y.float().cpu().numpy(), want) <= tol_of(dt)
     # no bias + fused ReLU
     y2 = Kx.matmul_bias_strided(_dev(a, cuda, dt), _dev(w, cuda, dt), None, act=1)
     want2 = np.maximum(oracle.matmul_bias_bt(a, w), 0)
-    assert rel_err(y2.float().cpu().numpy(), want2) <= (TOL_F32 if dt == "f32" else TOL_BF16)
+    assert rel_err(y2.float().cpu().numpy(), want2) <= tol_of(dt)
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("dt", ["bf16", "f32", "f16"])
 def test_backward(cuda, oracle, M, N, K, dt):
     from mograd_b200 import dispatch as Kx
 
@@ -62,7 +61,7 @@ def test_backward(cuda, oracle, M, N, K, dt):
     wdx, wdw, wdb = oracle.matmul_bias_bt_bwd(dy, x, w)
     dx, dw, db = Kx.matmul_bias_bt_bwd(_dev(dy, cuda, dt), _dev(x, cuda, dt), _dev(w, cuda, dt))
     assert _status() == 0
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    tol = tol_of(dt)
     assert rel_err(dx.float().cpu().numpy(), wdx) <= tol
     assert rel_err(dw.float().cpu().numpy(), wdw) <= tol
     assert rel_err(db.float().cpu().numpy(), wdb) <= tol
@@ -125,7 +124,7 @@ def test_large_linearity(cuda):
     assert rel_err(y1[:256].cpu().numpy(), ref.cpu().numpy()) <= TOL_BF16
 
 
-@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("dt", ["bf16", "f32", "f16"])
 @pytest.mark.parametrize("M,N,K", [(256, 384, 128), (130, 72, 200), (64, 10, 32)])
 def test_extended_epilogues(cuda, oracle, M, N, K, dt):
     """Fused residual add (forward), ReLU-backward mask and gradient accumulation (dX), db inside the dW GEMM."""
@@ -136,9 +135,8 @@ def test_extended_epilogues(cuda, oracle, M, N, K, dt):
     res = rng.standard_normal((M, N)).astype(np.float32)
     relu_y = np.maximum(rng.standard_normal((M, K)), 0).astype(np.float32)
     dres = rng.standard_normal((M, K)).astype(np.float32)
-    if dt == "bf16":
-        res, relu_y, dres = bf16_round(res), bf16_round(relu_y), bf16_round(dres)
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    res, relu_y, dres = round_to(dt, res), round_to(dt, relu_y), round_to(dt, dres)
+    tol = tol_of(dt)
     y = Kx.matmul_bias_strided(_dev(x, cuda, dt), _dev(w, cuda, dt), _dev(b, cuda, dt), act=1, residual=_dev(res, cuda, dt))
     want = np.maximum(oracle.matmul_bias_bt(x, w, b), 0) + res
     assert rel_err(y.float().cpu().numpy(), want) <= tol

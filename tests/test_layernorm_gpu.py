@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err
+from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err, round_to, tol_of, torch_dtype
 
 pytestmark = pytest.mark.gpu
 
@@ -10,7 +10,7 @@ SHAPES = [(1, 4), (2, 4), (128, 256), (300, 384), (257, 768), (64, 1000), (33, 4
 
 
 @pytest.mark.parametrize("rows,cols", SHAPES)
-@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 def test_bwd_matches_oracle(cuda, oracle, rows, cols, dt):
     import torch
     from mograd_b200 import dispatch as K
@@ -19,20 +19,19 @@ def test_bwd_matches_oracle(cuda, oracle, rows, cols, dt):
     x = rng.standard_normal((rows, cols)).astype(np.float32)
     dy = rng.standard_normal((rows, cols)).astype(np.float32)
     g = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
-    tdt = torch.float32 if dt == "f32" else torch.bfloat16
-    if dt == "bf16":
-        x, dy, g = bf16_round(x), bf16_round(dy), bf16_round(g)
+    tdt = torch_dtype(dt)
+    x, dy, g = round_to(dt, x), round_to(dt, dy), round_to(dt, g)
     wdx, wdg, wdb = oracle.layer_norm_bwd(dy, x, g)
     dx, dg, db = K.layer_norm_bwd_dispatch(torch.from_numpy(dy).to(cuda).to(tdt), torch.from_numpy(x).to(cuda).to(tdt),
                                            torch.from_numpy(g).to(cuda).to(tdt))
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    tol = tol_of(dt)
     assert rel_err(dx.float().cpu().numpy(), wdx) <= tol
     assert rel_err(dg.float().cpu().numpy(), wdg) <= tol
     assert rel_err(db.float().cpu().numpy(), wdb) <= tol
 
 
 @pytest.mark.parametrize("rows,cols", SHAPES)
-@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 def test_fwd_matches_oracle(cuda, oracle, rows, cols, dt):
     import torch
     from mograd_b200 import dispatch as K
@@ -41,13 +40,12 @@ def test_fwd_matches_oracle(cuda, oracle, rows, cols, dt):
     x = (rng.standard_normal((rows, cols)) * 1.5 + 0.3).astype(np.float32)
     g = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
     b = (0.1 * rng.standard_normal(cols)).astype(np.float32)
-    tdt = torch.float32 if dt == "f32" else torch.bfloat16
-    if dt == "bf16":
-        x, g, b = bf16_round(x), bf16_round(g), bf16_round(b)
+    tdt = torch_dtype(dt)
+    x, g, b = round_to(dt, x), round_to(dt, g), round_to(dt, b)
     wy, wmean, wrstd = oracle.layer_norm_fwd(x, g, b)
     y, mean, rstd = K.layer_norm_fwd_dispatch(torch.from_numpy(x).to(cuda).to(tdt), torch.from_numpy(g).to(cuda).to(tdt),
                                               torch.from_numpy(b).to(cuda).to(tdt), save_stats=True)
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    tol = tol_of(dt)
     assert rel_err(y.float().cpu().numpy(), wy) <= tol
     assert rel_err(mean.cpu().numpy(), wmean) <= 1e-4 + (0 if dt == "f32" else 1e-3)
     assert rel_err(rstd.cpu().numpy(), wrstd) <= 1e-4
@@ -108,7 +106,7 @@ def test_full_size_properties(cuda, oracle):
 
 
 @pytest.mark.parametrize("rows,cols", [(300, 768), (65, 4096), (9, 37)])
-@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 def test_bwd_with_residual_gradient(cuda, oracle, rows, cols, dt):
     """dx = layer_norm_bwd(...) + dx_residual, in place on the residual buffer."""
     import torch
@@ -117,21 +115,20 @@ def test_bwd_with_residual_gradient(cuda, oracle, rows, cols, dt):
     rng = np.random.default_rng(rows + cols)
     x, dy, res = (rng.standard_normal((rows, cols)).astype(np.float32) for _ in range(3))
     g = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
-    tdt = torch.float32 if dt == "f32" else torch.bfloat16
-    if dt == "bf16":
-        x, dy, res, g = (bf16_round(t) for t in (x, dy, res, g))
+    tdt = torch_dtype(dt)
+    x, dy, res, g = (round_to(dt, t) for t in (x, dy, res, g))
     wdx, wdg, wdb = oracle.layer_norm_bwd(dy, x, g)
     dev = lambda t: torch.from_numpy(t).to(cuda).to(tdt)
     rbuf = dev(res)
     dx, dg, db = K.layer_norm_bwd_dispatch(dev(dy), dev(x), dev(g), dx_out=rbuf, dx_residual=rbuf)
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    tol = tol_of(dt)
     assert dx.data_ptr() == rbuf.data_ptr()
     assert rel_err(dx.float().cpu().numpy(), wdx + res) <= tol
     assert rel_err(dg.float().cpu().numpy(), wdg) <= tol and rel_err(db.float().cpu().numpy(), wdb) <= tol
 
 
 @pytest.mark.parametrize("rows,cols", [(300, 768), (65, 4096), (9, 37), (40, 16384)])
-@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 def test_bwd_in_place_on_dy(cuda, oracle, rows, cols, dt):
     """dx may be written over dy (the train-step runner does so): a row's dy is read before its dx is stored."""
     import torch
@@ -140,14 +137,13 @@ def test_bwd_in_place_on_dy(cuda, oracle, rows, cols, dt):
     rng = np.random.default_rng(rows * 7 + cols)
     x, dy = (rng.standard_normal((rows, cols)).astype(np.float32) for _ in range(2))
     g = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
-    tdt = torch.float32 if dt == "f32" else torch.bfloat16
-    if dt == "bf16":
-        x, dy, g = (bf16_round(t) for t in (x, dy, g))
+    tdt = torch_dtype(dt)
+    x, dy, g = (round_to(dt, t) for t in (x, dy, g))
     wdx, wdg, wdb = oracle.layer_norm_bwd(dy, x, g)
     dev = lambda t: torch.from_numpy(t).to(cuda).to(tdt)
     buf = dev(dy)
     dx, dg, db = K.layer_norm_bwd_dispatch(buf, dev(x), dev(g), dx_out=buf)
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    tol = tol_of(dt)
     assert dx.data_ptr() == buf.data_ptr()
     assert rel_err(dx.float().cpu().numpy(), wdx) <= tol
     assert rel_err(dg.float().cpu().numpy(), wdg) <= tol and rel_err(db.float().cpu().numpy(), wdb) <= tol

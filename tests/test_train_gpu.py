@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err
+from conftest import TOL_BF16, TOL_F16, TOL_F32, bf16_round, rel_err, round_to
 
 pytestmark = pytest.mark.gpu
 
@@ -121,5 +121,34 @@ def test_transformer_bf16_step_matches_oracle(cuda, oracle):
         err = rel_err(got, g64[name])
         baseline = rel_err(g16[name], g64[name])
         if err > 2.0 * baseline + TOL_BF16:
+            bad[name] = (err, baseline)
+    assert not bad, bad
+
+
+def test_transformer_f16_step_matches_oracle(cuda, oracle):
+    """The same reduced char-transformer in float16 storage (the half type mograd's buffers carry today): tensor-core
+    GEMMs and attention with fp16 operands.  Same relative gate, with the float16 floor of 8e-3."""
+    import torch
+    from mograd_b200.train import TinyTransformer
+    from oracle import ref_model
+
+    cfg = dict(vocab=65, d=128, dff=512, L=2, H=2, B=2, S=256)
+    m = TinyTransformer(cfg["vocab"], cfg["d"], cfg["dff"], cfg["L"], cfg["H"], cfg["B"], cfg["S"], dtype=torch.float16,
+                        device=cuda, seed=3, init_std=0.05)
+    rng = np.random.default_rng(5)
+    tok = rng.integers(0, cfg["vocab"], (cfg["B"], cfg["S"])).astype(np.int64)
+    tgt = rng.integers(0, cfg["vocab"], (cfg["B"], cfg["S"])).astype(np.int64)
+    p0 = _params_np(m)
+    rf = lambda x: round_to("f16", x)
+    loss64, g64 = ref_model.transformer_step(p0, tok, tgt, cfg["L"], cfg["H"])
+    loss16, g16 = ref_model.transformer_step(p0, tok, tgt, cfg["L"], cfg["H"], round_fn=rf)
+    loss = m.step(torch.from_numpy(tok).pin_memory(), torch.from_numpy(tgt).pin_memory())
+    assert abs(loss - loss64) <= TOL_F16 * abs(loss64)
+    bad = {}
+    for name in g64:
+        got = m.store.G[name].float().cpu().numpy()
+        err = rel_err(got, g64[name])
+        baseline = rel_err(g16[name], g64[name])
+        if err > 2.0 * baseline + TOL_F16:
             bad[name] = (err, baseline)
     assert not bad, bad

@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err
+from conftest import TOL_BF16, TOL_F32, bf16_round, rel_err, round_to, tol_of, torch_dtype
 
 pytestmark = pytest.mark.gpu
 
@@ -15,20 +15,19 @@ def _mk(rng, N, C, sigma=2.0):
 
 @pytest.mark.parametrize("N,C", [(4, 10), (8, 5), (128, 10), (2048, 10), (1000, 65), (37, 2048), (16, 50304), (5, 4099),
                                  (449, 16384), (301, 50304), (1, 32768)])  # the last three: several rows per persistent CTA
-@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 def test_fused_index_matches_oracle(cuda, oracle, N, C, dt):
     import torch
     from mograd_b200 import dispatch as K
 
     rng = np.random.default_rng(N * 7919 + C)
     x, idx = _mk(rng, N, C)
-    tdt = torch.float32 if dt == "f32" else torch.bfloat16
-    if dt == "bf16":
-        x = bf16_round(x)
+    tdt = torch_dtype(dt)
+    x = round_to(dt, x)
     want_loss, want_d, _ = oracle.cross_entropy_index(x, idx, upstream=0.5)
     xd = torch.from_numpy(x).to(cuda).to(tdt)
     loss, d = K.softmax_xent_fwd_bwd(xd, torch.from_numpy(idx).to(cuda), upstream=0.5)
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    tol = tol_of(dt)
     assert abs(loss.item() - want_loss) <= 1e-4 * max(1.0, abs(want_loss))
     assert rel_err(d.float().cpu().numpy(), want_d) <= tol
     # gradient rows sum to zero (tests/test_grad.mojo:432-446)
@@ -37,7 +36,7 @@ def test_fused_index_matches_oracle(cuda, oracle, N, C, dt):
 
 
 @pytest.mark.parametrize("N,C", [(4, 10), (2, 4), (64, 65), (9, 3001)])
-@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
 def test_dense_label_entry_points(cuda, oracle, N, C, dt):
     import torch
     from mograd_b200 import dispatch as K
@@ -46,16 +45,15 @@ def test_dense_label_entry_points(cuda, oracle, N, C, dt):
     x = rng.standard_normal((N, C)).astype(np.float32)
     lab = rng.random((N, C)).astype(np.float32)
     lab /= lab.sum(axis=1, keepdims=True)
-    tdt = torch.float32 if dt == "f32" else torch.bfloat16
-    if dt == "bf16":
-        x, lab = bf16_round(x), bf16_round(lab)
+    tdt = torch_dtype(dt)
+    x, lab = round_to(dt, x), round_to(dt, lab)
     want_loss, want_d = oracle.cross_entropy_dense(x, lab, upstream=2.0)
     xd = torch.from_numpy(x).to(cuda).to(tdt)
     ld = torch.from_numpy(lab).to(cuda).to(tdt)
     loss = K.cross_entropy(xd, ld)
     up = torch.full((1,), 2.0, dtype=tdt, device=cuda)
     d = K.cross_entropy_grad(up, xd, ld)
-    tol = TOL_F32 if dt == "f32" else TOL_BF16
+    tol = tol_of(dt)
     assert abs(loss.float().item() - want_loss) <= tol * max(1.0, abs(want_loss))
     assert rel_err(d.float().cpu().numpy(), want_d) <= tol
 
