@@ -213,8 +213,12 @@ int mograd_b200_softmax_xent_fwd_bwd(const void* logits, const int64_t* labels, 
  * (B,H,S,S) tensor of `dtype`, read only when has_bias != 0; causal and
  * has_bias together are rejected as in the reference (__init__.mojo:
  * 868-873).  1 <= D <= 512 (attention/dispatch.mojo:28-29).
- * bf16, D in {64,128}, no bias: tcgen05 kernel; everything else: CUDA-core
- * kernel.
+ * bf16 or float16 with D in {64,128} (16-byte aligned tensors): tcgen05
+ * kernels, with or without the additive mask (the mask tile is added to the
+ * scores in registers before the exponentials, in the forward and in the
+ * backward kernel, as the reference's fused half kernels do,
+ * attention/nvidia_bwd.mojo:1061-1111); float32 and other head sizes:
+ * CUDA-core kernels.
  * ---------------------------------------------------------------------- */
 int mograd_b200_flash_attn_fwd(const void* q, const void* k, const void* v, const void* mask, void* dst,
                                float* lse, int64_t B, int64_t S, int64_t H, int64_t D, float scale, int causal,

@@ -29,15 +29,16 @@ int generic_bwd(const void* dy, const void* q, const void* k, const void* v, con
                 const float* delta, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale, int causal,
                 int has_bias, const Layouts& lay, cudaStream_t st);
 
-// tcgen05 kernels: bf16 or fp16 storage (f16 != 0), D in {64, 128}, no bias, 16-byte aligned tensors.
-bool tc_supported(int D, int has_bias, const Layouts& lay, const void* const* ptrs, int nptrs);
+// tcgen05 kernels: bf16 or fp16 storage (f16 != 0), D in {64, 128}, 16-byte aligned tensors; bias: the additive
+// (B, H, S, S) mask in the storage type, or nullptr.
+bool tc_supported(int D, const Layouts& lay, const void* const* ptrs, int nptrs);
 int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, int B, int S, int H, int D, float scale,
-           int causal, int f16, const Layouts& lay, cudaStream_t st);
+           int causal, int f16, const void* bias, const Layouts& lay, cudaStream_t st);
 // dq_acc: fp32 (B,S,H,D) accumulator; zero-filled by the callee unless acc_zeroed says an earlier kernel on the
 // stream has done it.
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
            float* dq_acc, bool acc_zeroed, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale,
-           int causal, int f16, const Layouts& lay, cudaStream_t st);
+           int causal, int f16, const void* bias, const Layouts& lay, cudaStream_t st);
 
 }  // namespace attn
 }  // namespace mgb

@@ -1,5 +1,5 @@
 // Attention entry points: argument checks and routing between the tcgen05
-// kernels (bf16 / fp16, D = 64 / 128, no bias) and the CUDA-core kernels (the rest).
+// kernels (bf16 / fp16, D = 64 / 128, with or without an additive mask) and the CUDA-core kernels (the rest).
 #include "attn.cuh"
 #include "common.cuh"
 
@@ -47,8 +47,8 @@ MGB_EXPORT int mograd_b200_flash_attn_fwd_ex(const void* q, const void* k, const
   if (dtype == MGB_F32)
     return attn::generic_fwd<float>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, lay, st);
   const void* ptrs[] = {q, k, v, dst};
-  if (attn::tc_supported(d, has_bias, lay, ptrs, 4))
-    return attn::tc_fwd(q, k, v, dst, lse, b, s, h, d, scale, causal, dtype == MGB_F16, lay, st);
+  if (attn::tc_supported(d, lay, ptrs, 4))
+    return attn::tc_fwd(q, k, v, dst, lse, b, s, h, d, scale, causal, dtype == MGB_F16, has_bias ? mask : nullptr, lay, st);
   if (dtype == MGB_F16)
     return attn::generic_fwd<__half>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, lay, st);
   return attn::generic_fwd<__nv_bfloat16>(q, k, v, mask, dst, lse, b, s, h, d, scale, causal, has_bias, lay, st);
@@ -93,7 +93,7 @@ MGB_EXPORT int mograd_b200_flash_attn_bwd_ex(const void* dy, const void* o, cons
                                     st);
   }
   const void* ptrs[] = {dy, q, k, v, dq, dk, dv};
-  const bool tc = attn::tc_supported(d, has_bias, lay, ptrs, 7);
+  const bool tc = attn::tc_supported(d, lay, ptrs, 7);
   float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes(B, S, H));
   bool acc_zeroed = false;
   const bool f16 = dtype == MGB_F16;
@@ -101,7 +101,8 @@ MGB_EXPORT int mograd_b200_flash_attn_bwd_ex(const void* dy, const void* o, cons
            : attn::launch_delta<__nv_bfloat16>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st);
   if (rc != MGB_OK) return rc;
   if (tc)
-    return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, acc_zeroed, dq, dk, dv, b, s, h, d, scale, causal, f16, lay, st);
+    return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, acc_zeroed, dq, dk, dv, b, s, h, d, scale, causal, f16,
+                        has_bias ? mask : nullptr, lay, st);
   if (f16)
     return attn::generic_bwd<__half>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal, has_bias, lay,
                                      st);

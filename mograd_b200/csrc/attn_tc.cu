@@ -86,8 +86,36 @@ struct AttnParams {
   int causal;
   int64_t ld_dqkv;  // elements between consecutive tokens of dK / dV
   int o_bshd;       // layout of O (forward output)
+  const bf16* bias;  // additive mask (B, H, S, S) in the storage type, or nullptr
+  float inv_scale;   // 1 / scale: the mask is folded into the raw scores as bias / scale
+  int bias_vec;      // mask rows take 16-byte loads (S a multiple of 8, aligned base)
   int* status;
 };
+
+// Additive mask: v[e] += bias[row][col0 + e] / scale for the N raw scores (Q K^T, before the softmax scale) of one
+// query row held by this thread, so that everything downstream (scale, running maximum, exponentials) stays as in
+// the unmasked kernels.  bias_row points at the first element of this thread's row of the (B, H, S, S) mask.
+template <typename T, int N>
+__device__ __forceinline__ void add_bias_row(uint32_t (&v)[N], const bf16* bias_row, int col0, int S, bool row_ok,
+                                             float inv_scale, int vec) {
+  if (!row_ok) return;
+  if (vec) {
+#pragma unroll
+    for (int e = 0; e < N; e += 8) {
+      if (col0 + e < S) {  // S is a multiple of 8 here: the whole chunk is inside the row
+        float b[8];
+        load_vec(reinterpret_cast<const T*>(bias_row + col0 + e), b);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[e + u] = __float_as_uint(fmaf(b[u], inv_scale, __uint_as_float(v[e + u])));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < N; ++e)
+      if (col0 + e < S)
+        v[e] = __float_as_uint(fmaf(to_f32(*reinterpret_cast<const T*>(bias_row + col0 + e)), inv_scale, __uint_as_float(v[e])));
+  }
+}
 
 // ============================================================== backward
 // Schedule of one CTA (key tile j), steady state of query tile i:
@@ -126,7 +154,7 @@ struct BwdCfg {
   static constexpr int THREADS = 608;  // TMA warp, MMA warp, 16 compute warps, dQ reduction warp
 };
 
-template <int D, typename T>
+template <int D, typename T, bool BIAS>
 __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -413,6 +441,9 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sfree);  // S and dP columns may be overwritten
+      if constexpr (BIAS)
+        add_bias_row<T, 32>(sv, p.bias + (static_cast<int64_t>(bh) * p.S + (vq ? qrow : 0)) * p.S, j * 128 + col0, p.S, vq,
+                            p.inv_scale, p.bias_vec);
       uint32_t pk[16], dk[16];
       if (!masked) {
 #pragma unroll
@@ -549,7 +580,7 @@ struct Fwd64Cfg {
   static constexpr int THREADS = 192;
 };
 
-template <typename T>
+template <typename T, bool BIAS>
 __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
     attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -685,6 +716,9 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sr);
+      if constexpr (BIAS)
+        add_bias_row<T, 128>(v, p.bias + (static_cast<int64_t>(bh) * p.S + (qrow < p.S ? qrow : 0)) * p.S, jt * 128, p.S,
+                             qrow < p.S, p.inv_scale, p.bias_vec);
       const bool diag = p.causal && (jt == i);
       if (diag || (jt * 128 + 128 > p.S)) {
 #pragma unroll
@@ -802,7 +836,7 @@ struct Fwd128Cfg {
   static constexpr int THREADS = 320;  // TMA, MMA, 4 softmax warps per query tile
 };
 
-template <typename T>
+template <typename T, bool BIAS>
 __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
     attn_fwd_tc128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                             const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -967,6 +1001,9 @@ __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sr(t));
+      if constexpr (BIAS)
+        add_bias_row<T, 128>(v, p.bias + (static_cast<int64_t>(bh) * p.S + (qrow < p.S ? qrow : 0)) * p.S, jt * 128, p.S,
+                             qrow < p.S, p.inv_scale, p.bias_vec);
       const bool diag = p.causal && (jt == i);
       if (diag || (jt * 128 + 128 > p.S)) {
 #pragma unroll
@@ -1107,7 +1144,7 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
     const uint32_t box[4] = {32, 1, 128, 1};
     if (!encode_tmap_f32(&mdq, p.dq_acc, 4, dims, strides, box)) return MGB_ECUDA;
   }
-  auto kern = attn_bwd_tc_kernel<D, T>;
+  auto kern = p.bias ? attn_bwd_tc_kernel<D, T, true> : attn_bwd_tc_kernel<D, T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
@@ -1122,7 +1159,7 @@ int run_fwd128x2(const void* q, const void* k, const void* v, AttnParams p, int6
   if (!map_bshd(&mq, q, p.B, p.S, p.H, 128, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 128, ld_qkv) ||
       !map_bshd(&mv, v, p.B, p.S, p.H, 128, ld_qkv))
     return MGB_ECUDA;
-  auto kern = attn_fwd_tc128x2_kernel<T>;
+  auto kern = p.bias ? attn_fwd_tc128x2_kernel<T, true> : attn_fwd_tc128x2_kernel<T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   const int nq = (p.S + 127) / 128;
@@ -1138,7 +1175,7 @@ int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t
   if (!map_bshd(&mq, q, p.B, p.S, p.H, 64, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 64, ld_qkv) ||
       !map_bshd(&mv, v, p.B, p.S, p.H, 64, ld_qkv))
     return MGB_ECUDA;
-  auto kern = attn_fwd_tc64_kernel<T>;
+  auto kern = p.bias ? attn_fwd_tc64_kernel<T, true> : attn_fwd_tc64_kernel<T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
@@ -1146,10 +1183,16 @@ int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t
   return check_launch("attn_fwd_tc64_kernel");
 }
 
+void set_bias(AttnParams& p, const void* bias, int S, float scale) {
+  p.bias = static_cast<const bf16*>(bias);
+  p.inv_scale = scale != 0.f ? 1.f / scale : 0.f;
+  p.bias_vec = (S % 8 == 0) && aligned16(bias);
+}
+
 }  // namespace
 
-bool tc_supported(int D, int has_bias, const Layouts& lay, const void* const* ptrs, int nptrs) {
-  if (has_bias || (D != 64 && D != 128)) return false;
+bool tc_supported(int D, const Layouts& lay, const void* const* ptrs, int nptrs) {
+  if (D != 64 && D != 128) return false;
   if (lay.ld_qkv % 8 != 0 || lay.ld_dqkv % 8 != 0) return false;
   for (int i = 0; i < nptrs; ++i)
     if (!aligned16(ptrs[i])) return false;
@@ -1157,8 +1200,9 @@ bool tc_supported(int D, int has_bias, const Layouts& lay, const void* const* pt
 }
 
 int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, int B, int S, int H, int D, float scale,
-           int causal, int f16, const Layouts& lay, cudaStream_t st) {
+           int causal, int f16, const void* bias, const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
+  set_bias(p, bias, S, scale);
   p.out = static_cast<bf16*>(dst);
   p.lse_out = lse;
   p.B = B, p.S = S, p.H = H, p.scale = scale, p.causal = causal;
@@ -1172,8 +1216,9 @@ int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, i
 
 int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
            float* dq_acc, bool acc_zeroed, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale,
-           int causal, int f16, const Layouts& lay, cudaStream_t st) {
+           int causal, int f16, const void* bias, const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
+  set_bias(p, bias, S, scale);
   p.lse = lse;
   p.delta = delta;
   p.dq_acc = dq_acc;

@@ -102,6 +102,22 @@ def test_additive_bias_path(cuda, oracle):
     assert rel_err(f(dk), wdk) <= TOL_F32 and rel_err(f(dv), wdv) <= TOL_F32
 
 
+@pytest.mark.parametrize("B,S,H,D", [(1, 256, 2, 64), (2, 200, 1, 128), (1, 203, 2, 64), (1, 384, 1, 128)])
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_additive_bias_on_tensor_cores(cuda, oracle, B, S, H, D, dt):
+    """A dense (B, H, S, S) additive mask with 16-bit storage and D in {64, 128} runs on the tcgen05 kernels
+    (forward and backward); S = 203 takes the unaligned mask loads."""
+    q, k, v, dy = _mk(B, S, H, D, dt, 11 + S)
+    mask = round_to(dt, 2.0 * np.random.default_rng(S).standard_normal((B, H, S, S)).astype(np.float32))
+    scale = 1 / math.sqrt(D)
+    wo, wlse = oracle.sdpa_fwd(q, k, v, scale, False, mask=mask)
+    wdq, wdk, wdv = oracle.sdpa_bwd(q, k, v, dy, scale, False, mask=mask)
+    o, lse, dq, dk, dv = _run(cuda, q, k, v, dy, dt, False, mask=mask)
+    tol = tol_of(dt)
+    assert rel_err(o, wo) <= tol and rel_err(lse, wlse) <= 2e-3
+    assert rel_err(dq, wdq) <= tol and rel_err(dk, wdk) <= tol and rel_err(dv, wdv) <= tol
+
+
 def test_causal_and_bias_together_rejected(cuda):
     import torch
     from mograd_b200 import _lib
