@@ -15,13 +15,10 @@ struct Layouts {
 };
 
 // delta[(b,h,s)] = sum_d O[.,d] * dO[.,d].
-// zero (optional): fp32 array of B*S*H*D elements cleared by the same kernel when it can; *zeroed says whether it was.
-// Padded form for the tensor-core backward (lse2_pad != nullptr; needs the vectorised kernel, i.e. 16-byte aligned
-// O / dO and D a power of two): every head gets Spad = S rounded up to 128 entries in delta and in
-// lse2_pad = lse * log2(e); entries past S are 0 and +inf.
 template <typename T>
+// zero (optional): fp32 array of B*S*H*D elements cleared by the same kernel when it can; *zeroed says whether it was
 int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, float* zero,
-                 bool* zeroed, cudaStream_t st, const float* lse = nullptr, float* lse2_pad = nullptr);
+                 bool* zeroed, cudaStream_t st);
 
 // CUDA-core kernels (any D <= 512, optional additive bias).
 template <typename T>
@@ -39,8 +36,7 @@ int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, i
            int causal, int f16, const void* bias, const Layouts& lay, cudaStream_t st);
 // dq_acc: fp32 (B,S,H,D) accumulator; zero-filled by the callee unless acc_zeroed says an earlier kernel on the
 // stream has done it.
-// lse2_pad / delta_pad: the padded per-query statistics launch_delta writes.
-int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse2_pad, const float* delta_pad,
+int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
            float* dq_acc, bool acc_zeroed, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale,
            int causal, int f16, const void* bias, const Layouts& lay, cudaStream_t st);
 

@@ -18,10 +18,7 @@ int check_attn(const char* who, int64_t B, int64_t S, int64_t H, int64_t D, int 
   return MGB_OK;
 }
 
-// per-query statistics, padded per head to whole 128-row tiles (the tensor-core backward reads them tile by tile)
-size_t delta_bytes(int64_t B, int64_t S, int64_t H) {
-  return round_up(static_cast<size_t>(B * H * ((S + 127) / 128 * 128)) * sizeof(float), 256);
-}
+size_t delta_bytes(int64_t B, int64_t S, int64_t H) { return round_up(static_cast<size_t>(B * H * S) * sizeof(float), 256); }
 size_t dq_acc_bytes(int64_t B, int64_t S, int64_t H, int64_t D) {
   return round_up(static_cast<size_t>(B * S * H * D) * sizeof(float), 256);
 }
@@ -67,7 +64,7 @@ MGB_EXPORT int mograd_b200_flash_attn_fwd(const void* q, const void* k, const vo
 MGB_EXPORT size_t mograd_b200_flash_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype) {
   if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return 0;
   size_t n = delta_bytes(B, S, H);
-  if (dtype != MGB_F32 && (D == 64 || D == 128)) n += delta_bytes(B, S, H) + dq_acc_bytes(B, S, H, D);  // + lse2
+  if (dtype != MGB_F32 && (D == 64 || D == 128)) n += dq_acc_bytes(B, S, H, D);
   return n;
 }
 
@@ -95,19 +92,16 @@ MGB_EXPORT int mograd_b200_flash_attn_bwd_ex(const void* dy, const void* o, cons
     return attn::generic_bwd<float>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal, has_bias, lay,
                                     st);
   }
-  const void* ptrs[] = {dy, o, q, k, v, dq, dk, dv};
-  const bool tc = attn::tc_supported(d, lay, ptrs, 8);
-  float* lse2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes(B, S, H));
-  float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + 2 * delta_bytes(B, S, H));
+  const void* ptrs[] = {dy, q, k, v, dq, dk, dv};
+  const bool tc = attn::tc_supported(d, lay, ptrs, 7);
+  float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + delta_bytes(B, S, H));
   bool acc_zeroed = false;
   const bool f16 = dtype == MGB_F16;
-  rc = f16 ? attn::launch_delta<__half>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st, lse,
-                                        tc ? lse2 : nullptr)
-           : attn::launch_delta<__nv_bfloat16>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st,
-                                               lse, tc ? lse2 : nullptr);
+  rc = f16 ? attn::launch_delta<__half>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st)
+           : attn::launch_delta<__nv_bfloat16>(o, dy, delta, b, s, h, d, o_layout, tc ? dq_acc : nullptr, &acc_zeroed, st);
   if (rc != MGB_OK) return rc;
   if (tc)
-    return attn::tc_bwd(dy, q, k, v, lse2, delta, dq_acc, acc_zeroed, dq, dk, dv, b, s, h, d, scale, causal, f16,
+    return attn::tc_bwd(dy, q, k, v, lse, delta, dq_acc, acc_zeroed, dq, dk, dv, b, s, h, d, scale, causal, f16,
                         has_bias ? mask : nullptr, lay, st);
   if (f16)
     return attn::generic_bwd<__half>(dy, q, k, v, mask, lse, delta, dq, dk, dv, b, s, h, d, scale, causal, has_bias, lay,

@@ -247,8 +247,7 @@ __global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ o, con
 template <typename T>
 __global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o, const T* __restrict__ dy,
                                                         float* __restrict__ delta, int64_t rows, int S, int H, int D,
-                                                        int o_bshd, float* __restrict__ zero,
-                                                        const float* __restrict__ lse, float* __restrict__ lse2_pad) {
+                                                        int o_bshd, float* __restrict__ zero) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int V = Vec<T>::N;
@@ -259,10 +258,9 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o,
   const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   const int64_t row = warp_global * rows_per_warp + sub;
   float acc = 0.f;
-  int s = 0, bh = 0;
   if (row < rows) {
-    s = static_cast<int>(row % S);
-    bh = static_cast<int>(row / S);
+    const int s = static_cast<int>(row % S);
+    const int bh = static_cast<int>(row / S);
     const int64_t off = o_row_off(o_bshd, bh / H, bh % H, s, S, H, D) + part * V;
     float a[V], b[V];
     load_vec(o + off, a);
@@ -271,23 +269,7 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o,
     for (int e = 0; e < V; ++e) acc = fmaf(a[e], b[e], acc);
   }
   for (int ofs = lanes_per_row >> 1; ofs > 0; ofs >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, ofs);
-  if (row < rows && part == 0) {
-    if (lse2_pad != nullptr) {
-      // per-head padded layout for the tensor-core backward: Spad entries per head, 0 / +inf past S
-      const int Spad = (S + 127) / 128 * 128;
-      const int64_t at = static_cast<int64_t>(bh) * Spad + s;
-      delta[at] = acc;
-      lse2_pad[at] = lse[row] * 1.4426950408889634f;
-      if (s == S - 1) {
-        for (int t = S; t < Spad; ++t) {
-          delta[static_cast<int64_t>(bh) * Spad + t] = 0.f;
-          lse2_pad[static_cast<int64_t>(bh) * Spad + t] = __int_as_float(0x7f800000);
-        }
-      }
-    } else {
-      delta[row] = acc;
-    }
-  }
+  if (row < rows && part == 0) delta[row] = acc;
   // optional: clear an fp32 array with one element per element of O (the dQ accumulator of the tensor-core
   // backward), V floats per thread, instead of a separate fill pass
   if (zero != nullptr && row < rows) {
@@ -299,7 +281,7 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o,
 
 template <typename T>
 int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int H, int D, int o_bshd, float* zero,
-                 bool* zeroed, cudaStream_t st, const float* lse, float* lse2_pad) {
+                 bool* zeroed, cudaStream_t st) {
   if (zeroed) *zeroed = false;
   const int64_t rows = static_cast<int64_t>(B) * H * S;
   constexpr int V = Vec<T>::N;
@@ -308,22 +290,18 @@ int launch_delta(const void* o, const void* dy, float* delta, int B, int S, int 
     const int rows_per_block = 8 * (32 / lpr);
     launch_pdl(delta_vec_kernel<T>, dim3(static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block)), dim3(256), 0, st,
                static_cast<const T*>(o), static_cast<const T*>(dy), delta, static_cast<int64_t>(rows), S, H, D, o_bshd,
-               aligned16(zero) ? zero : static_cast<float*>(nullptr), lse, lse2_pad);
+               aligned16(zero) ? zero : static_cast<float*>(nullptr));
     if (zeroed) *zeroed = zero != nullptr && aligned16(zero);
     return check_launch("delta_vec_kernel");
   }
-  MGB_REQUIRE(lse2_pad == nullptr, MGB_EALIGN, "flash_attn_bwd: O / dO must be 16-byte aligned for the tensor-core path");
   delta_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(static_cast<const T*>(o),
                                                                        static_cast<const T*>(dy), delta, rows, S, H, D,
                                                                        o_bshd);
   return check_launch("delta_kernel");
 }
-template int launch_delta<float>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t,
-                                 const float*, float*);
-template int launch_delta<__nv_bfloat16>(const void*, const void*, float*, int, int, int, int, int, float*, bool*,
-                                         cudaStream_t, const float*, float*);
-template int launch_delta<__half>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t,
-                                  const float*, float*);
+template int launch_delta<float>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
+template int launch_delta<__nv_bfloat16>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
+template int launch_delta<__half>(const void*, const void*, float*, int, int, int, int, int, float*, bool*, cudaStream_t);
 
 template <typename T>
 int generic_fwd(const void* q, const void* k, const void* v, const void* mask, void* dst, float* lse, int B, int S,

@@ -75,9 +75,7 @@ __device__ __forceinline__ uint32_t ps_chunk_off(int r, int c8) {
 
 struct AttnParams {
   const float* lse;
-  const float* delta;  // forward kernels: unused; backward: per head padded to Spad entries, 0 past S
-  const float* lse2;   // backward: lse * log2(e), per head padded to Spad entries, +inf past S
-  int Spad;            // S rounded up to whole 128-row tiles
+  const float* delta;
   float* dq_acc;
   bf16* dk;
   bf16* dv;
@@ -120,27 +118,12 @@ __device__ __forceinline__ void add_bias_row(uint32_t (&v)[N], const bf16* bias_
 }
 
 // ============================================================== backward
-// One CTA = one key tile j of one (batch, head), K_j and V_j resident in shared memory, looping over the query
-// tiles i (i >= j when causal).  Scores are formed TRANSPOSED, keys down the TMEM lanes and queries along the
-// columns, so that P^T and dS^T are A operands of the dV and dK products straight out of TMEM:
-//     S^T  = K_j Q_i^T              dP^T = V_j dO_i^T                    (A, B from shared memory -> TMEM)
-//     P^T  = exp2(S^T c - lse2[q])  written as packed 16-bit pairs over its own S^T columns
-//     dS^T = P^T (dP^T - delta[q])  written over its own dP^T columns, and to shared memory for dQ
-//     dV  += P^T dO_i               dK' += dS^T Q_i                      (A from TMEM, B from shared memory)
-//     dQ'_i = dS K_j                                                     (A = the shared dS^T tile read M-major)
-// A thread owns one key row and 32 query columns; the per-query statistics (lse * log2 e and delta, padded per
-// head to whole tiles: +inf / 0 past S, which also masks those queries) arrive in shared memory with the Q tile.
-// The softmax scale is left out of dS and applied once to dK (epilogue) and dQ (final cast).
-//
-// TMEM: A = S^T / P^T (128 columns) | B = dP^T / dS^T (128) | dV (D) | dK (D) | dQ: its own D columns for D = 64;
-// for D = 128 all 512 columns are taken, so dQ is produced over region B once the dK product has read dS^T from
-// it, and the next dP^T waits until the 16 warps have taken dQ out.
-//
-// Order of the tensor-core work in steady state (one thread issues, the pipe executes in order):
-//     [P_i ready] dV_i, S_{i+1} | [dS_i ready] dK_i, dQ_i | [D = 128: dQ_i drained] dP_{i+1}
-// and of the 16 compute warps:
-//     P_i (needs S_i) | dQ_{i-1}: TMEM -> registers -> fp32 staging tile -> TMA tensor reduce | dS_i (needs dP_i)
-// so the exponentials of tile i+1 run under dK_i / dQ_i / dP_{i+1}, and dS_i under dV_i / S_{i+1}.
+// Schedule of one CTA (key tile j), steady state of query tile i:
+//   tensor cores : dP_i | S_{i+1} (as soon as S_i, dP_i sit in registers) | dV_i, dK_i, dQ_i
+//   16 warps     : S_i, dP_i -> registers | exp / dS math -> P, dS in shared | dQ_i -> registers -> reductions
+//   TMA          : Q two tiles ahead (two slots), dO one tile ahead (D = 64: two slots; D = 128: one)
+// dQ_i is written over the dP columns, which are free once dP_i is in registers; the next dP waits for the
+// 16 warps to have read dQ_i out of TMEM (the reductions themselves are issued afterwards and do not block).
 template <int D>
 struct BwdCfg {
   static constexpr int HALVES = D / 64;
@@ -151,36 +134,25 @@ struct BwdCfg {
   static constexpr int OFF_V = TILE_BYTES;
   static constexpr int OFF_Q = 2 * TILE_BYTES;
   static constexpr int OFF_DO = OFF_Q + QST * TILE_BYTES;
-  static constexpr int OFF_DS = OFF_DO + DOST * TILE_BYTES;  // dS^T, [128 key rows][128 query columns], 16-bit
-  // fp32 dQ staging tile (128 x D floats).  D = 64: a buffer of its own.  D = 128: it starts on the dS^T tile (free
-  // once the dQ product has read it; the next dS^T is written after the TMA unit has read the staged dQ).
-  static constexpr int STG_BYTES = 128 * D * 4;
-  static constexpr int OFF_STG = (D == 64) ? OFF_DS + kPsBytes : OFF_DS;
-  static constexpr int OFF_STAT = OFF_STG + STG_BYTES;  // per-query lse2 | delta, QST slots of 512 + 512 bytes
-  static constexpr int OFF_BAR = OFF_STAT + QST * 1024;
-  static constexpr int SLACK = (D == 64) ? 1024 : 768;  // D = 128 fills the 227 KB: the base may be at most 768 B off
-  static constexpr int SMEM = OFF_BAR + 256 + SLACK;
-  static constexpr int COL_A = 0, COL_B = 128, COL_DV = 256, COL_DK = 256 + D;
-  static constexpr int COL_DQ = (D == 64) ? 384 : COL_B;
+  static constexpr int OFF_P = OFF_DO + DOST * TILE_BYTES;
+  static constexpr int OFF_DS = OFF_P + kPsBytes;
+  // D = 64 leaves room in TMEM and shared memory: dQ gets its own columns and its own fp32 staging tile, so the
+  // next tile's dP can start early and the dQ drain runs one tile behind the exp phase (LATE).  D = 128 fills
+  // TMEM: dQ overwrites the dP columns, is staged in the P | dS tiles and drained right away.
+  static constexpr bool LATE = (D == 64);
+  static constexpr int STG_BYTES = LATE ? 128 * D * 4 : 0;
+  static constexpr int OFF_STG = LATE ? OFF_DS + kPsBytes : OFF_P;
+  static constexpr int OFF_BAR = OFF_DS + kPsBytes + STG_BYTES;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
+  static constexpr int COL_DQ = LATE ? 384 : COL_DP;
+  // D = 64 also has 64 columns left for dS as a bf16 TMEM operand: dQ = dS K then reads its A operand from TMEM
+  // instead of shared memory (one operand stream less on the shared-memory port)
+  static constexpr bool DS_TMEM = LATE;
+  static constexpr int COL_DSA = 448;
   static constexpr int TMEM_COLS = 512;
   static constexpr int THREADS = 608;  // TMA warp, MMA warp, 16 compute warps, dQ reduction warp
 };
-
-// Packed 16-bit pair -> two floats.
-template <typename T>
-__device__ __forceinline__ float2 unpack_pair(uint32_t w);
-template <>
-__device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t w) {
-  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-}
-template <>
-__device__ __forceinline__ float2 unpack_pair<__half>(uint32_t w) {
-  return __half22float2(*reinterpret_cast<const __half2*>(&w));
-}
-
-// TMEM column (relative to the region) where the packed A operand of contraction step k (queries 16k .. 16k+15)
-// lives: the thread that owns query columns [32c, 32c+32) writes its 16 packed columns over the first half of them.
-__device__ __forceinline__ constexpr uint32_t packed_col(int k) { return 32u * (k >> 1) + 8u * (k & 1); }
 
 template <int D, typename T, bool BIAS>
 __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
@@ -192,16 +164,16 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
   const uint32_t bar = base + C::OFF_BAR;
-  const uint32_t bar_kv = bar, bar_sfull = bar + 8, bar_dpfull = bar + 16, bar_pready = bar + 24, bar_dsready = bar + 32,
-                 bar_dqf = bar + 40, bar_dqd = bar + 48;
-  auto bar_qf = [&](int s) { return bar + 56 + 8u * s; };
-  auto bar_qe = [&](int s) { return bar + 72 + 8u * s; };
-  auto bar_dof = [&](int s) { return bar + 88 + 8u * s; };
-  auto bar_doe = [&](int s) { return bar + 104 + 8u * s; };
-  const uint32_t bar_stg = bar + 120;   // dQ staging tile has been read by the TMA unit
-  const uint32_t bar_stgf = bar + 128;  // dQ staging tile holds this tile's fp32 dQ
-  const uint32_t tmem_slot = bar + 136;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 136);
+  const uint32_t bar_kv = bar, bar_sdp = bar + 8, bar_sfree = bar + 16, bar_pds = bar + 24, bar_dqf = bar + 32,
+                 bar_dqd = bar + 40;
+  auto bar_qf = [&](int s) { return bar + 48 + 8u * s; };
+  auto bar_qe = [&](int s) { return bar + 64 + 8u * s; };
+  auto bar_dof = [&](int s) { return bar + 80 + 8u * s; };
+  auto bar_doe = [&](int s) { return bar + 96 + 8u * s; };
+  const uint32_t bar_stg = bar + 112;   // dQ staging area (the P | dS tiles) has been read by the TMA unit
+  const uint32_t bar_stgf = bar + 120;  // dQ staging area holds this tile's fp32 dQ
+  const uint32_t tmem_slot = bar + 128;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.x;  // key tile
@@ -211,18 +183,11 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   const int i0 = p.causal ? j : 0;
   const int iters = nq - i0;
 
-  if (base - smem_u32(smem_dyn) > static_cast<uint32_t>(C::SLACK)) {  // uniform: the launch's shared memory is too misaligned
-    if (threadIdx.x == 0) atomicExch(p.status, kErrBwdTma);
-    pdl_launch_dependents();
-    pdl_wait();
-    return;
-  }
   if (threadIdx.x == 0) {
     mbar_init(bar_kv, 1);
-    mbar_init(bar_sfull, 1);
-    mbar_init(bar_dpfull, 1);
-    mbar_init(bar_pready, 16);
-    mbar_init(bar_dsready, 16);
+    mbar_init(bar_sdp, 1);
+    mbar_init(bar_sfree, 16);
+    mbar_init(bar_pds, 16);
     mbar_init(bar_dqf, 1);
     mbar_init(bar_dqd, 16);
     mbar_init(bar_stg, 1);
@@ -261,18 +226,14 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         tma_load_4d(base + C::OFF_V + c * kHalfBytes, &tm_v, bar_kv, c * 64, h, j * 128, b);
       }
       bool ok = true;
-      const float* stat_row = p.lse2 + static_cast<int64_t>(bh) * p.Spad;
-      const float* dlt_row = p.delta + static_cast<int64_t>(bh) * p.Spad;
-      auto load_q = [&](int it) {  // the query tile and its per-query statistics
+      auto load_q = [&](int it) {
         const int s = it % C::QST;
         if (!mbar_wait(bar_qe(s), ((it / C::QST) & 1u) ^ 1u)) return false;
-        mbar_expect_tx(bar_qf(s), C::TILE_BYTES + 1024);
+        mbar_expect_tx(bar_qf(s), C::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < C::HALVES; ++c)
           tma_load_4d(base + C::OFF_Q + s * C::TILE_BYTES + c * kHalfBytes, &tm_q, bar_qf(s), c * 64, h,
                       (i0 + it) * 128, b);
-        bulk_load_1d(base + C::OFF_STAT + s * 1024, stat_row + (i0 + it) * 128, 512, bar_qf(s));
-        bulk_load_1d(base + C::OFF_STAT + s * 1024 + 512, dlt_row + (i0 + it) * 128, 512, bar_qf(s));
         return true;
       };
       auto load_do = [&](int it) {
@@ -289,35 +250,54 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         }
         return true;
       };
-      ok = iters > 0 && load_q(0) && load_do(0);
+      ok = load_q(0) && load_do(0);
       for (int it = 0; it < iters && ok; ++it) {
         if (it + 1 < iters) ok = load_q(it + 1);
         if (ok && it + 1 < iters) ok = load_do(it + 1);
       }
-      if (!ok && iters > 0) atomicExch(p.status, kErrBwdTma);
+      if (!ok) atomicExch(p.status, kErrBwdTma);
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA
     if (lane == 0) {
-      constexpr uint32_t id_ss = umma_idesc_16<T>(128, 128, 0, 0);  // S^T, dP^T: both operands K-major
-      constexpr uint32_t id_ts = umma_idesc_16<T>(128, D, 0, 1);    // dV, dK: A from TMEM, B MN-major
-      constexpr uint32_t id_mm = umma_idesc_16<T>(128, D, 1, 1);    // dQ: dS^T read M-major, K_j MN-major
-      const uint32_t sK = base + C::OFF_K, sV = base + C::OFF_V, sDS = base + C::OFF_DS;
+      constexpr uint32_t id_ss = umma_idesc_16<T>(128, 128, 0, 0);
+      constexpr uint32_t id_mm = umma_idesc_16<T>(128, D, 1, 1);
+      constexpr uint32_t id_km = umma_idesc_16<T>(128, D, 0, 1);
+      const uint32_t sK = base + C::OFF_K, sV = base + C::OFF_V, sP = base + C::OFF_P, sDS = base + C::OFF_DS;
       auto q_tile = [&](int it) { return base + C::OFF_Q + (it % C::QST) * C::TILE_BYTES; };
       auto do_tile = [&](int it) { return base + C::OFF_DO + (it % C::DOST) * C::TILE_BYTES; };
-      const uint64_t dK_k = base_k(sK), dK_mn = base_mn(sK), dV_k = base_k(sV), dDS_mn = base_mn(sDS);
+      const uint64_t dK_k = base_k(sK), dK_mn = base_mn(sK), dV_k = base_k(sV);
+      const uint64_t dP_mn = base_mn(sP), dDS_mn = base_mn(sDS), dDS_k = base_k(sDS);
       auto issue_s = [&](int it) {
         const uint64_t dQ_k = base_k(q_tile(it));
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_A, desc_k(dK_k, k), desc_k(dQ_k, k), id_ss, k > 0);
-        umma_commit(bar_sfull);
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S, desc_k(dQ_k, k), desc_k(dK_k, k), id_ss, k > 0);
       };
       auto issue_dp = [&](int it) {
         const uint64_t dDO_k = base_k(do_tile(it));
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_B, desc_k(dV_k, k), desc_k(dDO_k, k), id_ss, k > 0);
-        umma_commit(bar_dpfull);
+        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_DP, desc_k(dDO_k, k), desc_k(dV_k, k), id_ss, k > 0);
+      };
+      auto issue_grads = [&](int it) {  // dV, dK (accumulating over tiles) and this tile's dQ
+        const uint64_t dQ_mn = base_mn(q_tile(it)), dDO_mn = base_mn(do_tile(it));
+        const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DV, desc_mn(dP_mn, k), desc_mn(dDO_mn, k), id_mm, k > 0 ? 1u : acc);
+        umma_commit(bar_doe(it % C::DOST));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ss(tmem + C::COL_DK, desc_mn(dDS_mn, k), desc_mn(dQ_mn, k), id_mm, k > 0 ? 1u : acc);
+        umma_commit(bar_qe(it % C::QST));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (C::DS_TMEM)
+            umma_ts(tmem + C::COL_DQ, tmem + C::COL_DSA + k * 8, desc_mn(dK_mn, k), id_km, k > 0);
+          else
+            umma_ss(tmem + C::COL_DQ, desc_k(dDS_k, k), desc_mn(dK_mn, k), id_km, k > 0);
+        }
+        umma_commit(bar_dqf);
       };
       auto wait_q = [&](int it) { return mbar_wait(bar_qf(it % C::QST), (it / C::QST) & 1u); };
       auto wait_do = [&](int it) { return mbar_wait(bar_dof(it % C::DOST), (it / C::DOST) & 1u); };
@@ -325,47 +305,55 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       if (ok) {
         tc_fence_after();
         issue_s(0);
-        ok = wait_do(0);
       }
-      if (ok) {
-        tc_fence_after();
-        issue_dp(0);
-      }
-      for (int it = 0; it < iters && ok; ++it) {
-        const uint32_t acc = it > 0 ? 1u : 0u;
-        if (!(ok = mbar_wait(bar_pready, it & 1u))) break;  // P_it sits in region A
-        tc_fence_after();
-        {
-          const uint64_t dDO_mn = base_mn(do_tile(it));
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma_ts(tmem + C::COL_DV, tmem + C::COL_A + packed_col(k), desc_mn(dDO_mn, k), id_ts, k > 0 ? 1u : acc);
-          umma_commit(bar_doe(it % C::DOST));  // dO_it is done with (dP_it was issued earlier)
-        }
-        if (it + 1 < iters) {  // region A is rewritten behind the dV product: the pipe runs in order
-          if (!(ok = wait_q(it + 1))) break;
+      if (C::LATE) {
+        if (ok && (ok = wait_do(0))) {
           tc_fence_after();
-          issue_s(it + 1);
+          issue_dp(0);
+          umma_commit(bar_sdp);
         }
-        if (!(ok = mbar_wait(bar_dsready, it & 1u))) break;  // dS_it sits in region B and in shared memory
-        tc_fence_after();
-        {
-          const uint64_t dQ_mn = base_mn(q_tile(it));
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma_ts(tmem + C::COL_DK, tmem + C::COL_B + packed_col(k), desc_mn(dQ_mn, k), id_ts, k > 0 ? 1u : acc);
-          umma_commit(bar_qe(it % C::QST));
-        }
-        if (D == 64 && it > 0 && !(ok = mbar_wait(bar_dqd, (it - 1) & 1u))) break;  // dQ_{it-1} has left its columns
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(tmem + C::COL_DQ, desc_mn(dDS_mn, k), desc_mn(dK_mn, k), id_mm, k > 0);
-        umma_commit(bar_dqf);
-        if (it + 1 < iters) {
-          if (D == 128 && !(ok = mbar_wait(bar_dqd, it & 1u))) break;  // dQ_it has left region B
-          if (!(ok = wait_do(it + 1))) break;
+        for (int it = 0; it < iters && ok; ++it) {
+          ok = mbar_wait(bar_sfree, it & 1u);  // S_it, dP_it are in registers
+          if (ok && it + 1 < iters) {
+            ok = wait_q(it + 1) && wait_do(it + 1);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(it + 1);
+            issue_dp(it + 1);
+            umma_commit(bar_sdp);
+          }
+          ok = ok && mbar_wait(bar_pds, it & 1u);
+          if (ok && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ_{it-1} has left its columns
+          if (!ok) break;
           tc_fence_after();
-          issue_dp(it + 1);
+          issue_grads(it);
+        }
+      } else {
+        for (int it = 0; it < iters && ok; ++it) {
+          ok = wait_do(it);
+          if (ok && it > 0) ok = mbar_wait(bar_dqd, (it - 1) & 1u);  // dQ_{it-1} has left the dP columns
+          if (!ok) break;
+          tc_fence_after();
+          issue_dp(it);
+          umma_commit(bar_sdp);  // also covers S_it, issued one iteration earlier
+          if (!mbar_wait(bar_sfree, it & 1u)) {
+            ok = false;
+            break;
+          }
+          if (it + 1 < iters) {
+            if (!wait_q(it + 1)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_s(it + 1);  // runs while the 16 warps work on tile it
+          }
+          if (!mbar_wait(bar_pds, it & 1u)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_grads(it);
         }
       }
       if (!ok && iters > 0) atomicExch(p.status, kErrBwdMma);
@@ -392,24 +380,21 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     __syncwarp();
   } else {
     // ------------------------------------------------------------ compute
-    // 16 warps: TMEM lane quarter = warp % 4 (hardware rule); lane r = key row r of the tile; column group cg = 32
-    // of the 128 query columns.
+    // 16 warps: TMEM lane quarter = warp % 4 (hardware rule), column group cg = 32 of the 128 S / dP columns.
+    // The softmax scale is left out of dS here and applied once to dK (epilogue) and dQ (final cast).
     const int cw = warp - 2;
     const int quarter = warp & 3;
     const int cg = cw >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float scale_log2 = p.scale * kLog2e;
-    const int col0 = cg * 32;
-    const int kvrow = j * 128 + r;
-    const bool key_ok = kvrow < p.S;
     constexpr int DC = D / 4;  // dQ / dK / dV columns per warp
     bool ok = true;
-    // dQ of tile t (lane = query row): TMEM -> registers (frees the columns) -> fp32 staging tile in shared memory
-    // as [128 rows][32 floats] boxes with the 128-byte swizzle -> the reduction warp lets the TMA unit add it into
+    // dQ of tile t: TMEM -> registers (frees the columns) -> fp32 staging tile in shared memory as
+    // [128 rows][32 floats] boxes with the 128-byte swizzle -> the reduction warp lets the TMA unit add it into
     // the accumulator (whole 128-byte lines per request; rows past S are clipped by the tensor map).
-    auto drain = [&](int t) -> bool {
-      if (!mbar_wait(bar_dqf, t & 1u)) return false;
+    auto drain = [&](int t, bool wait_ready) -> bool {
+      if (wait_ready && !mbar_wait(bar_dqf, t & 1u)) return false;  // never wait twice on one phase
       tc_fence_after();
       uint32_t v[DC];
       if constexpr (DC == 32) {
@@ -421,7 +406,7 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_dqd);
-      if (t > 0 && !mbar_wait(bar_stg, (t - 1) & 1u)) return false;  // staging tile read by the TMA unit
+      if (C::LATE && t > 0 && !mbar_wait(bar_stg, (t - 1) & 1u)) return false;  // staging tile read by the TMA unit
       constexpr int CH = DC / 4;             // 16-byte chunks this thread owns
       const int box = (cg * DC) / 32;        // which [128][32] box
       const int ch0 = ((cg * DC) % 32) / 4;  // first chunk inside the 128-byte row
@@ -437,95 +422,89 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     };
     for (int it = 0; it < iters && ok; ++it) {
       const int i = i0 + it;
-      const int slot = it % C::QST;
-      const bool diag = p.causal && (i == j);
-      const bool masked = diag || (j * 128 + 128 > p.S);  // uniform over the CTA (queries past S carry lse2 = +inf)
-      // ---- P^T of this tile: needs S^T and the per-query statistics
-      if (!mbar_wait(bar_qf(slot), (it / C::QST) & 1u) || !mbar_wait(bar_sfull, it & 1u)) {
+      const int qrow = i * 128 + r;
+      const bool vq = qrow < p.S;
+      const float lse2 = vq ? p.lse[static_cast<int64_t>(bh) * p.S + qrow] * kLog2e : 0.f;
+      const float dlt = vq ? p.delta[static_cast<int64_t>(bh) * p.S + qrow] : 0.f;
+      if (!mbar_wait(bar_sdp, it & 1u)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const float* lse2s = reinterpret_cast<const float*>(gen + C::OFF_STAT + slot * 1024) + col0;
-      const float* dlts = lse2s + 128;
-      uint32_t pk[16];
-      {
-        uint32_t sv[32];
-        tmem_ld32(tmem + lane_base + C::COL_A + col0, sv);
-        tmem_ld_wait();
-        if constexpr (BIAS) {  // mask element (query, key): one key per thread, queries S elements apart
-          if (key_ok) {
-            const bf16* bcol = p.bias + (static_cast<int64_t>(bh) * p.S + i * 128 + col0) * p.S + kvrow;
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (i * 128 + col0 + e < p.S)
-                sv[e] = __float_as_uint(fmaf(to_f32(*reinterpret_cast<const T*>(bcol + static_cast<int64_t>(e) * p.S)),
-                                             p.inv_scale, __uint_as_float(sv[e])));
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(lse2s + e);
-          float pe[4];
-          pe[0] = ex2(fmaf(__uint_as_float(sv[e]), scale_log2, -l4.x));
-          pe[1] = ex2(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -l4.y));
-          pe[2] = ex2(fmaf(__uint_as_float(sv[e + 2]), scale_log2, -l4.z));
-          pe[3] = ex2(fmaf(__uint_as_float(sv[e + 3]), scale_log2, -l4.w));
-          if (masked) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (!key_ok || (diag && r > col0 + e + u)) pe[u] = 0.f;  // key past S, or key after the query
-          }
-          pk[e >> 1] = pack_pair<T>(pe[0], pe[1]);
-          pk[(e >> 1) + 1] = pack_pair<T>(pe[2], pe[3]);
-        }
-      }
-      tmem_st16(tmem + lane_base + C::COL_A + col0, pk);  // over this thread's own S^T columns
-      tmem_st_wait();
+      const bool diag = p.causal && (i == j);
+      const bool masked = diag || (j * 128 + 128 > p.S) || (i * 128 + 128 > p.S);  // uniform over the CTA
+      const int col0 = cg * 32;
+      uint32_t sv[32], dpv[32];
+      tmem_ld32(tmem + lane_base + C::COL_S + col0, sv);
+      tmem_ld32(tmem + lane_base + C::COL_DP + col0, dpv);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pready);
-      // ---- dQ of the previous tile: its product ran while the exponentials above were computed
-      if (it > 0 && !(ok = drain(it - 1))) break;
-      // ---- dS^T of this tile: needs dP^T
-      if (!mbar_wait(bar_dpfull, it & 1u)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      uint32_t dk[16];
-      {
-        uint32_t dpv[32];
-        tmem_ld32(tmem + lane_base + C::COL_B + col0, dpv);
-        tmem_ld_wait();
+      if (lane == 0) mbar_arrive(bar_sfree);  // S and dP columns may be overwritten
+      if constexpr (BIAS)
+        add_bias_row<T, 32>(sv, p.bias + (static_cast<int64_t>(bh) * p.S + (vq ? qrow : 0)) * p.S, j * 128 + col0, p.S, vq,
+                            p.inv_scale, p.bias_vec);
+      uint32_t pk[16], dk[16];
+      if (!masked) {
+        // packed fp32 pairs: one FMA / ADD / MUL instruction per two elements
+        const float2 c2 = make_float2(scale_log2, scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dlt, -dlt);
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(dlts + e);
-          const float2 p01 = unpack_pair<T>(pk[e >> 1]), p23 = unpack_pair<T>(pk[(e >> 1) + 1]);
-          dk[e >> 1] = pack_pair<T>(p01.x * (__uint_as_float(dpv[e]) - d4.x), p01.y * (__uint_as_float(dpv[e + 1]) - d4.y));
-          dk[(e >> 1) + 1] =
-              pack_pair<T>(p23.x * (__uint_as_float(dpv[e + 2]) - d4.z), p23.y * (__uint_as_float(dpv[e + 3]) - d4.w));
+        for (int e = 0; e < 32; e += 2) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2, nl2);
+          const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+          const float2 ds =
+              __fmul2_rn(pp, __fadd2_rn(make_float2(__uint_as_float(dpv[e]), __uint_as_float(dpv[e + 1])), nd2));
+          pk[e >> 1] = pack_pair<T>(pp.x, pp.y);
+          dk[e >> 1] = pack_pair<T>(ds.x, ds.y);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kvrow = j * 128 + col0 + e + u;
+            const bool keep = vq && kvrow < p.S && (!diag || kvrow <= qrow);
+            const float pe = keep ? ex2(fmaf(__uint_as_float(sv[e + u]), scale_log2, -lse2)) : 0.f;
+            pv[u] = pe;
+            dv[u] = pe * (__uint_as_float(dpv[e + u]) - dlt);
+          }
+          pk[e >> 1] = pack_pair<T>(pv[0], pv[1]);
+          dk[e >> 1] = pack_pair<T>(dv[0], dv[1]);
         }
       }
-      // the shared dS^T tile may be rewritten: D = 64: the dQ product of the previous tile has read it (drain waited
-      // for that product); D = 128: the staged dQ that lies on it has been read by the TMA unit
-      if (D == 128 && it > 0 && !(ok = mbar_wait(bar_stg, (it - 1) & 1u))) break;
+      // P | dS may be rewritten once the previous tile's MMAs have read them (LATE: bar_dqf of that tile;
+      // otherwise: the TMA unit has read the dQ tile that was staged there)
+      if (it > 0) {
+        ok = C::LATE ? mbar_wait(bar_dqf, (it - 1) & 1u) : mbar_wait(bar_stg, (it - 1) & 1u);
+        if (!ok) break;
+      }
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
-        *reinterpret_cast<uint4*>(gen + C::OFF_DS + ps_chunk_off(r, (col0 >> 3) + t)) =
-            make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
-      tmem_st16(tmem + lane_base + C::COL_B + col0, dk);  // over this thread's own dP^T columns
-      tmem_st_wait();
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t off = ps_chunk_off(r, (col0 >> 3) + t);
+        *reinterpret_cast<uint4*>(gen + C::OFF_P + off) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+        *reinterpret_cast<uint4*>(gen + C::OFF_DS + off) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
+      }
+      if (C::DS_TMEM) {  // dS once more as packed bf16 pairs: 16 TMEM columns per 32 key columns
+        tmem_st16(tmem + lane_base + C::COL_DSA + cg * 16, dk);
+        tmem_st_wait();
+      }
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_dsready);
+      if (lane == 0) mbar_arrive(bar_pds);
+      if (C::LATE) {
+        if (it > 0) ok = drain(it - 1, false);  // bar_dqf of tile it-1 was waited for above
+      } else {
+        ok = drain(it, true);
+      }
     }
-    if (ok && iters > 0) ok = drain(iters - 1);
+    if (C::LATE && ok && iters > 0) ok = drain(iters - 1, true);
     if (!ok && lane == 0) atomicExch(p.status, kErrBwdCompute);
-    // dK / dV (lane = key row): every MMA was complete when the last bar_dqf fired
+    // dK / dV: every MMA was complete when the last bar_dqf fired
     if (ok && iters > 0) {
-      const int64_t tok = static_cast<int64_t>(b) * p.S + (key_ok ? kvrow : 0);
+      const int kvrow = j * 128 + r;
+      const int64_t tok = static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0);
       bf16* dk_row = p.dk + tok * p.ld_dqkv + static_cast<int64_t>(h) * D + cg * DC;
       bf16* dv_row = p.dv + tok * p.ld_dqkv + static_cast<int64_t>(h) * D + cg * DC;
       const float sc = p.scale;
@@ -535,7 +514,7 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         tmem_ld16(tmem + lane_base + C::COL_DK + cg * DC + c0, a);
         tmem_ld16(tmem + lane_base + C::COL_DV + cg * DC + c0, c);
         tmem_ld_wait();
-        if (key_ok) {
+        if (kvrow < p.S) {
 #pragma unroll
           for (int e = 0; e < 16; e += 8) {
             uint4 o1, o2;
@@ -1239,14 +1218,13 @@ int tc_fwd(const void* q, const void* k, const void* v, void* dst, float* lse, i
   return D == 64 ? run_fwd64<bf16>(q, k, v, p, lay.ld_qkv, st) : run_fwd128x2<bf16>(q, k, v, p, lay.ld_qkv, st);
 }
 
-int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse2_pad, const float* delta_pad,
+int tc_bwd(const void* dy, const void* q, const void* k, const void* v, const float* lse, const float* delta,
            float* dq_acc, bool acc_zeroed, void* dq, void* dk, void* dv, int B, int S, int H, int D, float scale,
            int causal, int f16, const void* bias, const Layouts& lay, cudaStream_t st) {
   AttnParams p{};
   set_bias(p, bias, S, scale);
-  p.lse2 = lse2_pad;
-  p.delta = delta_pad;
-  p.Spad = (S + 127) / 128 * 128;
+  p.lse = lse;
+  p.delta = delta;
   p.dq_acc = dq_acc;
   p.dk = static_cast<bf16*>(dk);
   p.dv = static_cast<bf16*>(dv);
