@@ -158,7 +158,8 @@ template <int D, typename T, bool BIAS>
 __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                       const __grid_constant__ CUtensorMap tm_dq, const AttnParams p) {
+                       const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
+                       const __grid_constant__ CUtensorMap tm_dv, const AttnParams p) {
   using C = BwdCfg<D>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -501,12 +502,11 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
     }
     if (C::LATE && ok && iters > 0) ok = drain(iters - 1, true);
     if (!ok && lane == 0) atomicExch(p.status, kErrBwdCompute);
-    // dK / dV: every MMA was complete when the last bar_dqf fired
+    // dK / dV: every MMA was complete when the last bar_dqf fired, so the K and V tiles in shared memory are free:
+    // each thread parks its slice of the two accumulators there (16-bit, same swizzled [128][64] boxes the loads
+    // used) and one thread lets the TMA unit write both tiles out, whole 128-byte lines per request, rows past S
+    // clipped by the tensor map.  (Per-thread 16-byte stores to rows 4.6 KB apart cost 9% of the kernel.)
     if (ok && iters > 0) {
-      const int kvrow = j * 128 + r;
-      const int64_t tok = static_cast<int64_t>(b) * p.S + (kvrow < p.S ? kvrow : 0);
-      bf16* dk_row = p.dk + tok * p.ld_dqkv + static_cast<int64_t>(h) * D + cg * DC;
-      bf16* dv_row = p.dv + tok * p.ld_dqkv + static_cast<int64_t>(h) * D + cg * DC;
       const float sc = p.scale;
 #pragma unroll 1
       for (int c0 = 0; c0 < DC; c0 += 16) {
@@ -514,23 +514,33 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
         tmem_ld16(tmem + lane_base + C::COL_DK + cg * DC + c0, a);
         tmem_ld16(tmem + lane_base + C::COL_DV + cg * DC + c0, c);
         tmem_ld_wait();
-        if (kvrow < p.S) {
 #pragma unroll
-          for (int e = 0; e < 16; e += 8) {
-            uint4 o1, o2;
-            o1.x = pack_pair<T>(__uint_as_float(a[e]) * sc, __uint_as_float(a[e + 1]) * sc);
-            o1.y = pack_pair<T>(__uint_as_float(a[e + 2]) * sc, __uint_as_float(a[e + 3]) * sc);
-            o1.z = pack_pair<T>(__uint_as_float(a[e + 4]) * sc, __uint_as_float(a[e + 5]) * sc);
-            o1.w = pack_pair<T>(__uint_as_float(a[e + 6]) * sc, __uint_as_float(a[e + 7]) * sc);
-            o2.x = pack_pair<T>(__uint_as_float(c[e]), __uint_as_float(c[e + 1]));
-            o2.y = pack_pair<T>(__uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
-            o2.z = pack_pair<T>(__uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
-            o2.w = pack_pair<T>(__uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
-            *reinterpret_cast<uint4*>(dk_row + c0 + e) = o1;
-            *reinterpret_cast<uint4*>(dv_row + c0 + e) = o2;
-          }
+        for (int e = 0; e < 16; e += 8) {
+          uint4 o1, o2;
+          o1.x = pack_pair<T>(__uint_as_float(a[e]) * sc, __uint_as_float(a[e + 1]) * sc);
+          o1.y = pack_pair<T>(__uint_as_float(a[e + 2]) * sc, __uint_as_float(a[e + 3]) * sc);
+          o1.z = pack_pair<T>(__uint_as_float(a[e + 4]) * sc, __uint_as_float(a[e + 5]) * sc);
+          o1.w = pack_pair<T>(__uint_as_float(a[e + 6]) * sc, __uint_as_float(a[e + 7]) * sc);
+          o2.x = pack_pair<T>(__uint_as_float(c[e]), __uint_as_float(c[e + 1]));
+          o2.y = pack_pair<T>(__uint_as_float(c[e + 2]), __uint_as_float(c[e + 3]));
+          o2.z = pack_pair<T>(__uint_as_float(c[e + 4]), __uint_as_float(c[e + 5]));
+          o2.w = pack_pair<T>(__uint_as_float(c[e + 6]), __uint_as_float(c[e + 7]));
+          const uint32_t off = ps_chunk_off(r, (cg * DC + c0 + e) >> 3);
+          *reinterpret_cast<uint4*>(gen + C::OFF_K + off) = o1;
+          *reinterpret_cast<uint4*>(gen + C::OFF_V + off) = o2;
         }
       }
+      fence_async_smem();
+    }
+    named_barrier(1, 16 * 32);  // the 16 compute warps (all of them get here, also after a failed wait)
+    if (ok && iters > 0 && warp == 2 && lane == 0) {
+#pragma unroll
+      for (int c = 0; c < C::HALVES; ++c) {
+        tma_store_4d(&tm_dk, base + C::OFF_K + c * kHalfBytes, c * 64, h, j * 128, b);
+        tma_store_4d(&tm_dv, base + C::OFF_V + c * kHalfBytes, c * 64, h, j * 128, b);
+      }
+      bulk_commit();
+      bulk_wait_read0();  // the tiles have been read; the writes themselves complete before the grid does
     }
   }
   tc_fence_before();
@@ -587,7 +597,8 @@ struct Fwd64Cfg {
 template <typename T, bool BIAS>
 __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
     attn_fwd_tc64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                         const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                         const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                         const AttnParams p) {
   using C = Fwd64Cfg;
   constexpr int D = C::D;
   extern __shared__ unsigned char smem_dyn[];
@@ -785,32 +796,40 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
       if (lane == 0) mbar_arrive(bar_pr);
     }
     if (ok && !mbar_wait(bar_pv, (nkv - 1) & 1u)) ok = false;
+    // The normalised output leaves through the TMA unit: every thread parks its row in the Q tile (free once the
+    // last scores were formed; same swizzled box) and one thread stores the tile, whole 128-byte lines per request,
+    // rows past S clipped by the tensor map.
     if (!ok) {
       if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
     } else {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int qr = qrow < p.S ? qrow : 0;
-      bf16* orow = p.out + (p.o_bshd ? ((static_cast<int64_t>(b) * p.S + qr) * p.H + h) * D
-                                     : (static_cast<int64_t>(bh) * p.S + qr) * D);
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 16) {
         uint32_t o[16];
         tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
         tmem_ld_wait();
-        if (qrow < p.S) {
 #pragma unroll
-          for (int e = 0; e < 16; e += 8) {
-            uint4 w;
-            w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-            w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
-            w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
-            w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c0 + e) = w;
-          }
+        for (int e = 0; e < 16; e += 8) {
+          uint4 w;
+          w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+          w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+          w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+          w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+          *reinterpret_cast<uint4*>(gen + C::OFF_Q + ps_chunk_off(r, (c0 + e) >> 3)) = w;
         }
       }
+      fence_async_smem();
       if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
+    }
+    named_barrier(1, 4 * 32);  // the four softmax warps
+    if (ok && warp == 2 && lane == 0) {
+      if (p.o_bshd)
+        tma_store_4d(&tm_o, base + C::OFF_Q, 0, h, i * 128, b);
+      else
+        tma_store_3d(&tm_o, base + C::OFF_Q, 0, i * 128, bh);
+      bulk_commit();
+      bulk_wait_read0();
     }
   }
   tc_fence_before();
@@ -843,7 +862,8 @@ struct Fwd128Cfg {
 template <typename T, bool BIAS>
 __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
     attn_fwd_tc128x2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                            const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                            const AttnParams p) {
   using C = Fwd128Cfg;
   constexpr int D = C::D;
   extern __shared__ unsigned char smem_dyn[];
@@ -1069,32 +1089,43 @@ __global__ void __launch_bounds__(Fwd128Cfg::THREADS, 1)
       if (lane == 0) mbar_arrive(bar_pr(t));
     }
     if (ok && my_nkv > 0 && !mbar_wait(bar_pv(t), (my_nkv - 1) & 1u)) ok = false;
+    // The normalised output leaves through the TMA unit: every thread parks its row in its query tile's Q buffer
+    // (free once the tile's last scores were formed) and one thread per tile stores it.
     if (!ok) {
       if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
     } else if (my_nkv > 0) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int qr = qrow < p.S ? qrow : 0;
-      bf16* orow = p.out + (p.o_bshd ? ((static_cast<int64_t>(b) * p.S + qr) * p.H + h) * D
-                                     : (static_cast<int64_t>(bh) * p.S + qr) * D);
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 16) {
         uint32_t o[16];
         tmem_ld16(tmem + lane_base + col_o + c0, o);
         tmem_ld_wait();
-        if (qrow < p.S) {
 #pragma unroll
-          for (int e = 0; e < 16; e += 8) {
-            uint4 w;
-            w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-            w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
-            w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
-            w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c0 + e) = w;
-          }
+        for (int e = 0; e < 16; e += 8) {
+          uint4 w;
+          w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+          w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+          w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+          w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+          *reinterpret_cast<uint4*>(gen + C::OFF_Q + t * C::TILE_BYTES + ps_chunk_off(r, (c0 + e) >> 3)) = w;
         }
       }
+      fence_async_smem();
       if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
+    }
+    named_barrier(1 + t, 4 * 32);  // the four softmax warps of this query tile
+    if (ok && my_nkv > 0 && (warp & 3) == 2 && lane == 0) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t src = base + C::OFF_Q + t * C::TILE_BYTES + c * kHalfBytes;
+        if (p.o_bshd)
+          tma_store_4d(&tm_o, src, c * 64, h, i * 128, b);
+        else
+          tma_store_3d(&tm_o, src, c * 64, i * 128, bh);
+      }
+      bulk_commit();
+      bulk_wait_read0();
     }
   }
   tc_fence_before();
@@ -1148,11 +1179,14 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
     const uint32_t box[4] = {32, 1, 128, 1};
     if (!encode_tmap_f32(&mdq, p.dq_acc, 4, dims, strides, box)) return MGB_ECUDA;
   }
+  CUtensorMap mdk, mdv;  // dK / dV leave through the TMA unit too
+  if (!map_bshd(&mdk, p.dk, p.B, p.S, p.H, D, p.ld_dqkv) || !map_bshd(&mdv, p.dv, p.B, p.S, p.H, D, p.ld_dqkv))
+    return MGB_ECUDA;
   auto kern = p.bias ? attn_bwd_tc_kernel<D, T, true> : attn_bwd_tc_kernel<D, T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
-  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mdo, mdq, p);
+  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mdo, mdq, mdk, mdv, p);
   return check_launch("attn_bwd_tc_kernel");
 }
 
@@ -1163,12 +1197,16 @@ int run_fwd128x2(const void* q, const void* k, const void* v, AttnParams p, int6
   if (!map_bshd(&mq, q, p.B, p.S, p.H, 128, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 128, ld_qkv) ||
       !map_bshd(&mv, v, p.B, p.S, p.H, 128, ld_qkv))
     return MGB_ECUDA;
+  CUtensorMap mo;
+  if (!(p.o_bshd ? map_bshd(&mo, p.out, p.B, p.S, p.H, 128, static_cast<int64_t>(p.H) * 128)
+                 : map_bhsd(&mo, p.out, p.B, p.S, p.H, 128)))
+    return MGB_ECUDA;
   auto kern = p.bias ? attn_fwd_tc128x2_kernel<T, true> : attn_fwd_tc128x2_kernel<T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   const int nq = (p.S + 127) / 128;
   dim3 grid(static_cast<unsigned>((nq + 1) / 2), static_cast<unsigned>(p.B * p.H));
-  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, p);
+  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mo, p);
   return check_launch("attn_fwd_tc128x2_kernel");
 }
 
@@ -1179,11 +1217,15 @@ int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t
   if (!map_bshd(&mq, q, p.B, p.S, p.H, 64, ld_qkv) || !map_bshd(&mk, k, p.B, p.S, p.H, 64, ld_qkv) ||
       !map_bshd(&mv, v, p.B, p.S, p.H, 64, ld_qkv))
     return MGB_ECUDA;
+  CUtensorMap mo;
+  if (!(p.o_bshd ? map_bshd(&mo, p.out, p.B, p.S, p.H, 64, static_cast<int64_t>(p.H) * 64)
+                 : map_bhsd(&mo, p.out, p.B, p.S, p.H, 64)))
+    return MGB_ECUDA;
   auto kern = p.bias ? attn_fwd_tc64_kernel<T, true> : attn_fwd_tc64_kernel<T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
   dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
-  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, p);
+  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mo, p);
   return check_launch("attn_fwd_tc64_kernel");
 }
 

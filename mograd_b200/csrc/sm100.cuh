@@ -116,6 +116,12 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src,
                "r"(src), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(src), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
 // L2 eviction-priority policies for loads and stores that carry a cache hint.
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t pol;
