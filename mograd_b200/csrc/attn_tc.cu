@@ -573,26 +573,56 @@ __global__ void __launch_bounds__(256) cast_dq_kernel(const float* __restrict__ 
 }
 
 // =============================================================== forward
-// ------------------------------------------------- forward, D = 64: two CTAs per SM
-// With 64-wide heads a query tile needs half the shared memory and TMEM of the D = 128 kernel, so two CTAs fit on
-// an SM and run out of phase: the fill and drain of one (Q/K/V loads, first scores, output epilogue) hide behind
-// the steady state of the other, and their softmax phases interleave on the MUFU pipe.  To make them fit, a CTA is
-// 6 warps (TMA, MMA, 4 softmax warps), a softmax thread owns a whole row (all 128 scores in registers, so no
-// exchange of row maxima and a single TMEM read), S has one 128-column buffer that goes back to the MMA warp as
-// soon as it is in registers, V has one stage, and 256 TMEM columns are allocated: S 128, O 64, and P as packed bf16
-// pairs in the last 64, so the P V product reads its A operand from TMEM and P never touches shared memory.
+// ------------------------------------------------- forward, D = 64: persistent, two CTAs per SM
+// A launch of one CTA per query tile spends 4 to 5 us per CTA outside the tile loop (launch gap, TMEM allocation,
+// first loads from cold, output epilogue) against 0.8 us per 64 keys inside it, so the kernel is persistent: two
+// CTAs per SM, each walking a static list of (batch, head, query tile) items, heavy tiles first and dealt out in
+// alternating direction so that the lists weigh about the same.  The pipelines run across item boundaries: Q has
+// two slots (the next item's Q arrives while this one computes; the finished item's output is parked in its own Q
+// slot and leaves by a TMA store that the next item does not wait for), and the first scores of the next item are
+// formed while the softmax warps are still in this item's epilogue.
+// A CTA is 6 warps (TMA, MMA, 4 softmax warps; a softmax thread owns a query row).  K and V arrive in 128-key
+// chunks (two stages each) but the products run on 64-key tiles, so that everything between the tensor pipe and
+// the softmax warps has two buffers inside 256 TMEM columns: S0 S1 (64 fp32 columns each), O (64), and P0 P1 as
+// packed 16-bit pairs (32 columns each; the P V product reads its A operand from TMEM).  With two buffers the
+// exponentials of tile t + 1 never wait for the product P_t V_t: the only dependence of a softmax thread on that
+// product is the rescale of O, which the lazy reference maximum makes rare.
 struct Fwd64Cfg {
   static constexpr int D = 64;
-  static constexpr int TILE_BYTES = 128 * D * 2;  // 16 KB
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = TILE_BYTES;        // 2 stages
-  static constexpr int OFF_V = 3 * TILE_BYTES;    // 1 stage
-  static constexpr int OFF_BAR = 4 * TILE_BYTES;  // P lives in TMEM
+  static constexpr int KT = 64;                   // keys per tile
+  static constexpr int TILE_BYTES = 128 * D * 2;  // 16 KB: a 128-row chunk of Q, K or V
+  static constexpr int OFF_Q = 0;                 // 2 slots
+  static constexpr int OFF_K = 2 * TILE_BYTES;    // 2 stages
+  static constexpr int OFF_V = 4 * TILE_BYTES;    // 2 stages
+  static constexpr int OFF_BAR = 6 * TILE_BYTES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
-  static constexpr int COL_S = 0, COL_O = 128, COL_P = 192;  // P: 128 bf16 per row as 64 packed columns
+  static constexpr int COL_S = 0, COL_O = 128, COL_P = 192;
   static constexpr int TMEM_COLS = 256;
   static constexpr int THREADS = 192;
 };
+
+// The n-th work item of this CTA.  Items are numbered heavy first (all heads of the last query tile, then of the
+// one before, ...); round n of the deal hands items n*G .. n*G + G - 1 to the G CTAs, in reversed order on odd rounds.
+struct Fwd64Item {
+  int i, bh, b, h;  // query tile, (batch, head)
+  int nt, nch;      // 64-key tiles, 128-key chunks
+};
+__device__ __forceinline__ bool fwd64_item(const AttnParams& p, int n, Fwd64Item& it) {
+  const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  const int BH = p.B * p.H, nq = (p.S + 127) / 128;
+  // 32-bit arithmetic: the host refuses launches with more than 2^30 items
+  const unsigned w = static_cast<unsigned>(n) * G + ((n & 1) ? G - 1 - c : c);
+  if (w >= static_cast<unsigned>(BH) * nq) return false;
+  const int level = static_cast<int>(w / static_cast<unsigned>(BH));
+  it.bh = static_cast<int>(w - static_cast<unsigned>(level) * BH);
+  it.i = nq - 1 - level;
+  it.b = it.bh / p.H;
+  it.h = it.bh - it.b * p.H;
+  const int nt_all = (p.S + Fwd64Cfg::KT - 1) / Fwd64Cfg::KT;
+  it.nt = p.causal ? min(2 * (it.i + 1), nt_all) : nt_all;
+  it.nch = (it.nt + 1) >> 1;
+  return true;
+}
 
 template <typename T, bool BIAS>
 __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
@@ -605,36 +635,34 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
   const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* gen = smem_dyn + (base - smem_u32(smem_dyn));
   const uint32_t bar = base + C::OFF_BAR;
-  const uint32_t bar_q = bar;
-  auto bar_kf = [&](int s) { return bar + 8 + 8u * s; };
-  auto bar_ke = [&](int s) { return bar + 24 + 8u * s; };
-  const uint32_t bar_vf = bar + 40, bar_ve = bar + 48;
-  const uint32_t bar_sf = bar + 56;  // scores complete in TMEM
-  const uint32_t bar_sr = bar + 64;  // scores are in registers: the buffer is free
-  const uint32_t bar_pr = bar + 72;  // P written (and O rescaled)
-  const uint32_t bar_pv = bar + 80;  // O += P V complete
-  const uint32_t tmem_slot = bar + 88;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 88);
+  auto bar_qf = [&](int s) { return bar + 0 + 8u * s; };    // Q slot s loaded
+  auto bar_qe = [&](int s) { return bar + 16 + 8u * s; };   // ... free again (its parked output has left)
+  auto bar_kf = [&](int s) { return bar + 32 + 8u * s; };
+  auto bar_ke = [&](int s) { return bar + 48 + 8u * s; };
+  auto bar_vf = [&](int s) { return bar + 64 + 8u * s; };
+  auto bar_ve = [&](int s) { return bar + 80 + 8u * s; };
+  auto bar_sf = [&](int u) { return bar + 96 + 8u * u; };   // scores of a tile complete in TMEM buffer u
+  auto bar_sr = [&](int u) { return bar + 112 + 8u * u; };  // ... are in registers: the buffer is free
+  auto bar_pr = [&](int u) { return bar + 128 + 8u * u; };  // P written into buffer u (and O rescaled)
+  auto bar_pv = [&](int u) { return bar + 144 + 8u * u; };  // O += P V complete for buffer u
+  const uint32_t tmem_slot = bar + 160;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 160);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nq = (p.S + 127) / 128;
-  const int i = nq - 1 - static_cast<int>(blockIdx.x);  // heavy (late) query tiles first
-  const int bh = blockIdx.y;
-  const int b = bh / p.H, h = bh % p.H;
-  const int nkv = p.causal ? i + 1 : nq;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_q, 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_qf(s), 1);
+      mbar_init(bar_qe(s), 1);
       mbar_init(bar_kf(s), 1);
       mbar_init(bar_ke(s), 1);
+      mbar_init(bar_vf(s), 1);
+      mbar_init(bar_ve(s), 1);
+      mbar_init(bar_sf(s), 1);
+      mbar_init(bar_sr(s), 4);
+      mbar_init(bar_pr(s), 4);
+      mbar_init(bar_pv(s), 1);
     }
-    mbar_init(bar_vf, 1);
-    mbar_init(bar_ve, 1);
-    mbar_init(bar_sf, 1);
-    mbar_init(bar_sr, 4);
-    mbar_init(bar_pr, 4);
-    mbar_init(bar_pv, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -653,60 +681,123 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(bar_q, C::TILE_BYTES);
-      tma_load_4d(base + C::OFF_Q, &tm_q, bar_q, 0, h, i * 128, b);
-      bool ok = true;
-      auto load_k = [&](int jt) {
-        const int s = jt & 1;
-        if (!mbar_wait(bar_ke(s), ((jt >> 1) & 1u) ^ 1u)) return false;
-        mbar_expect_tx(bar_kf(s), C::TILE_BYTES);
-        tma_load_4d(base + C::OFF_K + s * C::TILE_BYTES, &tm_k, bar_kf(s), 0, h, jt * 128, b);
+      tma_prefetch_desc(&tm_o);
+      auto load_q = [&](int n, const Fwd64Item& it) -> bool {
+        const int s = n & 1;
+        if (!mbar_wait(bar_qe(s), ((n >> 1) & 1u) ^ 1u)) return false;
+        mbar_expect_tx(bar_qf(s), C::TILE_BYTES);
+        tma_load_4d(base + C::OFF_Q + s * C::TILE_BYTES, &tm_q, bar_qf(s), 0, it.h, it.i * 128, it.b);
         return true;
       };
-      ok = load_k(0);
-      for (int jt = 0; jt < nkv && ok; ++jt) {
-        if (jt + 1 < nkv) ok = load_k(jt + 1);  // K runs a tile ahead of V: the next scores start early
-        if (!ok || !mbar_wait(bar_ve, (jt & 1u) ^ 1u)) {
-          ok = false;
-          break;
+      Fwd64Item it, nx;
+      bool ok = true;
+      bool have = fwd64_item(p, 0, it);
+      if (have) ok = load_q(0, it);
+      int g = 0;  // chunks loaded so far, over all items: stage and phase of the K / V rings
+      for (int n = 0; have && ok; ++n) {
+        const bool has_next = fwd64_item(p, n + 1, nx);
+        const int c_q = it.nch > 1 ? 1 : 0;  // the next Q is asked for once this item's first chunks are on their way
+        for (int c = 0; c < it.nch && ok; ++c, ++g) {
+          const int s = g & 1;
+          const uint32_t par = ((g >> 1) & 1u) ^ 1u;
+          if (!mbar_wait(bar_ke(s), par)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(bar_kf(s), C::TILE_BYTES);
+          tma_load_4d(base + C::OFF_K + s * C::TILE_BYTES, &tm_k, bar_kf(s), 0, it.h, c * 128, it.b);
+          if (!mbar_wait(bar_ve(s), par)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(bar_vf(s), C::TILE_BYTES);
+          tma_load_4d(base + C::OFF_V + s * C::TILE_BYTES, &tm_v, bar_vf(s), 0, it.h, c * 128, it.b);
+          if (c == c_q && has_next) ok = load_q(n + 1, nx);
         }
-        mbar_expect_tx(bar_vf, C::TILE_BYTES);
-        tma_load_4d(base + C::OFF_V, &tm_v, bar_vf, 0, h, jt * 128, b);
+        it = nx;
+        have = has_next;
       }
       if (!ok) atomicExch(p.status, kErrFwdTma);
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t id_s = umma_idesc_16<T>(128, 128, 0, 0);
+    // All 32 lanes walk the same control flow (waits included, their outcome made uniform by a vote) and one
+    // elected lane issues: descriptors and cursors then live in uniform registers.
+    {
+      constexpr uint32_t id_s = umma_idesc_16<T>(128, C::KT, 0, 0);
       constexpr uint32_t id_o = umma_idesc_16<T>(128, D, 0, 1);
-      const uint64_t dQ = base_k(base + C::OFF_Q);
-      const uint64_t dV = base_mn(base + C::OFF_V);
-      auto issue_s = [&](int jt) -> bool {
-        const int s = jt & 1;
-        if (!mbar_wait(bar_kf(s), (jt >> 1) & 1u)) return false;
-        if (jt >= 1 && !mbar_wait(bar_sr, (jt - 1) & 1u)) return false;  // previous scores are in registers
+      const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+      auto wait_all = [&](uint32_t bar_addr, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar_addr, parity));
+      };
+      // Two cursors over the CTA's tiles (item n, tile t of it, g0 = chunks of earlier items): the scores run two
+      // tiles ahead of the P V products, across item boundaries.
+      struct Cursor {
+        int n, t, g0;
+        bool valid;
+        Fwd64Item it;
+      };
+      auto advance = [&](Cursor& c) {
+        if (++c.t == c.it.nt) {
+          c.g0 += c.it.nch;
+          c.t = 0;
+          c.valid = fwd64_item(p, ++c.n, c.it);
+        }
+      };
+      Cursor cs{0, 0, 0, false, {}}, cp{0, 0, 0, false, {}};
+      cs.valid = fwd64_item(p, 0, cs.it);
+      cp = cs;
+      int ts = 0, tp = 0;  // tiles issued so far: buffer and phase of the S / P rings
+      // operand descriptors of every buffer, built once
+      const uint64_t dQs[2] = {base_k(base + C::OFF_Q), base_k(base + C::OFF_Q + C::TILE_BYTES)};
+      const uint64_t dKs[2] = {base_k(base + C::OFF_K), base_k(base + C::OFF_K + C::TILE_BYTES)};
+      const uint64_t dVs[2] = {base_mn(base + C::OFF_V), base_mn(base + C::OFF_V + C::TILE_BYTES)};
+      auto issue_s = [&]() -> bool {
+        const int t = cs.t, g = cs.g0 + (t >> 1), s = g & 1, u = ts & 1, qs = cs.n & 1;
+        if (t == 0 && !wait_all(bar_qf(qs), (cs.n >> 1) & 1u)) return false;
+        if ((t & 1) == 0 && !wait_all(bar_kf(s), (g >> 1) & 1u)) return false;
+        if (ts >= 2 && !wait_all(bar_sr(u), ((ts - 2) >> 1) & 1u)) return false;  // tile ts - 2 is in registers
         tc_fence_after();
-        const uint64_t dK = base_k(base + C::OFF_K + s * C::TILE_BYTES);
+        const uint64_t dQ = qs ? dQs[1] : dQs[0];
+        const uint64_t dK = (s ? dKs[1] : dKs[0]) + static_cast<uint64_t>(((t & 1) * (C::KT * 128)) >> 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(tmem + C::COL_S, desc_k(dQ, k), desc_k(dK, k), id_s, k > 0);
-        umma_commit(bar_ke(s));
-        umma_commit(bar_sf);
+          for (int k = 0; k < D / 16; ++k)
+            umma_ss(tm + C::COL_S + u * C::KT, desc_k(dQ, k), desc_k(dK, k), id_s, k > 0);
+          if ((t & 1) || t == cs.it.nt - 1) umma_commit(bar_ke(s));  // last product that reads this K chunk
+          umma_commit(bar_sf(u));
+        }
+        __syncwarp();
+        ++ts;
+        advance(cs);
         return true;
       };
-      bool ok = mbar_wait(bar_q, 0) && issue_s(0);
-      for (int jt = 0; jt < nkv && ok; ++jt) {
-        if (jt + 1 < nkv) ok = issue_s(jt + 1);
-        ok = ok && mbar_wait(bar_pr, jt & 1u) && mbar_wait(bar_vf, jt & 1u);
+      bool ok = true;
+      if (cs.valid) ok = issue_s();
+      if (ok && cs.valid) ok = issue_s();
+      while (ok && cp.valid) {
+        // scores first: tile tp + 2 only needs tile tp in registers, which comes before P of tile tp
+        if (cs.valid && ts < tp + 3) ok = issue_s();
+        if (!ok) break;
+        const int t = cp.t, g = cp.g0 + (t >> 1), s = g & 1, u = tp & 1;
+        ok = wait_all(bar_pr(u), (tp >> 1) & 1u);
+        if (ok && (t & 1) == 0) ok = wait_all(bar_vf(s), (g >> 1) & 1u);
         if (!ok) break;
         tc_fence_after();
+        const uint64_t dV = desc_mn(s ? dVs[1] : dVs[0], (t & 1) * 4);
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k)  // P is a TMEM operand: 8 packed columns per 16 keys
-          umma_ts(tmem + C::COL_O, tmem + C::COL_P + k * 8, desc_mn(dV, k), id_o, (jt > 0 || k > 0) ? 1u : 0u);
-        umma_commit(bar_ve);
-        umma_commit(bar_pv);
+          for (int k = 0; k < C::KT / 16; ++k)  // P is a TMEM operand: 8 packed columns per 16 keys
+            umma_ts(tm + C::COL_O, tm + C::COL_P + u * (C::KT / 2) + k * 8, desc_mn(dV, k), id_o,
+                    (t > 0 || k > 0) ? 1u : 0u);
+          if ((t & 1) || t == cp.it.nt - 1) umma_commit(bar_ve(s));
+          umma_commit(bar_pv(u));
+        }
+        __syncwarp();
+        ++tp;
+        advance(cp);
       }
-      if (!ok) atomicExch(p.status, kErrFwdMma);
+      if (!ok && lane == 0) atomicExch(p.status, kErrFwdMma);
     }
     __syncwarp();
   } else {
@@ -714,123 +805,153 @@ __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 2)
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const int qrow = i * 128 + r;
     const float scale_log2 = p.scale * kLog2e;
-    float m = -INFINITY, l = 0.f;
+    const bool storer = (warp == 2 && lane == 0);
+    int tt = 0;          // tiles done so far, over all items
+    int parked = -1;     // Q slot whose parked output is still leaving (storer only)
     bool ok = true;
-    for (int jt = 0; jt < nkv && ok; ++jt) {
-      if (!mbar_wait(bar_sf, jt & 1u)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      uint32_t v[128];
+    Fwd64Item it;
+    // After a failed wait a warp stops touching TMEM and mbarriers but still walks its items for the named
+    // barrier of the epilogue, so that the other softmax warps are never left waiting on it.
+    for (int n = 0; fwd64_item(p, n, it); ++n) {
+      const int i = it.i, bh = it.bh;
+      const int qrow = i * 128 + r;
+      float m = -INFINITY, l = 0.f;
+      for (int t = 0; t < it.nt && ok; ++t, ++tt) {
+        const int u = tt & 1;
+        if (!mbar_wait(bar_sf(u), (tt >> 1) & 1u)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t v[C::KT];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + C::COL_S + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_sr);
-      if constexpr (BIAS)
-        add_bias_row<T, 128>(v, p.bias + (static_cast<int64_t>(bh) * p.S + (qrow < p.S ? qrow : 0)) * p.S, jt * 128, p.S,
-                             qrow < p.S, p.inv_scale, p.bias_vec);
-      const bool diag = p.causal && (jt == i);
-      if (diag || (jt * 128 + 128 > p.S)) {
+        for (int c = 0; c < C::KT / 32; ++c)
+          tmem_ld32(tmem + lane_base + C::COL_S + u * C::KT + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sr(u));
+        const int key0 = t * C::KT;
+        if constexpr (BIAS)
+          add_bias_row<T, C::KT>(v, p.bias + (static_cast<int64_t>(bh) * p.S + (qrow < p.S ? qrow : 0)) * p.S, key0, p.S,
+                                 qrow < p.S, p.inv_scale, p.bias_vec);
+        const bool diag = p.causal && (key0 + C::KT - 1 > i * 128);
+        if (diag || (key0 + C::KT > p.S)) {
 #pragma unroll
-        for (int e = 0; e < 128; ++e) {
-          const int kvrow = jt * 128 + e;
-          const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
-          if (!keep) v[e] = __float_as_uint(-INFINITY);
+          for (int e = 0; e < C::KT; ++e) {
+            const int kvrow = key0 + e;
+            const bool keep = kvrow < p.S && (!diag || kvrow <= qrow);
+            if (!keep) v[e] = __float_as_uint(-INFINITY);
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < C::KT; e += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(v[e]));
+          mx1 = fmaxf(mx1, __uint_as_float(v[e + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(v[e + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(v[e + 3]));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        // lazy reference maximum, as in the D = 128 kernel
+        const float m_cand = fmaxf(m, mx * scale_log2);
+        const float m_new = (t == 0 || m_cand - m > 8.f) ? m_cand : m;
+        const float corr = (t == 0) ? 0.f : ex2(m - m_new);
+        // P buffer u is free once the product of tile tt - 2 is complete (every phase of bar_pv(u) is waited for
+        // here, in order)
+        if (tt >= 2 && !mbar_wait(bar_pv(u), ((tt - 2) >> 1) & 1u)) {
+          ok = false;
+          break;
+        }
+        if (t > 0 && __any_sync(0xffffffffu, m_new != m)) {
+          // O must be stable: the product of tile tt - 1 (the other buffer; this phase is waited for again, as the
+          // "buffer free" wait of tile tt + 1, which is harmless)
+          if (!mbar_wait(bar_pv(u ^ 1), ((tt - 1) >> 1) & 1u)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 16) {
+            uint32_t o[16];
+            tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+            tmem_st16(tmem + lane_base + C::COL_O + c0, o);
+          }
+          tmem_st_wait();
+        }
+        tc_fence_after();
+        float rs0 = 0.f, rs1 = 0.f;
+        const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+#pragma unroll
+        for (int c32 = 0; c32 < C::KT / 32; ++c32) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = ex2(fmaf(__uint_as_float(v[c32 * 32 + 2 * e]), scale_log2, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(v[c32 * 32 + 2 * e + 1]), scale_log2, neg_m));
+            rs0 += p0;
+            rs1 += p1;
+            pk[e] = pack_pair<T>(p0, p1);
+          }
+          tmem_st16(tmem + lane_base + C::COL_P + u * (C::KT / 2) + c32 * 16, pk);
+        }
+        tmem_st_wait();
+        l = l * corr + (rs0 + rs1);
+        m = m_new;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pr(u));
+        if (t == 0 && storer && parked >= 0) {  // the previous item's output has had a tile's time to leave
+          bulk_wait_read0();
+          mbar_arrive(bar_qe(parked));
+          parked = -1;
         }
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < 128; e += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(v[e]));
-        mx1 = fmaxf(mx1, __uint_as_float(v[e + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(v[e + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(v[e + 3]));
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // lazy reference maximum, as in the D = 128 kernel
-      const float m_cand = fmaxf(m, mx * scale_log2);
-      const float m_new = (jt == 0 || m_cand - m > 8.f) ? m_cand : m;
-      const float corr = (jt == 0) ? 0.f : ex2(m - m_new);
-      if (jt > 0 && !mbar_wait(bar_pv, (jt - 1) & 1u)) {  // P may be overwritten, O is stable
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      if (jt > 0 && __any_sync(0xffffffffu, m_new != m)) {
+      // the item's last product; the tensor pipe completes a thread's products in order, so every earlier one is
+      // done too
+      if (ok && !mbar_wait(bar_pv((tt - 1) & 1), ((tt - 1) >> 1) & 1u)) ok = false;
+      // The normalised output leaves through the TMA unit: every thread parks its row in the item's Q slot (free
+      // once the last scores were formed; same swizzled box) and one thread stores the tile, whole 128-byte lines
+      // per request, rows past S clipped by the tensor map.
+      const uint32_t q_off = C::OFF_Q + (n & 1) * C::TILE_BYTES;
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 16) {
           uint32_t o[16];
           tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
-          tmem_st16(tmem + lane_base + C::COL_O + c0, o);
+          for (int e = 0; e < 16; e += 8) {
+            uint4 w;
+            w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+            w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+            w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+            w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(gen + q_off + ps_chunk_off(r, (c0 + e) >> 3)) = w;
+          }
         }
-        tmem_st_wait();
+        tc_fence_before();
+        fence_async_smem();
+        if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
       }
-      float rs0 = 0.f, rs1 = 0.f;
-      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
-#pragma unroll
-      for (int c32 = 0; c32 < 4; ++c32) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(v[c32 * 32 + 2 * e]), scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(v[c32 * 32 + 2 * e + 1]), scale_log2, neg_m));
-          rs0 += p0;
-          rs1 += p1;
-          pk[e] = pack_pair<T>(p0, p1);
-        }
-        tmem_st16(tmem + lane_base + C::COL_P + c32 * 16, pk);
+      named_barrier(1, 4 * 32);  // the four softmax warps
+      if (ok && storer) {
+        if (p.o_bshd)
+          tma_store_4d(&tm_o, base + q_off, 0, it.h, i * 128, it.b);
+        else
+          tma_store_3d(&tm_o, base + q_off, 0, i * 128, bh);
+        bulk_commit();
+        parked = n & 1;
       }
-      tmem_st_wait();
-      l = l * corr + (rs0 + rs1);
-      m = m_new;
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pr);
     }
-    if (ok && !mbar_wait(bar_pv, (nkv - 1) & 1u)) ok = false;
-    // The normalised output leaves through the TMA unit: every thread parks its row in the Q tile (free once the
-    // last scores were formed; same swizzled box) and one thread stores the tile, whole 128-byte lines per request,
-    // rows past S clipped by the tensor map.
-    if (!ok) {
-      if (lane == 0) atomicExch(p.status, kErrFwdSoftmax);
-    } else {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 16) {
-        uint32_t o[16];
-        tmem_ld16(tmem + lane_base + C::COL_O + c0, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 16; e += 8) {
-          uint4 w;
-          w.x = pack_pair<T>(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-          w.y = pack_pair<T>(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
-          w.z = pack_pair<T>(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
-          w.w = pack_pair<T>(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
-          *reinterpret_cast<uint4*>(gen + C::OFF_Q + ps_chunk_off(r, (c0 + e) >> 3)) = w;
-        }
-      }
-      fence_async_smem();
-      if (qrow < p.S) p.lse_out[static_cast<int64_t>(bh) * p.S + qrow] = (m + log2f(l)) / kLog2e;
-    }
-    named_barrier(1, 4 * 32);  // the four softmax warps
-    if (ok && warp == 2 && lane == 0) {
-      if (p.o_bshd)
-        tma_store_4d(&tm_o, base + C::OFF_Q, 0, h, i * 128, b);
-      else
-        tma_store_3d(&tm_o, base + C::OFF_Q, 0, i * 128, bh);
-      bulk_commit();
-      bulk_wait_read0();
-    }
+    if (storer && parked >= 0) bulk_wait_read0();  // shared memory must outlive the last store's reads
+    if (!ok && lane == 0) atomicExch(p.status, kErrFwdSoftmax);
   }
   tc_fence_before();
   __syncthreads();
@@ -1156,6 +1277,8 @@ template <typename K>
 int set_smem(K kern, int bytes) {
   const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   if (e != cudaSuccess) return fail(MGB_ECUDA, "attention smem opt-in (%d B): %s", bytes, cudaGetErrorString(e));
+  // the largest shared-memory carveout, so that two CTAs of the D = 64 forward kernel fit on an SM
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   return MGB_OK;
 }
 
@@ -1224,8 +1347,11 @@ int run_fwd64(const void* q, const void* k, const void* v, AttnParams p, int64_t
   auto kern = p.bias ? attn_fwd_tc64_kernel<T, true> : attn_fwd_tc64_kernel<T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
-  dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
-  launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mo, p);
+  const int64_t items = static_cast<int64_t>((p.S + 127) / 128) * p.B * p.H;
+  MGB_REQUIRE(items <= (int64_t{1} << 30), MGB_EUNSUPPORTED, "flash_attn_fwd: %lld query tiles exceed 2^30",
+              static_cast<long long>(items));
+  const int ctas = static_cast<int>(std::min<int64_t>(items, 2 * static_cast<int64_t>(sm_count())));
+  launch_pdl(kern, dim3(static_cast<unsigned>(ctas)), dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mo, p);
   return check_launch("attn_fwd_tc64_kernel");
 }
 
