@@ -604,6 +604,57 @@ __global__ void __launch_bounds__(kFinCols* kFinLanes)
   }
 }
 
+// The same sums with 16-byte loads: a block owns 32 consecutive entries of the [2*cols] partial row (8 threads of
+// float4) and 32 lanes stride over the partial rows with four loads in flight each; the 32 lane sums of a column are
+// then added in lane order, so the result does not depend on timing.  Needs 2*cols % 4 == 0 and a 16-byte aligned
+// workspace.
+constexpr int kFin4Lanes = 32;
+template <typename T>
+__global__ void __launch_bounds__(8 * kFin4Lanes)
+    ln_bwd_finalize4_kernel(const float* __restrict__ part, int nparts, int64_t cols, T* __restrict__ dgamma,
+                            T* __restrict__ dbeta) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[kFin4Lanes][33];
+  const int cx = threadIdx.x & 7, ry = threadIdx.x >> 3;
+  const int64_t c4 = static_cast<int64_t>(blockIdx.x) * 32 + cx * 4;  // index into [2*cols]
+  float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
+  if (c4 < 2 * cols) {
+    const float* col = part + c4;
+    const int64_t ld = 2 * cols;
+    int q = ry;
+    for (; q + 3 * kFin4Lanes < nparts; q += 4 * kFin4Lanes) {
+      const float4 v0 = *reinterpret_cast<const float4*>(col + static_cast<int64_t>(q) * ld);
+      const float4 v1 = *reinterpret_cast<const float4*>(col + static_cast<int64_t>(q + kFin4Lanes) * ld);
+      const float4 v2 = *reinterpret_cast<const float4*>(col + static_cast<int64_t>(q + 2 * kFin4Lanes) * ld);
+      const float4 v3 = *reinterpret_cast<const float4*>(col + static_cast<int64_t>(q + 3 * kFin4Lanes) * ld);
+      a0.x += v0.x, a0.y += v0.y, a0.z += v0.z, a0.w += v0.w;
+      a1.x += v1.x, a1.y += v1.y, a1.z += v1.z, a1.w += v1.w;
+      a2.x += v2.x, a2.y += v2.y, a2.z += v2.z, a2.w += v2.w;
+      a3.x += v3.x, a3.y += v3.y, a3.z += v3.z, a3.w += v3.w;
+    }
+    for (; q < nparts; q += kFin4Lanes) {
+      const float4 v0 = *reinterpret_cast<const float4*>(col + static_cast<int64_t>(q) * ld);
+      a0.x += v0.x, a0.y += v0.y, a0.z += v0.z, a0.w += v0.w;
+    }
+  }
+  red[ry][cx * 4 + 0] = (a0.x + a1.x) + (a2.x + a3.x);
+  red[ry][cx * 4 + 1] = (a0.y + a1.y) + (a2.y + a3.y);
+  red[ry][cx * 4 + 2] = (a0.z + a1.z) + (a2.z + a3.z);
+  red[ry][cx * 4 + 3] = (a0.w + a1.w) + (a2.w + a3.w);
+  __syncthreads();
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x;
+  if (threadIdx.x < 32 && c < 2 * cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kFin4Lanes; ++i) t += red[i][threadIdx.x];
+    if (c < cols)
+      dgamma[c] = from_f32<T>(t);
+    else
+      dbeta[c - cols] = from_f32<T>(t);
+  }
+}
+
 struct Plan {
   int wpr, chunks, grid;
 };
@@ -705,6 +756,20 @@ int ln_bwd_main(const void* dy, const void* x, const void* gamma, const void* re
 }
 
 template <typename T>
+int ln_bwd_finalize(const float* part, int nparts, int64_t cols, void* dgamma, void* dbeta, cudaStream_t st) {
+  if (cols % 2 == 0 && aligned16(part)) {
+    const unsigned fgrid = static_cast<unsigned>((2 * cols + 31) / 32);
+    launch_pdl(ln_bwd_finalize4_kernel<T>, dim3(fgrid), dim3(8 * kFin4Lanes), 0, st, part, nparts, cols,
+               static_cast<T*>(dgamma), static_cast<T*>(dbeta));
+    return check_launch("ln_bwd_finalize4_kernel");
+  }
+  const unsigned fgrid = static_cast<unsigned>((2 * cols + kFinCols - 1) / kFinCols);
+  launch_pdl(ln_bwd_finalize_kernel<T>, dim3(fgrid), dim3(kFinCols * kFinLanes), 0, st, part, nparts, cols,
+             static_cast<T*>(dgamma), static_cast<T*>(dbeta));
+  return check_launch("ln_bwd_finalize_kernel");
+}
+
+template <typename T>
 int ln_bwd(const void* dy, const void* x, const void* gamma, const void* resid, void* dx, void* dgamma, void* dbeta,
            int64_t rows, int64_t cols, float eps, void* ws, size_t ws_bytes, cudaStream_t st) {
   Plan pl;
@@ -716,10 +781,7 @@ int ln_bwd(const void* dy, const void* x, const void* gamma, const void* resid, 
   float* part = static_cast<float*>(ws);
   int rc = ln_bwd_main<T>(dy, x, gamma, resid, dx, part, rows, cols, eps, pl, st);
   if (rc != MGB_OK) return rc;
-  const unsigned fgrid = static_cast<unsigned>((2 * cols + kFinCols - 1) / kFinCols);
-  launch_pdl(ln_bwd_finalize_kernel<T>, dim3(fgrid), dim3(kFinCols * kFinLanes), 0, st, static_cast<const float*>(part),
-             pl.grid, cols, static_cast<T*>(dgamma), static_cast<T*>(dbeta));
-  return check_launch("ln_bwd_finalize_kernel");
+  return ln_bwd_finalize<T>(part, pl.grid, cols, dgamma, dbeta, st);
 }
 
 // Scratch for mograd_b200_layer_norm_bwd_static: room for the per-CTA dgamma /
