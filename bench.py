@@ -297,12 +297,13 @@ def profile_case(name, reps, device):
         a = torch.randn((16384, 768), generator=g, device=device).bfloat16()
         w = (torch.randn((50304, 768), generator=g, device=device) / 28).bfloat16()
         fn = lambda: K.matmul_bias_strided(a, w)
-    elif name in ("flash_fwd", "flash_bwd"):
-        B, S, H, D = 1, 4096, 16, 128
+    elif name in ("flash_fwd", "flash_bwd", "flash_fwd_d64", "flash_bwd_d64"):
+        # D = 128: one batch element of the attention benchmark; D = 64: the train step's own shape
+        B, S, H, D = (16, 1024, 12, 64) if name.endswith("d64") else (1, 4096, 16, 128)
         q, k, v = (torch.randn((B, S, H, D), generator=g, device=device).bfloat16() for _ in range(3))
         do = torch.randn((B, H, S, D), generator=g, device=device).bfloat16()
         o, lse = K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False)
-        if name == "flash_fwd":
+        if name.startswith("flash_fwd"):
             fn = lambda: K.flash_attn_fwd_dispatch(q, k, v, None, None, True, False)
         else:
             fn = lambda: K.flash_attn_bwd_dispatch(do, o, q, k, v, None, lse, None, True, False)
@@ -312,6 +313,64 @@ def profile_case(name, reps, device):
         fn()
     torch.cuda.synchronize()
     print(json.dumps(dict(case=name, reps=reps, status="ok")), flush=True)
+
+
+# ----------------------------------------------------------------------------- in-step timeline
+def step_timeline(cfg, device, steps=3):
+    """Device timeline of one train step from the CUDA activity records (torch.profiler / CUPTI, no kernel
+    replay): per kernel its launches and its EXCLUSIVE time inside the step, i.e. the part of each launch that does
+    not overlap the kernels before it (programmatic dependent launch lets a kernel's set-up run under its
+    predecessor's tail, so plain durations add up to more than the step).  Prints a table to stderr and returns
+    the rows; the numbers are of a real step at the clocks the step runs at, unlike per-launch times under a
+    replaying profiler."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    model = build_model(cfg, device, 1, None, seed=0)
+    bx, by = make_batch(cfg, seed=100)
+    model.d_inputs.copy_(bx)
+    model.d_targets.copy_(by)
+    for _ in range(3):
+        model.step_device()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            model.step_device()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                key=lambda e: e.time_range.start)
+    marks = [i for i, e in enumerate(ev) if "adamw" in e.name]  # the optimizer kernel closes a step
+    if len(marks) < 2:
+        raise SystemExit("timeline: fewer than two optimizer launches recorded")
+    step = ev[marks[0] + 1:marks[1] + 1]
+    t0 = step[0].time_range.start
+    agg, prev_end = collections.OrderedDict(), t0
+    for e in step:
+        s0, s1 = e.time_range.start, e.time_range.end
+        name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").replace("mgb::", "")
+        depth = 0
+        for ci, ch in enumerate(name):
+            depth += (ch == "<") - (ch == ">")
+            if ch == "(" and depth == 0:
+                name = name[:ci]
+                break
+        a = agg.setdefault(name[:72], [0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += max(0.0, s1 - max(s0, prev_end))
+        a[2] += s1 - s0
+        prev_end = max(prev_end, s1)
+    span = (prev_end - t0) / 1e3
+    rows = sorted(agg.items(), key=lambda kv: -kv[1][1])
+    print(f"one train step: span {span:.3f} ms, {len(step)} launches, exclusive times sum "
+          f"{sum(a[1] for _, a in rows) / 1e3:.3f} ms", file=sys.stderr)
+    print(f"{'launches':>8} {'exclusive ms':>13} {'share':>6} {'avg us':>8} {'avg duration us':>16}  kernel", file=sys.stderr)
+    tot = sum(a[1] for _, a in rows)
+    for name, (n, ex, du) in rows:
+        print(f"{n:8d} {ex / 1e3:13.3f} {100 * ex / tot:5.1f}% {ex / n:8.1f} {du / n:16.1f}  {name}", file=sys.stderr)
+    return dict(span_ms=round(span, 3), launches=len(step),
+                kernels={k: dict(launches=n, exclusive_ms=round(ex / 1e3, 4)) for k, (n, ex, du) in rows})
 
 
 # ----------------------------------------------------------------------------- CPU baseline (oracle)
@@ -390,6 +449,8 @@ def main():
     ap.add_argument("--no-kernels", action="store_true", help="skip the standalone kernel section")
     ap.add_argument("--case", default=None, help="run one small kernel case --reps times and exit (for profiling)")
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the per-kernel exclusive-time table of one train step (1 GPU) and exit")
     ap.add_argument("--bucket-mb", type=int, default=64, help="gradient all-reduce bucket size (N > 1)")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to stdout; the contract is one JSON line there.  Everything
@@ -412,6 +473,13 @@ def main():
         profile_case(args.case, args.reps, torch.device("cuda", 0))
         return 0
     cfg = dict(WORKLOADS[args.workload], name=args.workload)
+    if args.timeline:
+        import torch
+        import mograd_b200
+
+        mograd_b200.load()
+        emit(dict(timeline=step_timeline(cfg, torch.device("cuda", 0)), workload=args.workload))
+        return 0
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
