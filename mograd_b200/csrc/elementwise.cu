@@ -112,7 +112,13 @@ __global__ void __launch_bounds__(kEwThreads)
     gi *= grad_scale;
     mi = b1 * mi + (1.f - b1) * gi;
     vi = b2 * vi + (1.f - b2) * gi * gi;
-    wi = wi * decay - lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+    // sqrt.approx and the reciprocal-multiply division are within 2 ulp each; their error enters w scaled by lr,
+    // far below the rounding of w itself, and they take a third of the instructions of the IEEE forms: under the
+    // step's power cap this kernel is bound by instruction issue, not by DRAM
+    float root, inv;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(root) : "f"(vi * inv_bc2));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(root + eps));
+    wi = fmaf(-lr * (mi * inv_bc1), inv, wi * decay);
   };
   const int64_t nv = vec ? n / V : 0;
   for (int64_t i = tid; i < nv; i += stride) {
