@@ -575,7 +575,8 @@ def main():
     value = cfg["tokens_per_step"] * world / (ms_per_step * 1e-3)
 
     # end to end through the host-facing call: host batch in, loss out, every step
-    for i in range(2):
+    # (untimed: two eager steps, then the steps in which Model.step() captures its two CUDA graphs, one per slot)
+    for i in range(6):
         model.step(*batches[i & 1], prefetch=batches[(i + 1) & 1])
     barrier()
     t0 = time.perf_counter()

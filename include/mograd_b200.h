@@ -335,6 +335,15 @@ int mograd_b200_adamw_step(void* w, const void* g, float* m, float* v, float* ma
                            float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale,
                            int dtype, void* stream);
 
+/* The same update with the step number read from device memory, for callers
+ * that replay a captured stream (a CUDA graph): a replay cannot carry a new
+ * scalar argument, so the 1-based step lives in *step_dev.  advance != 0
+ * first adds 1 to *step_dev on the stream (use it on the first range of a
+ * step when the parameters are updated range by range). */
+int mograd_b200_adamw_step_dev(void* w, const void* g, float* m, float* v, float* master, int64_t numel, float lr,
+                               float beta1, float beta2, float eps, float weight_decay, int* step_dev, int advance,
+                               float grad_scale, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

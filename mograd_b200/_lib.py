@@ -75,6 +75,8 @@ SIGNATURES = {
     "mograd_b200_scatter_add_rows_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "mograd_b200_scatter_add_rows": (_int, [_p, _p, _p, _i64, _i64, _i64, _int, _p, _sz, _p]),
     "mograd_b200_adamw_step": (_int, [_p, _p, _p, _p, _p, _i64, _f32, _f32, _f32, _f32, _f32, _int, _f32, _int, _p]),
+    "mograd_b200_adamw_step_dev": (_int, [_p, _p, _p, _p, _p, _i64, _f32, _f32, _f32, _f32, _f32, _p, _int, _f32, _int,
+                                          _p]),
 }
 
 

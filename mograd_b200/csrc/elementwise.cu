@@ -103,8 +103,13 @@ template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
     adamw_kernel(T* __restrict__ w, const T* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                  float* __restrict__ master, int64_t n, float lr, float b1, float b2, float eps, float wd, float inv_bc1,
-                 float inv_bc2, float grad_scale, int vec) {
+                 float inv_bc2, float grad_scale, int vec, const int* __restrict__ step_dev) {
   constexpr int V = Vec<T>::N;  // elements per 16-byte access of the parameter type
+  if (step_dev) {  // step number kept on the device (a captured launch cannot carry a new scalar per replay)
+    const float t = static_cast<float>(*step_dev);
+    inv_bc1 = 1.f / (1.f - powf(b1, t));
+    inv_bc2 = 1.f / (1.f - powf(b2, t));
+  }
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kEwThreads;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x;
   const float decay = wd > 0.f ? 1.f - lr * wd : 1.f;
@@ -284,7 +289,33 @@ MGB_EXPORT int mograd_b200_adamw_step(void* w, const void* g, float* m, float* v
     const int vec = aligned16(w) && aligned16(g) && aligned16(m) && aligned16(v) && (!master || aligned16(master));
     adamw_kernel<T><<<ew_grid(numel / Vec<T>::N + 1), kEwThreads, 0, st>>>(
         static_cast<T*>(w), static_cast<const T*>(g), m, v, master, numel, lr, beta1, beta2, eps, weight_decay, inv_bc1,
-        inv_bc2, grad_scale, vec);
+        inv_bc2, grad_scale, vec, nullptr);
+  })
+  return check_launch("adamw_kernel");
+}
+
+namespace mgb {
+namespace {
+__global__ void bump_counter_kernel(int* c) { *c += 1; }
+}  // namespace
+}  // namespace mgb
+
+MGB_EXPORT int mograd_b200_adamw_step_dev(void* w, const void* g, float* m, float* v, float* master, int64_t numel,
+                                          float lr, float beta1, float beta2, float eps, float weight_decay,
+                                          int* step_dev, int advance, float grad_scale, int dtype, void* stream) {
+  MGB_REQUIRE(w && g && m && v && step_dev, MGB_EINVAL, "adamw_step_dev: NULL argument");
+  MGB_REQUIRE(numel > 0, MGB_EINVAL, "adamw_step_dev: numel=%lld", (long long)numel);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (advance) {
+    mgb::bump_counter_kernel<<<1, 1, 0, st>>>(step_dev);
+    int rc = check_launch("bump_counter_kernel");
+    if (rc != MGB_OK) return rc;
+  }
+  MGB_DTYPE_SWITCH(dtype, "adamw_step_dev", {
+    const int vec = aligned16(w) && aligned16(g) && aligned16(m) && aligned16(v) && (!master || aligned16(master));
+    adamw_kernel<T><<<ew_grid(numel / Vec<T>::N + 1), kEwThreads, 0, st>>>(
+        static_cast<T*>(w), static_cast<const T*>(g), m, v, master, numel, lr, beta1, beta2, eps, weight_decay, 1.f, 1.f,
+        grad_scale, vec, step_dev);
   })
   return check_launch("adamw_kernel");
 }

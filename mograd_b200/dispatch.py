@@ -362,3 +362,12 @@ def adamw_step(w, g, m, v, master, lr, beta1, beta2, eps, weight_decay, step, gr
     _require_cuda(w, g, m, v, master)
     call("mograd_b200_adamw_step", _ptr(w), _ptr(g), _ptr(m), _ptr(v), _ptr(master), w.numel(), float(lr), float(beta1),
          float(beta2), float(eps), float(weight_decay), int(step), float(grad_scale), dtype_code(w), _stream())
+
+
+def adamw_step_dev(w, g, m, v, master, lr, beta1, beta2, eps, weight_decay, step_dev, advance, grad_scale=1.0):
+    """AdamW with the 1-based step number in the device int32 tensor step_dev (for captured / replayed streams);
+    advance=True adds 1 to it on the stream first."""
+    _require_cuda(w, g, m, v, master, step_dev)
+    call("mograd_b200_adamw_step_dev", _ptr(w), _ptr(g), _ptr(m), _ptr(v), _ptr(master), w.numel(), float(lr),
+         float(beta1), float(beta2), float(eps), float(weight_decay), _ptr(step_dev), int(bool(advance)),
+         float(grad_scale), dtype_code(w), _stream())

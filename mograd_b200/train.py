@@ -16,6 +16,7 @@ PyTorch supplies device memory, streams and the NCCL process group only.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from dataclasses import dataclass
 
@@ -117,6 +118,20 @@ class _Model:
         self.exposed_events = []    # per step: [(lo, hi, before, after)] CUDA events around each wait
         self._staged = None         # input slot whose host->device copy has been issued ahead of its step
         self._slot = 0
+        # step() replays a captured CUDA graph of the whole step (one per input slot) after two eager steps: the
+        # host then issues one launch per step instead of several hundred, which matters whenever step() must hand
+        # the loss back before the next step can be queued.  Data-parallel runs stay eager: with the bucket
+        # all-reduces captured (NCCL on the communication stream, joined by events) the two-GPU test produced the
+        # same losses but took minutes instead of seconds and did not shut down cleanly.  MOGRAD_B200_GRAPH=0
+        # switches the replay off.
+        self.use_graph = (self.device.type == "cuda" and world_size == 1 and
+                          os.environ.get("MOGRAD_B200_GRAPH", "1") != "0")
+        self._graphs = [None, None]
+        self._graph_loss = [None, None]
+        self._eager_steps = 0
+        self._advanced = False      # this step's optimiser launches have already advanced the device step counter
+        # 1-based step number on the device: a replayed launch cannot carry a new scalar
+        self.d_step = torch.zeros(1, dtype=torch.int32, device=self.device) if self.device.type == "cuda" else None
 
     # ---- host-side input staging ---------------------------------------------------------
     def _setup_io(self, in_shape, in_dtype, tgt_shape):
@@ -201,8 +216,13 @@ class _Model:
         o = self.opt
         s = self.store
         hi = s.size if hi is None else hi
-        K.adamw_step(s.w[lo:hi], s.g[lo:hi], s.m[lo:hi], s.v[lo:hi], s.master[lo:hi], o.lr, o.beta1, o.beta2, o.eps,
-                     o.weight_decay, self.step_count, grad_scale=1.0 / self.world_size)
+        if self.d_step is not None:
+            K.adamw_step_dev(s.w[lo:hi], s.g[lo:hi], s.m[lo:hi], s.v[lo:hi], s.master[lo:hi], o.lr, o.beta1, o.beta2,
+                             o.eps, o.weight_decay, self.d_step, not self._advanced, grad_scale=1.0 / self.world_size)
+            self._advanced = True
+        else:
+            K.adamw_step(s.w[lo:hi], s.g[lo:hi], s.m[lo:hi], s.v[lo:hi], s.master[lo:hi], o.lr, o.beta1, o.beta2,
+                         o.eps, o.weight_decay, self.step_count, grad_scale=1.0 / self.world_size)
 
     # ---- host-facing call: host buffers in, loss out -------------------------------------
     def step(self, host_inputs, host_targets, prefetch=None) -> float:
@@ -221,18 +241,43 @@ class _Model:
             self._staged = None
             self.d_inputs.copy_(host_inputs, non_blocking=True)
             self.d_targets.copy_(host_targets, non_blocking=True)
-        loss = self.step_device()
+        k = self._slot
+        if self.use_graph and self._graphs[k] is None and self._eager_steps >= 2:
+            self._capture(k)
+        if self.use_graph and self._graphs[k] is not None:
+            self._graphs[k].replay()
+            self.step_count += 1
+        else:
+            loss = self.step_device()
+            self._eager_steps += 1
+            self.h_loss.copy_(loss, non_blocking=True)
+            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self.h_status.data_ptr()),
+                      ctypes.c_void_p(main.cuda_stream))
         if prefetch is not None:
             self._prefetch(*prefetch)
-        self.h_loss.copy_(loss, non_blocking=True)
-        _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self.h_status.data_ptr()),
-                  ctypes.c_void_p(main.cuda_stream))
         main.synchronize()
         if int(self.h_status[0]) != 0:
             _lib.check_device_status("Model.step")
         return float(self.h_loss.item())
 
+    def _capture(self, k):
+        """Records one whole step reading input slot k (kernels, the loss and status copies to pinned host words)
+        into a CUDA graph.  Nothing runs during the capture; the caller replays it."""
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        g = torch.cuda.CUDAGraph()
+        count = self.step_count
+        with torch.cuda.graph(g, stream=side):
+            loss = self.step_device()
+            self.h_loss.copy_(loss, non_blocking=True)
+            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self.h_status.data_ptr()),
+                      ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self.step_count = count  # the capture executed nothing
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        self._graphs[k], self._graph_loss[k] = g, loss
+
     def step_device(self):
+        self._advanced = False
         loss = self.forward_backward()
         self.step_count += 1
         if self.world_size > 1 and self.comm_stream is not None:
