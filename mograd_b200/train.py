@@ -130,6 +130,13 @@ class _Model:
         self._graph_loss = [None, None]
         self._eager_steps = 0
         self._advanced = False      # this step's optimiser launches have already advanced the device step counter
+        # dW products on a second stream (see _linear_bwd): single-GPU runs, MOGRAD_B200_DW_STREAM=0 switches it off
+        # (data-parallel runs keep one compute stream: their gradient buckets are handed to the communication
+        # stream in the order the backward pass finishes them)
+        self.dw_overlap = (self.device.type == "cuda" and world_size == 1 and
+                           os.environ.get("MOGRAD_B200_DW_STREAM", "1") != "0")
+        self.dw_stream = torch.cuda.Stream(device=self.device) if self.dw_overlap else None
+        self._dw_done = {}          # name of the dY buffer -> event: the dW product that reads it has finished
         # 1-based step number on the device: a replayed launch cannot carry a new scalar
         self.d_step = torch.zeros(1, dtype=torch.int32, device=self.device) if self.device.type == "cuda" else None
 
@@ -223,6 +230,36 @@ class _Model:
         else:
             K.adamw_step(s.w[lo:hi], s.g[lo:hi], s.m[lo:hi], s.v[lo:hi], s.master[lo:hi], o.lr, o.beta1, o.beta2,
                          o.eps, o.weight_decay, self.step_count, grad_scale=1.0 / self.world_size)
+
+    # ---- backward of a linear layer, dW optionally on its own stream -----------------------
+    def _linear_bwd(self, tag, dy, x, w, dx_out, dw_out, db_out=None, **kw):
+        """dX on the current stream; dW (and db) either behind it or, with dw_overlap, on a second stream that only
+        waits for dY: nothing downstream needs dW before the optimiser, so its CTAs can fill the SMs that the tail
+        wave of the dX chain leaves idle.  `tag` names the dY buffer; _dy_free(tag) must precede whatever overwrites
+        that buffer."""
+        if not self.dw_overlap:
+            K.matmul_bias_bt_bwd(dy, x, w, dx_out=dx_out, dw_out=dw_out, db_out=db_out, need_db=db_out is not None, **kw)
+            return
+        main = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        K.matmul_bias_bt_bwd(dy, x, w, dx_out=dx_out, need_dw=False, need_db=False, **kw)
+        side = self.dw_stream
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            K.matmul_bias_bt_bwd(dy, x, w, need_dx=False, dw_out=dw_out, db_out=db_out, need_db=db_out is not None)
+            done = torch.cuda.Event()
+            done.record(side)
+        self._dw_done[tag] = done
+
+    def _dy_free(self, tag):
+        ev = self._dw_done.pop(tag, None)
+        if ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+
+    def _dw_join(self):
+        for tag in list(self._dw_done):
+            self._dy_free(tag)
 
     # ---- host-facing call: host buffers in, loss out -------------------------------------
     def step(self, host_inputs, host_targets, prefetch=None) -> float:
@@ -502,26 +539,29 @@ class TinyTransformer(_Model):
 
         # ---- backward
         dx = self.t_dx  # gradient w.r.t. the current block's output
-        K.matmul_bias_bt_bwd(dl, self.x[L], P["lm_head"], dx_out=dx, dw_out=G["lm_head"], need_db=False)
+        self._linear_bwd("dl", dl, self.x[L], P["lm_head"], dx, G["lm_head"])
         self._grads_ready_down_to(st.range["lm_head"][0])
         for l in range(L - 1, -1, -1):
             sv, x = self.saved[l], self.x[l]
             # FFN: out = h + W2 relu(W1 ln2 + b1)
-            K.matmul_bias_bt_bwd(dx, sv["f1"], P[f"W2_{l}"], dx_out=self.t_ff, dw_out=G[f"W2_{l}"], need_db=False,
-                                 relu_y=None if self.relu_bits else sv["f1"], relu_bits=sv.get("f1_bits"))
-            K.matmul_bias_bt_bwd(self.t_ff, sv["ln2"], P[f"W1_{l}"], dx_out=self.t_b, dw_out=G[f"W1_{l}"],
-                                 db_out=G[f"b1_{l}"])
+            self._dy_free("t_ff")  # the previous block's W1 dW has read t_ff
+            self._linear_bwd("dx", dx, sv["f1"], P[f"W2_{l}"], self.t_ff, G[f"W2_{l}"],
+                             relu_y=None if self.relu_bits else sv["f1"], relu_bits=sv.get("f1_bits"))
+            self._linear_bwd("t_ff", self.t_ff, sv["ln2"], P[f"W1_{l}"], self.t_b, G[f"W1_{l}"], db_out=G[f"b1_{l}"])
+            self._dy_free("dx")
             K.layer_norm_bwd_dispatch(self.t_b, sv["h"], P[f"g2_{l}"], dx_out=dx, dgamma_out=G[f"g2_{l}"],
                                       dbeta_out=G[f"be2_{l}"], dx_residual=dx)  # dx is now dL/dh
             # attention: h = x + Wo ctx
-            K.matmul_bias_bt_bwd(dx, sv["ctx"], P[f"Wo{l}"], dx_out=self.t_b, dw_out=G[f"Wo{l}"], need_db=False)
+            self._linear_bwd("dx", dx, sv["ctx"], P[f"Wo{l}"], self.t_b, G[f"Wo{l}"])
             q4, k4, v4 = self._heads(sv["qkv"])
+            self._dy_free("t_dqkv")  # the previous block's Wqkv dW has read t_dqkv
             K.flash_attn_bwd_dispatch(self.t_b.view(B, S, H, Dh), sv["ctx"].view(B, S, H, Dh), q4, k4, v4, None,
                                       sv["lse"], None, True, False, out=self._heads(self.t_dqkv), o_bshd=True)
-            K.matmul_bias_bt_bwd(self.t_dqkv, sv["ln1"], P[f"Wqkv{l}"], dx_out=self.t_b, dw_out=G[f"Wqkv{l}"],
-                                 need_db=False)
+            self._linear_bwd("t_dqkv", self.t_dqkv, sv["ln1"], P[f"Wqkv{l}"], self.t_b, G[f"Wqkv{l}"])
+            self._dy_free("dx")
             K.layer_norm_bwd_dispatch(self.t_b, x, P[f"g1_{l}"], dx_out=dx, dgamma_out=G[f"g1_{l}"],
                                       dbeta_out=G[f"be1_{l}"], dx_residual=dx)  # dx is now dL/dx
             self._grads_ready_down_to(st.range[f"Wqkv{l}"][0])
         K.scatter_add_rows(dx, tok, self.V, out=G["embed"])
+        self._dw_join()
         return loss
