@@ -128,11 +128,12 @@ class _Model:
                           os.environ.get("MOGRAD_B200_GRAPH", "1") != "0")
         self._graphs = [None, None]
         self._graph_loss = [None, None]
+        self.graph_launches = [0, 0]  # kernels of this library recorded in each slot's graph (= launched per replay)
         self._eager_steps = 0
         self._advanced = False      # this step's optimiser launches have already advanced the device step counter
-        # dW products on a second stream (see _linear_bwd): single-GPU runs, MOGRAD_B200_DW_STREAM=0 switches it off
-        # (data-parallel runs keep one compute stream: their gradient buckets are handed to the communication
-        # stream in the order the backward pass finishes them)
+        # dW products on a second stream inside captured steps (see _linear_bwd): single-GPU runs,
+        # MOGRAD_B200_DW_STREAM=0 switches it off (data-parallel runs keep one compute stream: their gradient buckets
+        # are handed to the communication stream in the order the backward pass finishes them)
         self.dw_overlap = (self.device.type == "cuda" and world_size == 1 and
                            os.environ.get("MOGRAD_B200_DW_STREAM", "1") != "0")
         self.dw_stream = torch.cuda.Stream(device=self.device) if self.dw_overlap else None
@@ -237,7 +238,9 @@ class _Model:
         waits for dY: nothing downstream needs dW before the optimiser, so its CTAs can fill the SMs that the tail
         wave of the dX chain leaves idle.  `tag` names the dY buffer; _dy_free(tag) must precede whatever overwrites
         that buffer."""
-        if not self.dw_overlap:
+        # only while a step is being captured into a graph: launched kernel by kernel, the extra event records and
+        # waits cost the host more than the overlap gives the device on small models
+        if not (self.dw_overlap and torch.cuda.is_current_stream_capturing()):
             K.matmul_bias_bt_bwd(dy, x, w, dx_out=dx_out, dw_out=dw_out, db_out=db_out, need_db=db_out is not None, **kw)
             return
         main = torch.cuda.current_stream(self.device)
@@ -304,14 +307,30 @@ class _Model:
         side.wait_stream(torch.cuda.current_stream(self.device))
         g = torch.cuda.CUDAGraph()
         count = self.step_count
+        n0 = _lib.load().mograd_b200_launch_count()
         with torch.cuda.graph(g, stream=side):
             loss = self.step_device()
             self.h_loss.copy_(loss, non_blocking=True)
             _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self.h_status.data_ptr()),
                       ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
         self.step_count = count  # the capture executed nothing
+        self.graph_launches[k] = int(_lib.load().mograd_b200_launch_count() - n0)
         torch.cuda.current_stream(self.device).wait_stream(side)
         self._graphs[k], self._graph_loss[k] = g, loss
+
+    def step_resident(self, k: int):
+        """One train step on the batch already resident in input slot k, no host input or output: replays the
+        slot's captured graph (captured on first use after two eager steps) or, without graphs, launches the step
+        kernel by kernel.  Returns the loss as a device tensor."""
+        self.use_slot(k)
+        if self.use_graph and self._graphs[k] is None and self._eager_steps >= 2:
+            self._capture(k)
+        if self.use_graph and self._graphs[k] is not None:
+            self._graphs[k].replay()
+            self.step_count += 1
+            return self._graph_loss[k]
+        self._eager_steps += 1
+        return self.step_device()
 
     def step_device(self):
         self._advanced = False
