@@ -117,6 +117,7 @@ class _Model:
         self.time_exposed = False   # record how long the main stream waits for each bucket's all-reduce
         self.exposed_events = []    # per step: [(lo, hi, before, after)] CUDA events around each wait
         self._staged = None         # input slot whose host->device copy has been issued ahead of its step
+        self._inflight = None       # (slot, host inputs) of a step that step(launch_next=True) has already queued
         self._slot = 0
         # step() replays a captured CUDA graph of the whole step (one per input slot) after two eager steps: the
         # host then issues one launch per step instead of several hundred, which matters whenever step() must hand
@@ -152,6 +153,10 @@ class _Model:
         on_gpu = dev.type == "cuda"
         self.h_loss = torch.empty((), dtype=torch.float32).pin_memory() if on_gpu else torch.empty(())
         self.h_status = torch.zeros(4, dtype=torch.int32).pin_memory() if on_gpu else torch.zeros(4, dtype=torch.int32)
+        # per input slot, for the slot's captured graph: pinned result words and an event recorded behind each replay
+        self._h_loss = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)] if on_gpu else None
+        self._h_status = [torch.zeros(4, dtype=torch.int32).pin_memory() for _ in range(2)] if on_gpu else None
+        self._done = [torch.cuda.Event() for _ in range(2)] if on_gpu else None
         self.copy_stream = torch.cuda.Stream(device=dev) if on_gpu else None
         self._copied = [None, None]  # event per slot: its host->device copy has finished
 
@@ -265,40 +270,73 @@ class _Model:
             self._dy_free(tag)
 
     # ---- host-facing call: host buffers in, loss out -------------------------------------
-    def step(self, host_inputs, host_targets, prefetch=None) -> float:
+    def step(self, host_inputs, host_targets, prefetch=None, launch_next=False) -> float:
         """One train step from pinned host tensors; returns the loss as a Python float (device->host read).
 
         prefetch=(next_inputs, next_targets): the next step's batch; its host->device copy is issued on a second
         stream right after this step's kernels are queued, so it runs under them, and the next step(next_inputs,
-        ...) finds its batch on the device.  Raises KernelError when a kernel's bounded wait gave up during the
-        step (the status word rides back with the loss)."""
+        ...) finds its batch on the device.
+
+        launch_next=True (with prefetch, once the step is replayed from its captured graphs) commits to that next
+        step: it is queued behind this one before this call waits for its own loss, so the device never idles
+        between steps while the host reads a result and queues the next graph; the call still returns this step's
+        loss (each slot's graph writes its loss and status to pinned words of its own).  The caller must then make
+        its next call step(next_inputs, next_targets, ...).
+
+        Raises KernelError when a kernel's bounded wait gave up during the step (the status word rides back with
+        the loss)."""
         main = torch.cuda.current_stream(self.device)
-        if self._staged is not None and self._staged[1] is host_inputs:
-            k, self._staged = self._staged[0], None
+        if self._inflight is not None:
+            k, expected = self._inflight
+            self._inflight = None
+            if expected is not host_inputs:
+                raise ValueError("Model.step: the previous call committed to a different next batch (launch_next)")
             self.use_slot(k)
-            main.wait_event(self._copied[k])
+            launched = True
         else:
-            self._staged = None
-            self.d_inputs.copy_(host_inputs, non_blocking=True)
-            self.d_targets.copy_(host_targets, non_blocking=True)
-        k = self._slot
-        if self.use_graph and self._graphs[k] is None and self._eager_steps >= 2:
-            self._capture(k)
-        if self.use_graph and self._graphs[k] is not None:
-            self._graphs[k].replay()
-            self.step_count += 1
+            launched = False
+            if self._staged is not None and self._staged[1] is host_inputs:
+                k, self._staged = self._staged[0], None
+                self.use_slot(k)
+                main.wait_event(self._copied[k])
+            else:
+                self._staged = None
+                self.d_inputs.copy_(host_inputs, non_blocking=True)
+                self.d_targets.copy_(host_targets, non_blocking=True)
+            k = self._slot
+            if self.use_graph and self._graphs[k] is None and self._eager_steps >= 2:
+                self._capture(k)
+        graph = self.use_graph and self._graphs[k] is not None
+        if graph:
+            if not launched:
+                self._graphs[k].replay()
+                self._done[k].record(main)
+                self.step_count += 1
+            h_loss, h_status = self._h_loss[k], self._h_status[k]
         else:
             loss = self.step_device()
             self._eager_steps += 1
-            self.h_loss.copy_(loss, non_blocking=True)
-            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self.h_status.data_ptr()),
+            h_loss, h_status = self.h_loss, self.h_status
+            h_loss.copy_(loss, non_blocking=True)
+            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(h_status.data_ptr()),
                       ctypes.c_void_p(main.cuda_stream))
         if prefetch is not None:
             self._prefetch(*prefetch)
-        main.synchronize()
-        if int(self.h_status[0]) != 0:
+            kn = k ^ 1
+            if launch_next and graph and self._graphs[kn] is not None:
+                # the next step, queued now: its batch copy is ordered before it by the slot's event
+                main.wait_event(self._copied[kn])
+                self._graphs[kn].replay()
+                self._done[kn].record(main)
+                self.step_count += 1
+                self._inflight, self._staged = (kn, prefetch[0]), None
+        if graph:
+            self._done[k].synchronize()
+        else:
+            main.synchronize()
+        if int(h_status[0]) != 0:
             _lib.check_device_status("Model.step")
-        return float(self.h_loss.item())
+        return float(h_loss.item())
 
     def _capture(self, k):
         """Records one whole step reading input slot k (kernels, the loss and status copies to pinned host words)
@@ -310,8 +348,8 @@ class _Model:
         n0 = _lib.load().mograd_b200_launch_count()
         with torch.cuda.graph(g, stream=side):
             loss = self.step_device()
-            self.h_loss.copy_(loss, non_blocking=True)
-            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self.h_status.data_ptr()),
+            self._h_loss[k].copy_(loss, non_blocking=True)
+            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self._h_status[k].data_ptr()),
                       ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
         self.step_count = count  # the capture executed nothing
         self.graph_launches[k] = int(_lib.load().mograd_b200_launch_count() - n0)

@@ -163,12 +163,14 @@ def test_graph_replay_of_the_step_matches_eager_launches(cuda, oracle):
     import torch
     from mograd_b200.train import MLP, AdamWConfig, TinyTransformer
 
-    def run(make, batches, graph):
+    def run(make, batches, graph, ahead=False):
         m = make()
         m.use_graph = graph
-        losses = [m.step(*batches[i & 1], prefetch=batches[(i + 1) & 1]) for i in range(6)]
+        losses = [m.step(*batches[i & 1], prefetch=batches[(i + 1) & 1], launch_next=ahead and i < 5)
+                  for i in range(6)]
         torch.cuda.synchronize()
         assert (m._graphs[0] is not None and m._graphs[1] is not None) == graph
+        assert m._inflight is None
         return losses, m.store.master.clone(), m.store.w.clone(), int(m.d_step.item())
 
     rng = np.random.default_rng(21)
@@ -182,6 +184,9 @@ def test_graph_replay_of_the_step_matches_eager_launches(cuda, oracle):
     assert le == lg, (le, lg)
     assert torch.equal(me, mg) and torch.equal(we, wg)
     assert le[-1] < le[0]  # and the optimiser does make progress
+    # with each step's successor queued before the step's own loss is read (launch_next): same losses, same state
+    la, ma, wa, sa = run(mk, b, True, ahead=True)
+    assert sa == 6 and la == le and torch.equal(ma, me) and torch.equal(wa, we)
 
     mk = lambda: TinyTransformer(65, 128, 512, 2, 2, 2, 256, dtype=torch.bfloat16, device=cuda, seed=3, init_std=0.05,
                                  opt=AdamWConfig(lr=1e-3, weight_decay=0.1))
@@ -189,8 +194,10 @@ def test_graph_replay_of_the_step_matches_eager_launches(cuda, oracle):
           torch.from_numpy(rng.integers(0, 65, (2, 256)).astype(np.int64)).pin_memory()) for _ in range(2)]
     le, _, _, se = run(mk, b, False)
     lg, _, _, sg = run(mk, b, True)
-    assert se == sg == 6
+    la, _, _, sa = run(mk, b, True, ahead=True)
+    assert se == sg == sa == 6
     assert all(abs(a - c) <= 1e-3 * abs(a) for a, c in zip(le, lg)), (le, lg)
+    assert all(abs(a - c) <= 1e-3 * abs(a) for a, c in zip(le, la)), (le, la)
 
 
 def test_dw_products_on_their_own_stream_give_the_same_gradients(cuda, oracle):
