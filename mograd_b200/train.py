@@ -493,14 +493,15 @@ class MLP(_Model):
         for i in range(self.nl - 1, 0, -1):
             inp = self.act[i - 1] if i > 1 else self.ln_out
             dst = self.dact[i - 1] if i > 1 else self.dln
-            K.matmul_bias_bt_bwd(dy, inp, P[f"W{i}"], dx_out=dst, dw_out=G[f"W{i}"], db_out=G[f"b{i}"],
-                                 relu_y=self.act[i - 1] if i > 1 else None)
+            self._linear_bwd(f"dy{i}", dy, inp, P[f"W{i}"], dst, G[f"W{i}"], db_out=G[f"b{i}"],
+                             relu_y=self.act[i - 1] if i > 1 else None)
             self._grads_ready_down_to(self.store.range[f"W{i}"][0])
             dy = dst
         K.layer_norm_bwd_dispatch(self.dln, self.act[0], P["ln_g"], dx_out=self.dln, dgamma_out=G["ln_g"],
                                   dbeta_out=G["ln_b"])
         K.relu_grad(self.act[0], self.dln)
         K.matmul_bias_bt_bwd(self.dln, x, P["W0"], need_dx=False, dw_out=G["W0"], db_out=G["b0"])
+        self._dw_join()
         return loss
 
 
