@@ -177,8 +177,11 @@ __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen + C::OFF_BAR + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x;  // key tile
-  const int bh = blockIdx.y;
+  // D = 128: (batch, head) runs fastest in launch order, the key tile slowest: with a causal mask the CTAs of key
+  // tile 0 (the most query tiles) all start first and the single-tile CTAs last, so the grid ends on short CTAs
+  // (3% at B4 H16 S4096).  D = 64 keeps the key tile fastest: there the same order measured 1-2% slower.
+  const int j = (D == 128) ? blockIdx.y : blockIdx.x;  // key tile
+  const int bh = (D == 128) ? blockIdx.x : blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int nq = (p.S + 127) / 128;
   const int i0 = p.causal ? j : 0;
@@ -1308,7 +1311,8 @@ int run_bwd(const void* dy, const void* q, const void* k, const void* v, AttnPar
   auto kern = p.bias ? attn_bwd_tc_kernel<D, T, true> : attn_bwd_tc_kernel<D, T, false>;
   int rc = set_smem(kern, C::SMEM);
   if (rc != MGB_OK) return rc;
-  dim3 grid(static_cast<unsigned>((p.S + 127) / 128), static_cast<unsigned>(p.B * p.H));
+  const unsigned nkt = static_cast<unsigned>((p.S + 127) / 128), nbh = static_cast<unsigned>(p.B * p.H);
+  dim3 grid(D == 128 ? nbh : nkt, D == 128 ? nkt : nbh);
   launch_pdl(kern, grid, dim3(C::THREADS), C::SMEM, st, mq, mk, mv, mdo, mdq, mdk, mdv, p);
   return check_launch("attn_bwd_tc_kernel");
 }
