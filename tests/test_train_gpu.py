@@ -187,6 +187,15 @@ def test_graph_replay_of_the_step_matches_eager_launches(cuda, oracle):
     # with each step's successor queued before the step's own loss is read (launch_next): same losses, same state
     la, ma, wa, sa = run(mk, b, True, ahead=True)
     assert sa == 6 and la == le and torch.equal(ma, me) and torch.equal(wa, we)
+    # a call that committed to its successor refuses any other batch next
+    m = mk()
+    for i in range(5):
+        m.step(*b[i & 1], prefetch=b[(i + 1) & 1], launch_next=i == 4)
+    assert m._inflight is not None
+    other = (b[1][0].clone().pin_memory(), b[1][1])
+    with pytest.raises(ValueError):
+        m.step(*other)
+    torch.cuda.synchronize()
 
     mk = lambda: TinyTransformer(65, 128, 512, 2, 2, 2, 256, dtype=torch.bfloat16, device=cuda, seed=3, init_std=0.05,
                                  opt=AdamWConfig(lr=1e-3, weight_decay=0.1))
