@@ -144,16 +144,14 @@ class _Model:
 
     # ---- host-side input staging ---------------------------------------------------------
     def _setup_io(self, in_shape, in_dtype, tgt_shape):
-        """Two device slots for the batch (the copy of step k+1 may run while step k computes), a pinned word for
-        the loss and pinned words for the device status."""
+        """Two device slots for the batch (the copy of step k+1 may run while step k computes), each with a pinned
+        word for the loss and pinned words for the device status of the step that reads it."""
         dev = self.device
         self._in = [torch.empty(in_shape, dtype=in_dtype, device=dev) for _ in range(2)]
         self._tgt = [torch.empty(tgt_shape, dtype=torch.int64, device=dev) for _ in range(2)]
         self.d_inputs, self.d_targets = self._in[0], self._tgt[0]
         on_gpu = dev.type == "cuda"
-        self.h_loss = torch.empty((), dtype=torch.float32).pin_memory() if on_gpu else torch.empty(())
-        self.h_status = torch.zeros(4, dtype=torch.int32).pin_memory() if on_gpu else torch.zeros(4, dtype=torch.int32)
-        # per input slot, for the slot's captured graph: pinned result words and an event recorded behind each replay
+        # per input slot: pinned result words and an event recorded behind each step that reads the slot
         self._h_loss = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)] if on_gpu else None
         self._h_status = [torch.zeros(4, dtype=torch.int32).pin_memory() for _ in range(2)] if on_gpu else None
         self._done = [torch.cuda.Event() for _ in range(2)] if on_gpu else None
@@ -277,11 +275,11 @@ class _Model:
         stream right after this step's kernels are queued, so it runs under them, and the next step(next_inputs,
         ...) finds its batch on the device.
 
-        launch_next=True (with prefetch, once the step is replayed from its captured graphs) commits to that next
-        step: it is queued behind this one before this call waits for its own loss, so the device never idles
-        between steps while the host reads a result and queues the next graph; the call still returns this step's
-        loss (each slot's graph writes its loss and status to pinned words of its own).  The caller must then make
-        its next call step(next_inputs, next_targets, ...).
+        launch_next=True (with prefetch) commits to that next step: it is queued behind this one before this call
+        waits for its own loss, so the device never idles between steps while the host reads a result and queues
+        the next step (one graph launch on a single GPU, several hundred kernel launches otherwise); the call
+        still returns this step's loss (each input slot has pinned result words of its own).  The caller must then
+        make its next call step(next_inputs, next_targets, ...).
 
         Raises KernelError when a kernel's bounded wait gave up during the step (the status word rides back with
         the loss)."""
@@ -292,9 +290,7 @@ class _Model:
             if expected is not host_inputs:
                 raise ValueError("Model.step: the previous call committed to a different next batch (launch_next)")
             self.use_slot(k)
-            launched = True
         else:
-            launched = False
             if self._staged is not None and self._staged[1] is host_inputs:
                 k, self._staged = self._staged[0], None
                 self.use_slot(k)
@@ -304,39 +300,39 @@ class _Model:
                 self.d_inputs.copy_(host_inputs, non_blocking=True)
                 self.d_targets.copy_(host_targets, non_blocking=True)
             k = self._slot
-            if self.use_graph and self._graphs[k] is None and self._eager_steps >= 2:
-                self._capture(k)
-        graph = self.use_graph and self._graphs[k] is not None
-        if graph:
-            if not launched:
-                self._graphs[k].replay()
-                self._done[k].record(main)
-                self.step_count += 1
-            h_loss, h_status = self._h_loss[k], self._h_status[k]
+            self._launch(k)
+        if prefetch is not None:
+            self._prefetch(*prefetch)
+            if launch_next:
+                # the next step, queued now: its batch copy is ordered before it by the slot's event
+                kn = k ^ 1
+                main.wait_event(self._copied[kn])
+                self._launch(kn)
+                self.use_slot(k)
+                self._inflight, self._staged = (kn, prefetch[0]), None
+        self._done[k].synchronize()
+        if int(self._h_status[k][0]) != 0:
+            _lib.check_device_status("Model.step")
+        return float(self._h_loss[k].item())
+
+    def _launch(self, k):
+        """Queues one step on the batch in input slot k (graph replay when the slot's graph exists, kernel by kernel
+        otherwise), the copies of its loss and of the device status to the slot's pinned words, and the slot's
+        event behind them."""
+        main = torch.cuda.current_stream(self.device)
+        self.use_slot(k)
+        if self.use_graph and self._graphs[k] is None and self._eager_steps >= 2:
+            self._capture(k)
+        if self.use_graph and self._graphs[k] is not None:
+            self._graphs[k].replay()
+            self.step_count += 1
         else:
             loss = self.step_device()
             self._eager_steps += 1
-            h_loss, h_status = self.h_loss, self.h_status
-            h_loss.copy_(loss, non_blocking=True)
-            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(h_status.data_ptr()),
+            self._h_loss[k].copy_(loss, non_blocking=True)
+            _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self._h_status[k].data_ptr()),
                       ctypes.c_void_p(main.cuda_stream))
-        if prefetch is not None:
-            self._prefetch(*prefetch)
-            kn = k ^ 1
-            if launch_next and graph and self._graphs[kn] is not None:
-                # the next step, queued now: its batch copy is ordered before it by the slot's event
-                main.wait_event(self._copied[kn])
-                self._graphs[kn].replay()
-                self._done[kn].record(main)
-                self.step_count += 1
-                self._inflight, self._staged = (kn, prefetch[0]), None
-        if graph:
-            self._done[k].synchronize()
-        else:
-            main.synchronize()
-        if int(h_status[0]) != 0:
-            _lib.check_device_status("Model.step")
-        return float(h_loss.item())
+        self._done[k].record(main)
 
     def _capture(self, k):
         """Records one whole step reading input slot k (kernels, the loss and status copies to pinned host words)

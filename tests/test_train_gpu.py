@@ -187,6 +187,9 @@ def test_graph_replay_of_the_step_matches_eager_launches(cuda, oracle):
     # with each step's successor queued before the step's own loss is read (launch_next): same losses, same state
     la, ma, wa, sa = run(mk, b, True, ahead=True)
     assert sa == 6 and la == le and torch.equal(ma, me) and torch.equal(wa, we)
+    # ... and the same without graphs (the successor's kernels are launched one by one before the loss is read)
+    la, ma, wa, sa = run(mk, b, False, ahead=True)
+    assert sa == 6 and la == le and torch.equal(ma, me) and torch.equal(wa, we)
     # a call that committed to its successor refuses any other batch next
     m = mk()
     for i in range(5):
