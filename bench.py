@@ -550,9 +550,9 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # Resident-input steps go through Model.step_resident(): on one GPU that replays the step's captured CUDA graph
-    # (captured during the warm-up: two steps launched kernel by kernel, then one capture per input slot), on
-    # several GPUs it launches the step kernel by kernel.
+    # Resident-input steps go through Model.step_resident(), which replays the step's captured CUDA graph(s)
+    # (captured during the warm-up: two steps launched kernel by kernel, then one capture per input slot; with
+    # several GPUs the capture is cut where a gradient bucket is complete and the all-reduces run between the cuts).
     for i in range(max(3, args.warmup) + 3):
         model.step_resident(i & 1)
     barrier()
@@ -580,9 +580,9 @@ def main():
 
     # end to end through the host-facing call: host batch in, loss out, every step
     # (untimed: two eager steps, then the steps in which Model.step() captures its two CUDA graphs, one per slot)
-    # Every call copies its successor's batch to the device while its own step runs and (launch_next, single-GPU
-    # graph replay) queues that successor before it waits for its own loss; the last call of each loop queues
-    # nothing, so the timed region holds exactly --steps steps.
+    # Every call copies its successor's batch to the device while its own step runs and (launch_next) queues that
+    # successor before it waits for its own loss; the last call of each loop queues nothing, so the timed region
+    # holds exactly --steps steps.
     for i in range(6):
         model.step(*batches[i & 1], prefetch=batches[(i + 1) & 1], launch_next=i < 5)
     barrier()
@@ -621,8 +621,10 @@ def main():
                     e2e=dict(value=round(e2e_val, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4),
                     gpu_launches=int(launches), loss=round(float(last), 4))
         line["config"]["batches"] = "two seeded batches per rank, alternated every step"
-        line["config"]["launch"] = ("one captured CUDA graph per step, replayed" if model._graphs[0] is not None
-                                    else "kernel by kernel")
+        line["config"]["launch"] = ("kernel by kernel" if model._graphs[0] is None else
+                                    "one captured CUDA graph per step, replayed" if world == 1 else
+                                    "captured CUDA graphs cut at the gradient-bucket boundaries, replayed, with the "
+                                    "NCCL all-reduces issued between them")
         if dp is not None:
             line["dp"] = dp
             line["dp_in_sync"] = dp["in_sync"]

@@ -98,6 +98,29 @@ class AdamWConfig:
     weight_decay: float = 0.1
 
 
+class _SegmentedStep:
+    """Replay of a data-parallel step: its graphs and, between them, the all-reduces of the buckets they complete,
+    then AdamW bucket by bucket as each all-reduce finishes (the same order as the kernel-by-kernel step)."""
+
+    def __init__(self, model, segments):
+        self.model, self.segments = model, segments
+
+    def replay(self):
+        m = self.model
+        m._advanced = False
+        for kind, what in self.segments:
+            if kind == "graph":
+                what.replay()
+            else:
+                for i in what:
+                    m._exchange_bucket(i)
+        main = torch.cuda.current_stream(m.device)
+        for lo, hi, done in m._bucket_done:
+            main.wait_event(done)
+            m.optimizer_step(lo, hi)
+        m._bucket_done.clear()
+
+
 class _Model:
     """Shared plumbing: flat params, bucketed gradient exchange, optimiser, host-facing step()."""
 
@@ -121,12 +144,12 @@ class _Model:
         self._slot = 0
         # step() replays a captured CUDA graph of the whole step (one per input slot) after two eager steps: the
         # host then issues one launch per step instead of several hundred, which matters whenever step() must hand
-        # the loss back before the next step can be queued.  Data-parallel runs stay eager: with the bucket
-        # all-reduces captured (NCCL on the communication stream, joined by events) the two-GPU test produced the
-        # same losses but took minutes instead of seconds and did not shut down cleanly.  MOGRAD_B200_GRAPH=0
-        # switches the replay off.
-        self.use_graph = (self.device.type == "cuda" and world_size == 1 and
-                          os.environ.get("MOGRAD_B200_GRAPH", "1") != "0")
+        # the loss back before the next step can be queued.  A data-parallel step is captured as a sequence of
+        # graphs cut at the points where a gradient bucket is complete; the all-reduces themselves stay ordinary
+        # NCCL calls on the communication stream between the replays (captured together with the step they made the
+        # two-GPU test take minutes instead of seconds).  MOGRAD_B200_GRAPH=0 switches the replay off.
+        self.use_graph = self.device.type == "cuda" and os.environ.get("MOGRAD_B200_GRAPH", "1") != "0"
+        self._cap = None            # state of a segmented capture in progress (data-parallel runs)
         self._graphs = [None, None]
         self._graph_loss = [None, None]
         self.graph_launches = [0, 0]  # kernels of this library recorded in each slot's graph (= launched per replay)
@@ -135,8 +158,7 @@ class _Model:
         # dW products on a second stream inside captured steps (see _linear_bwd): single-GPU runs,
         # MOGRAD_B200_DW_STREAM=0 switches it off (data-parallel runs keep one compute stream: their gradient buckets
         # are handed to the communication stream in the order the backward pass finishes them)
-        self.dw_overlap = (self.device.type == "cuda" and world_size == 1 and
-                           os.environ.get("MOGRAD_B200_DW_STREAM", "1") != "0")
+        self.dw_overlap = self.device.type == "cuda" and os.environ.get("MOGRAD_B200_DW_STREAM", "1") != "0"
         self.dw_stream = torch.cuda.Stream(device=self.device) if self.dw_overlap else None
         self._dw_done = {}          # name of the dY buffer -> event: the dW product that reads it has finished
         # 1-based step number on the device: a replayed launch cannot carry a new scalar
@@ -198,21 +220,38 @@ class _Model:
             return
         import torch.distributed as dist
 
+        ready = []
         while self._next_bucket < len(self.buckets) and self.buckets[self._next_bucket][0] >= offset:
-            lo, hi = self.buckets[self._next_bucket]
-            if self.comm_stream is None:  # host tensors (gloo): no streams to order
-                dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
-            else:
-                ev = torch.cuda.Event()
-                ev.record(torch.cuda.current_stream(self.device))
-                self.comm_stream.wait_event(ev)
-                with torch.cuda.stream(self.comm_stream):
-                    dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
-                    done = torch.cuda.Event()
-                    done.record(self.comm_stream)
-                self._bucket_done.append((lo, hi, done))
-            self.exchanged.append((lo, hi))
+            ready.append(self._next_bucket)
             self._next_bucket += 1
+        if not ready:
+            return
+        if self._cap is not None:
+            # a step is being captured: close the graph that produced these buckets, note the exchange to be issued
+            # at this point of every replay, open the next graph
+            self._end_segment()
+            self._cap["segments"].append(("exchange", ready))
+            self._begin_segment()
+            return
+        for i in ready:
+            self._exchange_bucket(i)
+
+    def _exchange_bucket(self, i):
+        import torch.distributed as dist
+
+        lo, hi = self.buckets[i]
+        if self.comm_stream is None:  # host tensors (gloo): no streams to order
+            dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
+        else:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                dist.all_reduce(self.store.g[lo:hi], op=dist.ReduceOp.SUM, group=self.pg)
+                done = torch.cuda.Event()
+                done.record(self.comm_stream)
+            self._bucket_done.append((lo, hi, done))
+        self.exchanged.append((lo, hi))
 
     def _finish_exchange(self):
         if self.world_size == 1:
@@ -334,9 +373,52 @@ class _Model:
                       ctypes.c_void_p(main.cuda_stream))
         self._done[k].record(main)
 
+    def _begin_segment(self):
+        g = torch.cuda.CUDAGraph()
+        # thread-local mode: NCCL's watchdog thread makes CUDA calls of its own while this thread captures
+        g.capture_begin(pool=self._cap["pool"], capture_error_mode="thread_local")
+        self._cap["graph"] = g
+
+    def _end_segment(self):
+        self._dw_join()  # streams forked inside a graph are joined inside it
+        self._cap["graph"].capture_end()
+        self._cap["segments"].append(("graph", self._cap["graph"]))
+
+    def _capture_segments(self, k):
+        """Data-parallel form of _capture: the forward and backward pass of a step reading input slot k as a sequence
+        of graphs cut wherever a gradient bucket is complete, with the bucket's all-reduce noted between them; the
+        replay object issues graphs and all-reduces in that order and then the per-bucket optimiser launches."""
+        main = torch.cuda.current_stream(self.device)
+        side = torch.cuda.Stream(device=self.device)
+        torch.cuda.synchronize(self.device)
+        side.wait_stream(main)
+        count = self.step_count
+        n0 = _lib.load().mograd_b200_launch_count()
+        self._cap = dict(pool=torch.cuda.graph_pool_handle(), segments=[], graph=None)
+        self._next_bucket = 0
+        try:
+            with torch.cuda.stream(side):
+                self._begin_segment()
+                loss = self.forward_backward()
+                self._grads_ready_down_to(0)
+                self._h_loss[k].copy_(loss, non_blocking=True)
+                _lib.call("mograd_b200_device_status_async", ctypes.c_void_p(self._h_status[k].data_ptr()),
+                          ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+                self._end_segment()
+            segments = self._cap["segments"]
+        finally:
+            self._cap = None
+            self._next_bucket = 0
+        self.step_count = count
+        self.graph_launches[k] = int(_lib.load().mograd_b200_launch_count() - n0)
+        main.wait_stream(side)
+        self._graphs[k], self._graph_loss[k] = _SegmentedStep(self, segments), loss
+
     def _capture(self, k):
         """Records one whole step reading input slot k (kernels, the loss and status copies to pinned host words)
         into a CUDA graph.  Nothing runs during the capture; the caller replays it."""
+        if self.world_size > 1:
+            return self._capture_segments(k)
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         g = torch.cuda.CUDAGraph()

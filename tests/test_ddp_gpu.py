@@ -1,6 +1,7 @@
 """Data-parallel train steps over NCCL on two GPUs: the gradient exchange the product path runs (bf16 buckets on a
 side stream, ordered by events, overlapped with the backward pass, AdamW bucket by bucket) against a plain
-exchange of the same local gradients, and bit-identical replicas after several steps.  Needs two GPUs; with one
+exchange of the same local gradients, bit-identical replicas after several steps, and the replayed form of the step
+(graphs cut at the bucket boundaries, all-reduces between them) against the same steps launched kernel by kernel.  Needs two GPUs; with one
 it is skipped (the gloo test covers the bucket logic on CPU ranks)."""
 import os
 import socket
@@ -49,9 +50,19 @@ def _worker(rank, world, port, q):
         m.d_targets.copy_(tgt)
         err = m.check_data_parallel()
         nb = len(m.buckets)
-        losses = [m.step(tok, tgt) for _ in range(4)]
+        losses = [m.step(tok, tgt) for _ in range(6)]  # two launched kernel by kernel, then the captured graphs
         sync = m.replicas_in_sync()
-        q.put((rank, dict(err=err, buckets=nb, sync=sync, finite=bool(np.all(np.isfinite(losses))))))
+        graphs = m._graphs[0] is not None and sum(1 for kind, _ in m._graphs[0].segments if kind == "exchange") >= 3
+        # the same six steps launched kernel by kernel, from the same initial state: the same losses up to the
+        # order of the dQ and embedding-gradient atomics
+        m2 = TinyTransformer(512, 256, 1024, 3, 4, 4, 256, dtype=torch.bfloat16, device=dev, seed=3, init_std=0.05,
+                             world_size=world, process_group=dist.group.WORLD, bucket_bytes=1 << 20)
+        m2.use_graph = False
+        losses2 = [m2.step(tok, tgt) for _ in range(6)]
+        close = all(abs(a - b) <= 2e-3 * abs(b) for a, b in zip(losses, losses2))
+        q.put((rank, dict(err=err, buckets=nb, sync=sync and m2.replicas_in_sync(),
+                          finite=bool(np.all(np.isfinite(losses))), graphs=graphs, close=close,
+                          losses=[round(x, 5) for x in losses], losses2=[round(x, 5) for x in losses2])))
         dist.barrier()
         dist.destroy_process_group()
     except Exception as e:  # reported to the parent, never swallowed
@@ -79,3 +90,4 @@ def test_two_gpu_exchange_matches_plain_allreduce_and_replicas_stay_in_sync():
         assert out[r]["buckets"] >= 3
         assert out[r]["err"] <= 2e-2, out[r]  # bf16 bucket sums against the fp32 sum of the same local gradients
         assert out[r]["sync"] and out[r]["finite"]
+        assert out[r]["graphs"] and out[r]["close"], out[r]
