@@ -155,9 +155,8 @@ class _Model:
         self.graph_launches = [0, 0]  # kernels of this library recorded in each slot's graph (= launched per replay)
         self._eager_steps = 0
         self._advanced = False      # this step's optimiser launches have already advanced the device step counter
-        # dW products on a second stream inside captured steps (see _linear_bwd): single-GPU runs,
-        # MOGRAD_B200_DW_STREAM=0 switches it off (data-parallel runs keep one compute stream: their gradient buckets
-        # are handed to the communication stream in the order the backward pass finishes them)
+        # dW products on a second stream inside captured steps (see _linear_bwd); MOGRAD_B200_DW_STREAM=0 switches
+        # it off
         self.dw_overlap = self.device.type == "cuda" and os.environ.get("MOGRAD_B200_DW_STREAM", "1") != "0"
         self.dw_stream = torch.cuda.Stream(device=self.device) if self.dw_overlap else None
         self._dw_done = {}          # name of the dY buffer -> event: the dW product that reads it has finished
