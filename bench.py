@@ -7,12 +7,17 @@ A "step" is one full train step (forward, backward, gradient exchange when
 N > 1, AdamW) on one batch of seeded synthetic data.  One JSON line is printed
 by rank 0:
 
-  value        whole-job tokens/s with the batch already resident in HBM,
-               timed with CUDA events over exactly K steps, max over ranks
+  value        whole-job tokens/s with the batch already resident in HBM
+               (Model.step_resident(): the step's captured CUDA graphs are
+               replayed), timed with CUDA events over exactly K steps, max
+               over ranks
   e2e          the same metric through the host-facing call Model.step(): the
                batch comes from pinned host memory every step (the copy of the
-               next batch is issued under the current step's kernels) and the
-               loss is read back to the host every step
+               next batch is issued under the current step's kernels, and the
+               next step is queued before this step's loss is waited for) and
+               the loss is read back to the host every step
+  gpu_launches kernels of this library run inside the timed K steps: those
+               launched directly plus those recorded in each replayed graph
   dp           N > 1 only: a check that the overlapped bf16 bucket exchange
                gives the gradients a plain fp32 all-reduce gives, that the
                replicas hold identical parameters after the timed steps, and
