@@ -321,13 +321,13 @@ def profile_case(name, reps, device):
 
 
 # ----------------------------------------------------------------------------- in-step timeline
-def step_timeline(cfg, device, steps=3):
+def step_timeline(cfg, device, steps=14):
     """Device timeline of one train step from the CUDA activity records (torch.profiler / CUPTI, no kernel
     replay): per kernel its launches and its EXCLUSIVE time inside the step, i.e. the part of each launch that does
     not overlap the kernels before it (programmatic dependent launch lets a kernel's set-up run under its
     predecessor's tail, so plain durations add up to more than the step).  Prints a table to stderr and returns
-    the rows; the numbers are of a real step at the clocks the step runs at, unlike per-launch times under a
-    replaying profiler."""
+    the rows; the numbers are of a real step (the last of `steps` consecutive ones, so that the GPU has settled at
+    the clocks its power cap allows), unlike per-launch times under a replaying profiler."""
     import collections
 
     import torch
@@ -337,9 +337,16 @@ def step_timeline(cfg, device, steps=3):
     bx, by = make_batch(cfg, seed=100)
     model.d_inputs.copy_(bx)
     model.d_targets.copy_(by)
-    for _ in range(3):
+    for _ in range(5):
         model.step_device()
+    # the same kernel-by-kernel step timed with CUDA events over 20 steps, for comparison with the span below
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        model.step_device()
+    e1.record()
     torch.cuda.synchronize()
+    print(f"20 steps launched kernel by kernel, CUDA events: {e0.elapsed_time(e1) / 20:.3f} ms per step", file=sys.stderr)
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         for _ in range(steps):
             model.step_device()
@@ -349,7 +356,9 @@ def step_timeline(cfg, device, steps=3):
     marks = [i for i, e in enumerate(ev) if "adamw" in e.name]  # the optimizer kernel closes a step
     if len(marks) < 2:
         raise SystemExit("timeline: fewer than two optimizer launches recorded")
-    step = ev[marks[0] + 1:marks[1] + 1]
+    # the last complete step: the profiler starts after an idle moment, and the first steps behind it run above the
+    # clocks the GPU settles at under its power cap
+    step = ev[marks[-2] + 1:marks[-1] + 1]
     t0 = step[0].time_range.start
     agg, prev_end = collections.OrderedDict(), t0
     for e in step:
@@ -457,6 +466,9 @@ def main():
     ap.add_argument("--timeline", action="store_true",
                     help="print the per-kernel exclusive-time table of one train step (1 GPU) and exit")
     ap.add_argument("--bucket-mb", type=int, default=64, help="gradient all-reduce bucket size (N > 1)")
+    ap.add_argument("--batches", type=int, default=8,
+                    help="distinct seeded batches per rank, used in rotation (with one or two the model memorises "
+                         "them within the run, its gradients shrink and the GPU clocks higher under its power cap)")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to stdout; the contract is one JSON line there.  Everything
     # but that line goes to stderr: fd 1 is pointed at fd 2 until emit() restores it.
@@ -534,12 +546,21 @@ def main():
         pg = dist.group.WORLD
     peaks = load_peaks()
     model = build_model(cfg, device, world, pg, seed=0, bucket_mb=args.bucket_mb)
-    # two different batches per rank, alternated step by step (both resident for the device-timed loop)
-    batches = [make_batch(cfg, seed=100 + rank), make_batch(cfg, seed=7100 + rank)]
-    for k, (bx, by) in enumerate(batches):
+    # several different batches per rank, used in rotation: pinned on the host for the end-to-end loop, resident in
+    # HBM for the device-timed loop (a step copies its batch device-to-device into the input slot it reads)
+    nb = max(2, args.batches)
+    batches = [make_batch(cfg, seed=100 + 7000 * j + rank) for j in range(nb)]
+    resident = [(bx.to(device), by.to(device)) for bx, by in batches]
+
+    def resident_step(i):
+        k = i & 1
         model.use_slot(k)
-        model.d_inputs.copy_(bx)
-        model.d_targets.copy_(by)
+        model.d_inputs.copy_(resident[i % nb][0])
+        model.d_targets.copy_(resident[i % nb][1])
+        return model.step_resident(k)
+
+    resident_step(0)  # (also gives check_data_parallel below a batch to work on)
+    torch.cuda.synchronize()
     hx, hy = batches[0]
     dp = None
     if world > 1:
@@ -559,14 +580,14 @@ def main():
     # (captured during the warm-up: two steps launched kernel by kernel, then one capture per input slot; with
     # several GPUs the capture is cut where a gradient bucket is complete and the all-reduces run between the cuts).
     for i in range(max(3, args.warmup) + 3):
-        model.step_resident(i & 1)
+        resident_step(i)
     barrier()
     l0 = lib.mograd_b200_launch_count()
     replayed = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        loss = model.step_resident(i & 1)
+        loss = resident_step(i)
         replayed += model.graph_launches[i & 1] if model._graphs[i & 1] is not None else 0
     e1.record()
     barrier()
@@ -589,11 +610,11 @@ def main():
     # successor before it waits for its own loss; the last call of each loop queues nothing, so the timed region
     # holds exactly --steps steps.
     for i in range(6):
-        model.step(*batches[i & 1], prefetch=batches[(i + 1) & 1], launch_next=i < 5)
+        model.step(*batches[i % nb], prefetch=batches[(i + 1) % nb], launch_next=i < 5)
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        last = model.step(*batches[i & 1], prefetch=batches[(i + 1) & 1], launch_next=i + 1 < args.steps)
+        last = model.step(*batches[i % nb], prefetch=batches[(i + 1) % nb], launch_next=i + 1 < args.steps)
     barrier()
     e2e_s = time.perf_counter() - t0
     if world > 1:
@@ -625,7 +646,7 @@ def main():
         line = dict(base, value=round(value, 1), ms_per_step=round(ms_per_step, 4), clocks=clocks,
                     e2e=dict(value=round(e2e_val, 1), unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=4),
                     gpu_launches=int(launches), loss=round(float(last), 4))
-        line["config"]["batches"] = "two seeded batches per rank, alternated every step"
+        line["config"]["batches"] = f"{nb} seeded batches per rank, used in rotation"
         line["config"]["launch"] = ("kernel by kernel" if model._graphs[0] is None else
                                     "one captured CUDA graph per step, replayed" if world == 1 else
                                     "captured CUDA graphs cut at the gradient-bucket boundaries, replayed, with the "
